@@ -1,0 +1,458 @@
+// Host side of the C ABI declared in include/dfb_decode.h: decoder object,
+// per-step kernel chain (programmatic dependent launch), CUDA-graph cache,
+// host-buffer step, standalone launchers.
+#include "dfb_kernels.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <vector>
+
+#include "../../include/dfb_decode.h"
+
+using namespace dfb;
+
+#define DFB_CUDA(expr)                          \
+  do {                                          \
+    cudaError_t e_ = (expr);                    \
+    if (e_ != cudaSuccess) return (int)e_;      \
+  } while (0)
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+struct Launcher {
+  cudaStream_t stream;
+  bool pdl;
+  int count = 0;
+  int err = 0;
+  template <typename Args>
+  void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true) {
+    if (err) return;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && allow_pdl) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
+    if (e != cudaSuccess) err = (int)e;
+    ++count;
+  }
+};
+
+}  // namespace
+
+struct DfbHandle {
+  DfbModelDesc m;
+  std::vector<DfbLayerWeights> layers;
+  int device = 0;
+  int sm_count = 148;
+  int max_pages = 0;
+  size_t kv_layer_elems = 0;
+  // options
+  bool use_graph = true;
+  bool use_pdl = true;
+  int lmhead_ctas = 0;
+  // device scratch (one slab)
+  void* slab = nullptr;
+  int* stage = nullptr;          // ids[8] | positions[8] | row_active[8] | block_tables[8, max_pages]
+  bf16* hbuf = nullptr;          // [8, hidden]   output of o_proj / down_proj
+  bf16* res[2] = {nullptr, nullptr};
+  bf16* qkv = nullptr;           // [8, qkv_rows]
+  bf16* attn = nullptr;          // [8, q_size]
+  bf16* act = nullptr;           // [8, intermediate]
+  float* part_o = nullptr;
+  float2* part_ml = nullptr;
+  unsigned int* tickets = nullptr;  // [8*kv_heads] attention + [1] lm head
+  ArgmaxPart* parts = nullptr;
+  int* tokens = nullptr;         // [8]
+  int* status = nullptr;         // [4]
+  // pinned host staging
+  int* host_stage = nullptr;
+  int* host_tokens = nullptr;
+  cudaStream_t capture_stream = nullptr;
+  std::map<int, cudaGraphExec_t> graphs;
+  int64_t steps = 0;
+  int kernels_per_step = 0;
+  int last_status[4] = {0, 0, 0, 0};  // last non-zero status word seen by a host-buffer step
+  int qkv_rows() const { return (m.q_heads + 2 * m.kv_heads) * m.head_dim; }
+  int q_size() const { return m.q_heads * m.head_dim; }
+  int kv_size() const { return m.kv_heads * m.head_dim; }
+  int* st_ids() const { return stage; }
+  int* st_pos() const { return stage + 8; }
+  int* st_active() const { return stage + 16; }
+  int* st_bt() const { return stage + 24; }
+  int stage_ints() const { return 24 + 8 * max_pages; }
+};
+
+namespace {
+
+int loads_for_k(int k) { return (k % 256 == 0) ? k / 256 : 0; }
+
+// ---- kernel launch wrappers -------------------------------------------------
+int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_in, bf16* res_out, const bf16* ln_w,
+                    const bf16* w, bf16* out, int rows, int hidden, int n, float eps, bool allow_pdl) {
+  if (hidden != 1024 || n % kTileRows) return DFB_E_GEOMETRY;
+  GemvArgs a = {};
+  a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = hidden;
+  a.x = x; a.ids = ids; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
+  a.out = out; a.out_stride = n;
+  const int grid = a.n_tiles < 256 ? a.n_tiles : 256;
+  L.launch(stream_gemv_kernel<4, 2, kModeNormStore>, dim3(grid), dim3(kThreads), a, allow_pdl);
+  return L.err;
+}
+
+int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows, int n, int k) {
+  if (n % kTileRows) return DFB_E_GEOMETRY;
+  GemvArgs a = {};
+  a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = k; a.x = x; a.out = out; a.out_stride = n;
+  const int grid = a.n_tiles < 296 ? a.n_tiles : 296;
+  switch (loads_for_k(k)) {
+    case 4: L.launch(stream_gemv_kernel<4, 2, kModeStore>, dim3(grid), dim3(kThreads), a); break;
+    case 8: L.launch(stream_gemv_kernel<8, 1, kModeStore>, dim3(grid), dim3(kThreads), a); break;
+    case 12: L.launch(stream_gemv_kernel<12, 1, kModeStore>, dim3(grid), dim3(kThreads), a); break;
+    default: return DFB_E_GEOMETRY;
+  }
+  return L.err;
+}
+
+int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out, const bf16* ln_w, const bf16* wgu,
+                  bf16* act, int rows, int hidden, int inter, float eps) {
+  if (hidden != 1024 || inter % 4) return DFB_E_GEOMETRY;
+  GemvArgs a = {};
+  a.w = wgu; a.n_tiles = inter / 4; a.rows = rows; a.k = hidden;
+  a.x = h; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
+  a.out = act; a.out_stride = inter; a.gate_rows = inter;
+  const int grid = a.n_tiles < 256 ? a.n_tiles : 256;
+  L.launch(stream_gemv_kernel<4, 3, kModeNormSwiglu>, dim3(grid), dim3(kThreads), a);
+  return L.err;
+}
+
+int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in, int rows, int* tokens_out,
+                  float* logits_out) {
+  const DfbModelDesc& m = h->m;
+  GemvArgs a = {};
+  a.w = (const bf16*)m.embed; a.n_tiles = m.vocab / kTileRows; a.rows = rows; a.k = m.hidden;
+  a.x = hid; a.res_in = res_in; a.norm_w = (const bf16*)m.final_norm; a.eps = m.eps;
+  a.logits_out = logits_out; a.vocab = m.vocab;
+  a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens; a.tokens_out = tokens_out;
+  int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 2 * h->sm_count;
+  if (grid > a.n_tiles) grid = a.n_tiles;
+  L.launch(stream_gemv_kernel<4, 3, kModeNormArgmax>, dim3(grid), dim3(kThreads), a);
+  return L.err;
+}
+
+int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
+                     int bt_stride, const int* row_active, bf16* out, int rows, int nsplit) {
+  const DfbModelDesc& m = h->m;
+  AttnArgs a = {};
+  a.qkv = qkv; a.qkv_stride = h->qkv_rows(); a.q_size = h->q_size(); a.kv_size = h->kv_size();
+  a.positions = positions; a.block_tables = bt; a.bt_stride = bt_stride; a.row_active = row_active;
+  a.q_norm = (const bf16*)h->layers[layer].q_norm; a.k_norm = (const bf16*)h->layers[layer].k_norm;
+  a.cos_sin = m.rope_cos_sin; a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim);
+  a.k_cache = (bf16*)m.k_cache + (size_t)layer * h->kv_layer_elems;
+  a.v_cache = (bf16*)m.v_cache + (size_t)layer * h->kv_layer_elems;
+  a.block_size = m.block_size; a.kv_heads = m.kv_heads; a.num_blocks = m.num_blocks; a.max_pos = m.max_model_len;
+  a.out = out; a.part_o = h->part_o; a.part_ml = h->part_ml; a.tickets = h->tickets; a.status = h->status;
+  L.launch(paged_attention_kernel, dim3(nsplit, m.kv_heads, rows), dim3(kAttnThreads), a);
+  return L.err;
+}
+
+int split_bucket(const DfbHandle* h, int max_context) {
+  if (max_context < 1) max_context = 1;
+  if (max_context > h->m.max_model_len) max_context = h->m.max_model_len;
+  const int need = (max_context + kAttnChunk - 1) / kAttnChunk;
+  int b = 1;
+  while (b < need) b <<= 1;
+  return b > kMaxSplits ? kMaxSplits : b;
+}
+
+// The whole step as one chain of 5 kernels per layer + the LM head.
+int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
+  const DfbModelDesc& m = h->m;
+  Launcher L{stream, h->use_pdl};
+  int rc = 0;
+  int cur = 0;  // index of the residual buffer holding the current residual
+  for (int l = 0; l < m.layers && !rc; ++l) {
+    const DfbLayerWeights& w = h->layers[l];
+    if (l == 0) {
+      // embedding rows are gathered by token id; the residual starts as the embedding itself.
+      // No PDL on the first kernel: it must observe the staged inputs of this step.
+      rc = launch_norm_qkv(L, (const bf16*)m.embed, h->st_ids(), nullptr, h->res[cur], (const bf16*)w.ln_in,
+                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, false);
+    } else {
+      rc = launch_norm_qkv(L, h->hbuf, nullptr, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_in,
+                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, true);
+      cur ^= 1;
+    }
+    if (rc) break;
+    rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, h->st_active(), h->attn, rows, nsplit);
+    if (rc) break;
+    rc = launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size());
+    if (rc) break;
+    rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
+                       rows, m.hidden, m.intermediate, m.eps);
+    cur ^= 1;
+    if (rc) break;
+    rc = launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate);
+  }
+  if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
+  h->kernels_per_step = L.count;
+  return rc ? rc : L.err;
+}
+
+int run_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
+  if (!h->use_graph || logits_out) return enqueue_step(h, rows, nsplit, stream, logits_out);
+  const int key = rows * 64 + nsplit + (h->use_pdl ? 4096 : 0);
+  auto it = h->graphs.find(key);
+  if (it == h->graphs.end()) {
+    cudaGraph_t graph = nullptr;
+    DFB_CUDA(cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_step(h, rows, nsplit, h->capture_stream, nullptr);
+    cudaError_t e = cudaStreamEndCapture(h->capture_stream, &graph);
+    if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) return (int)e;
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return (int)e;
+    it = h->graphs.emplace(key, exec).first;
+  }
+  DFB_CUDA(cudaGraphLaunch(it->second, stream));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* dfb_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case DFB_E_BAD_ARG: return "dfb: bad argument";
+    case DFB_E_GEOMETRY: return "dfb: unsupported model geometry";
+    case DFB_E_ABI: return "dfb: ABI version mismatch";
+    case DFB_E_DEVICE_STATUS: return "dfb: a kernel reported an error (see dfb_read_status)";
+    case DFB_E_TOO_LARGE: return "dfb: request exceeds a fixed capacity";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "dfb: unknown error";
+  }
+}
+
+int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
+  if (!d || !out) return DFB_E_BAD_ARG;
+  *out = nullptr;
+  if (d->abi_version != DFB_ABI_VERSION) return DFB_E_ABI;
+  if (d->hidden != 1024 || d->head_dim != kHeadDim || d->q_heads != 2 * d->kv_heads || d->kv_heads < 1 ||
+      d->kv_heads > 8 || d->layers < 1 || d->vocab % kTileRows || d->vocab < kTileRows ||
+      d->intermediate % 256 || loads_for_k(d->intermediate) != 12 || loads_for_k(d->q_heads * d->head_dim) != 8 ||
+      d->max_model_len < 1 || d->max_model_len > kMaxSplits * kAttnChunk || d->block_size < kAttnChunk ||
+      d->block_size % kAttnChunk || d->num_blocks < 1)
+    return DFB_E_GEOMETRY;
+  if (!d->embed || !d->final_norm || !d->rope_cos_sin || !d->layer_weights || !d->k_cache || !d->v_cache)
+    return DFB_E_BAD_ARG;
+  DfbHandle* h = new (std::nothrow) DfbHandle();
+  if (!h) return (int)cudaErrorMemoryAllocation;
+  h->m = *d;
+  h->layers.assign(d->layer_weights, d->layer_weights + d->layers);
+  h->m.layer_weights = nullptr;
+  for (const DfbLayerWeights& w : h->layers)
+    if (!w.ln_in || !w.wqkv || !w.q_norm || !w.k_norm || !w.wo || !w.ln_post || !w.wgu || !w.wd) {
+      delete h;
+      return DFB_E_BAD_ARG;
+    }
+  cudaError_t e = cudaGetDevice(&h->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, h->device);
+  if (e != cudaSuccess) { delete h; return (int)e; }
+  h->max_pages = (d->max_model_len + d->block_size - 1) / d->block_size;
+  h->kv_layer_elems = (size_t)d->num_blocks * d->block_size * d->kv_heads * d->head_dim;
+
+  // one slab, 256-byte aligned pieces
+  size_t off = 0;
+  auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+  const size_t o_stage = carve(sizeof(int) * h->stage_ints());
+  const size_t o_h = carve(sizeof(bf16) * kMaxRows * d->hidden);
+  const size_t o_r0 = carve(sizeof(bf16) * kMaxRows * d->hidden);
+  const size_t o_r1 = carve(sizeof(bf16) * kMaxRows * d->hidden);
+  const size_t o_qkv = carve(sizeof(bf16) * kMaxRows * h->qkv_rows());
+  const size_t o_attn = carve(sizeof(bf16) * kMaxRows * h->q_size());
+  const size_t o_act = carve(sizeof(bf16) * kMaxRows * d->intermediate);
+  const size_t o_po = carve(sizeof(float) * kMaxRows * d->kv_heads * kMaxSplits * 2 * kHeadDim);
+  const size_t o_pml = carve(sizeof(float2) * kMaxRows * d->kv_heads * kMaxSplits * 2);
+  const size_t o_tk = carve(sizeof(unsigned) * (kMaxRows * d->kv_heads + 1));
+  const size_t o_parts = carve(sizeof(ArgmaxPart) * kMaxRows * 4096);
+  const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
+  e = cudaMalloc(&h->slab, off);
+  if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_tokens, sizeof(int) * (kMaxRows + 4));
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { dfb_destroy(h); return (int)e; }
+  char* s = (char*)h->slab;
+  h->stage = (int*)(s + o_stage); h->hbuf = (bf16*)(s + o_h);
+  h->res[0] = (bf16*)(s + o_r0); h->res[1] = (bf16*)(s + o_r1);
+  h->qkv = (bf16*)(s + o_qkv); h->attn = (bf16*)(s + o_attn); h->act = (bf16*)(s + o_act);
+  h->part_o = (float*)(s + o_po); h->part_ml = (float2*)(s + o_pml); h->tickets = (unsigned*)(s + o_tk);
+  h->parts = (ArgmaxPart*)(s + o_parts); h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
+  *out = h;
+  return 0;
+}
+
+void dfb_destroy(DfbHandle* h) {
+  if (!h) return;
+  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
+  if (h->host_stage) cudaFreeHost(h->host_stage);
+  if (h->host_tokens) cudaFreeHost(h->host_tokens);
+  if (h->slab) cudaFree(h->slab);
+  delete h;
+}
+
+int dfb_set_option(DfbHandle* h, int option, int value) {
+  if (!h) return DFB_E_BAD_ARG;
+  switch (option) {
+    case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
+    case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
+    case DFB_OPT_LMHEAD_CTAS:
+      if (value < 0 || value > 4096) return DFB_E_BAD_ARG;
+      h->lmhead_ctas = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    default: return DFB_E_BAD_ARG;
+  }
+}
+
+int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
+  if (!h || !s) return DFB_E_BAD_ARG;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (s->rows < 1 || s->rows > kMaxRows || !s->positions || !s->block_tables) return DFB_E_BAD_ARG;
+  if (s->block_table_cols < 1 || s->block_table_stride < s->block_table_cols) return DFB_E_BAD_ARG;
+  if (s->block_table_cols > h->max_pages) return DFB_E_TOO_LARGE;
+  StageArgs a = {};
+  a.ids = s->input_ids; a.positions = s->positions; a.block_tables = s->block_tables;
+  a.bt_cols = s->block_table_cols; a.bt_stride_in = s->block_table_stride; a.bt_stride_out = h->max_pages;
+  a.row_active = s->row_active; a.rows = s->rows;
+  a.ids_out = s->input_ids ? h->st_ids() : nullptr; a.positions_out = h->st_pos(); a.bt_out = h->st_bt();
+  a.row_active_out = h->st_active();
+  if (!s->input_ids) {
+    // feedback: the previous step's tokens become this step's input ids
+    DFB_CUDA(cudaMemcpyAsync(h->st_ids(), h->tokens, sizeof(int) * s->rows, cudaMemcpyDeviceToDevice, stream));
+  }
+  stage_inputs_kernel<<<1, 128, 0, stream>>>(a);
+  DFB_CUDA(cudaGetLastError());
+  const int bound = s->max_context > 0 ? s->max_context : s->block_table_cols * h->m.block_size;
+  int rc = run_step(h, s->rows, split_bucket(h, bound), stream, s->out_logits);
+  if (rc) return rc;
+  if (s->out_tokens)
+    DFB_CUDA(cudaMemcpyAsync(s->out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
+  ++h->steps;
+  return 0;
+}
+
+int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
+                         const int32_t* block_tables, int32_t cols, const int32_t* row_active, int32_t* out_tokens,
+                         dfb_stream_t stream_) {
+  if (!h || !input_ids || !positions || !block_tables || !out_tokens) return DFB_E_BAD_ARG;
+  if (rows < 1 || rows > kMaxRows || cols < 1) return DFB_E_BAD_ARG;
+  if (cols > h->max_pages) return DFB_E_TOO_LARGE;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int* hs = h->host_stage;
+  int max_ctx = 1;
+  for (int r = 0; r < rows; ++r) {
+    if (positions[r] < 0 || positions[r] >= h->m.max_model_len) return DFB_E_BAD_ARG;
+    if (input_ids[r] < 0 || input_ids[r] >= h->m.vocab) return DFB_E_BAD_ARG;
+    hs[r] = (int)input_ids[r];
+    hs[8 + r] = (int)positions[r];
+    hs[16 + r] = row_active ? row_active[r] : 1;
+    if (positions[r] + 1 > max_ctx) max_ctx = (int)positions[r] + 1;
+    for (int c = 0; c < cols; ++c) hs[24 + r * h->max_pages + c] = block_tables[r * cols + c];
+  }
+  DFB_CUDA(cudaMemcpyAsync(h->stage, hs, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
+  int rc = run_step(h, rows, split_bucket(h, max_ctx), stream, nullptr);
+  if (rc) return rc;
+  DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
+  DFB_CUDA(cudaStreamSynchronize(stream));
+  for (int r = 0; r < rows; ++r) out_tokens[r] = h->host_tokens[r];
+  ++h->steps;
+  if (h->host_tokens[kMaxRows]) {
+    h->last_status[0] = h->host_tokens[kMaxRows]; h->last_status[1] = h->host_tokens[kMaxRows + 1];
+    h->last_status[2] = h->host_tokens[kMaxRows + 2]; h->last_status[3] = h->host_tokens[kMaxRows + 3];
+    DFB_CUDA(cudaMemsetAsync(h->status, 0, sizeof(int) * 4, stream));
+    return DFB_E_DEVICE_STATUS;
+  }
+  return 0;
+}
+
+int dfb_read_status(DfbHandle* h, DfbStatus* out) {
+  if (!h || !out) return DFB_E_BAD_ARG;
+  int st[4];
+  DFB_CUDA(cudaMemcpy(st, h->status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (!st[0] && h->last_status[0]) {
+    memcpy(st, h->last_status, sizeof(st));
+    memset(h->last_status, 0, sizeof(h->last_status));
+    out->device_status = st[0];
+    out->detail[0] = st[1]; out->detail[1] = st[2]; out->detail[2] = st[3];
+    out->steps = h->steps;
+    out->kernels_per_step = h->kernels_per_step;
+    return DFB_E_DEVICE_STATUS;
+  }
+  out->device_status = st[0];
+  out->detail[0] = st[1]; out->detail[1] = st[2]; out->detail[2] = st[3];
+  out->steps = h->steps;
+  out->kernels_per_step = h->kernels_per_step;
+  if (st[0]) DFB_CUDA(cudaMemset(h->status, 0, sizeof(st)));
+  return st[0] ? DFB_E_DEVICE_STATUS : 0;
+}
+
+// ---- standalone launchers ----------------------------------------------------
+int dfb_launch_rmsnorm_qkv(const void* hh, const int32_t* ids, const void* residual, void* residual_out,
+                           const void* ln_w, const void* wqkv, void* qkv_out, int32_t rows, int32_t hidden,
+                           int32_t qkv_rows, float eps, dfb_stream_t stream) {
+  if (!hh || !ln_w || !wqkv || !qkv_out || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
+  if (ids && residual) return DFB_E_BAD_ARG;
+  Launcher L{(cudaStream_t)stream, false};
+  return launch_norm_qkv(L, (const bf16*)hh, ids, (const bf16*)residual, (bf16*)residual_out, (const bf16*)ln_w,
+                         (const bf16*)wqkv, (bf16*)qkv_out, rows, hidden, qkv_rows, eps, false);
+}
+
+int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int32_t* positions,
+                         const int32_t* block_tables, int32_t block_table_stride, const int32_t* row_active,
+                         void* attn_out, int32_t rows, int32_t max_context, dfb_stream_t stream) {
+  if (!h || !qkv || !positions || !block_tables || !attn_out) return DFB_E_BAD_ARG;
+  if (rows < 1 || rows > kMaxRows || layer < 0 || layer >= h->m.layers) return DFB_E_BAD_ARG;
+  Launcher L{(cudaStream_t)stream, false};
+  return launch_attention(L, h, layer, (const bf16*)qkv, positions, block_tables, block_table_stride, row_active,
+                          (bf16*)attn_out, rows, split_bucket(h, max_context > 0 ? max_context : h->m.max_model_len));
+}
+
+int dfb_launch_linear(const void* x, const void* w, void* out, int32_t rows, int32_t n, int32_t k,
+                      dfb_stream_t stream) {
+  if (!x || !w || !out || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
+  Launcher L{(cudaStream_t)stream, false};
+  return launch_linear(L, (const bf16*)x, (const bf16*)w, (bf16*)out, rows, n, k);
+}
+
+int dfb_launch_rmsnorm_gateup_swiglu(const void* hh, const void* residual, void* residual_out, const void* ln_w,
+                                     const void* wgu, void* act_out, int32_t rows, int32_t hidden,
+                                     int32_t intermediate, float eps, dfb_stream_t stream) {
+  if (!hh || !residual || !ln_w || !wgu || !act_out || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
+  Launcher L{(cudaStream_t)stream, false};
+  return launch_gateup(L, (const bf16*)hh, (const bf16*)residual, (bf16*)residual_out, (const bf16*)ln_w,
+                       (const bf16*)wgu, (bf16*)act_out, rows, hidden, intermediate, eps);
+}
+
+int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,
+                             float* out_logits, int32_t rows, dfb_stream_t stream) {
+  if (!h || !hidden_in || !residual || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
+  Launcher L{(cudaStream_t)stream, false};
+  return launch_lmhead(L, h, (const bf16*)hidden_in, (const bf16*)residual, rows, out_tokens, out_logits);
+}
+
+}  // extern "C"

@@ -1,0 +1,587 @@
+// Device code of the Qwen3 decode step for sm_100a.
+//
+// Two kernel families:
+//   * stream_gemv_kernel<LOADS, DEPTH, MODE>: a weight-streaming skinny GEMM
+//     out[rows<=8, N] = x[rows, K] @ W[N, K]^T with a fused prologue (residual
+//     add + RMSNorm, or the embedding gather) and a fused epilogue (bf16 store,
+//     SwiGLU, or bf16-rounded logits + greedy argmax).
+//   * paged_attention_kernel: q/k RMSNorm + RoPE + KV-cache write + split-KV
+//     paged GQA decode attention with an in-kernel merge of the splits.
+//
+// Every kernel is an ordinary (non-cooperative) launch.  Inside a step they are
+// chained with programmatic dependent launch: each kernel first lets its
+// successor start (griddepcontrol.launch_dependents), issues the loads that do
+// not depend on its predecessor (its weights / the old KV entries), and only
+// then waits for the predecessor (griddepcontrol.wait).  No kernel spins on a
+// flag: the two cross-CTA reductions use the "last CTA to arrive finishes the
+// job" pattern (one atomic ticket per CTA), so there is no unbounded wait.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dfb {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxRows = 8;
+constexpr int kTileRows = 8;          // weight rows per tile = N of mma.m16n8k16
+constexpr int kAttnThreads = 128;
+constexpr int kAttnChunk = 64;        // context positions per attention CTA
+constexpr int kHeadDim = 128;
+constexpr int kMaxSplits = 32;        // 2048 / kAttnChunk
+
+enum GemvMode : int {
+  kModeStore = 0,      // plain x, bf16 store            (o_proj, down_proj)
+  kModeNormStore = 1,  // add+RMSNorm prologue, bf16 store (qkv_proj)
+  kModeNormSwiglu = 2, // add+RMSNorm prologue, SwiGLU epilogue (gate_up_proj)
+  kModeNormArgmax = 3, // add+RMSNorm prologue, logits + argmax (lm_head)
+};
+
+struct __align__(8) ArgmaxPart {
+  float value;
+  int index;
+};
+
+struct GemvArgs {
+  const __nv_bfloat16* w;        // [N, K] row-major
+  int n_tiles;                   // tiles of 8 output rows (SwiGLU: 4 gate + 4 up rows)
+  int rows;                      // batch rows, 1..8
+  int k;                         // K (= LOADS * 256)
+  // prologue
+  const __nv_bfloat16* x;        // [rows, K] input (norm modes: hidden state or embedding table)
+  const int* ids;                // norm modes: if non-null, x row r = x[ids[r]]
+  const __nv_bfloat16* res_in;   // norm modes: residual or null
+  __nv_bfloat16* res_out;        // norm modes: new residual or null
+  const __nv_bfloat16* norm_w;   // [K]
+  float eps;
+  // epilogue
+  __nv_bfloat16* out;            // [rows, out_stride]
+  int out_stride;
+  int gate_rows;                 // SwiGLU: intermediate size (up rows start here)
+  float* logits_out;             // argmax: optional [rows, vocab] fp32
+  int vocab;
+  ArgmaxPart* parts;             // argmax: [gridDim.x, 8]
+  unsigned int* ticket;          // argmax: arrival counter (self-resetting)
+  int* tokens;                   // argmax: [rows] result (feedback buffer)
+  int* tokens_out;               // argmax: optional second copy
+};
+
+// ---------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Streaming 128-bit weight load: read-only path, no L1 allocation.
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// Coherent 128-bit load served from L2: for data written by the previous kernel.
+__device__ __forceinline__ uint4 ldg_cg(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+  f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // A rows 8..15 (a1, a3) are always zero: the batch has at most 8 rows.
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// Device-side error reporting: the first error of a step wins; the kernel goes
+// on with a safe substitute value and the host reads the word after the step.
+constexpr int kStatusBadPosition = 1;
+constexpr int kStatusBadBlock = 2;
+constexpr int kKernelAttention = 2;
+__device__ __forceinline__ void report_status(int* status, int code, int kernel, int index, int value) {
+  if (status && atomicCAS(status, 0, code) == 0) {
+    status[1] = kernel;
+    status[2] = index;
+    status[3] = value;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Weight-streaming skinny GEMM.
+//
+// One tile = 8 weight rows x K.  The 8 warps of a CTA split K: warp w owns
+// columns [w*K/8, (w+1)*K/8) = LOADS blocks of 32 columns.  In block j, lane
+// (g = lane/4, t = lane%4) loads the 16 bytes W[row g][32j + 8t .. +7] and the
+// matching 16 bytes of x[batch g]; word pairs (0,1) and (2,3) feed two
+// m16n8k16 MMAs with the batch on M and the weight rows on N.  The k order
+// inside an MMA is a fixed permutation applied to both operands, which a dot
+// product does not care about.  x fragments are loaded once per CTA and stay in
+// registers; weights are double/triple buffered in registers (DEPTH tiles in
+// flight), and the first DEPTH tiles are requested BEFORE the dependency wait.
+// ---------------------------------------------------------------------------
+template <int LOADS, int DEPTH, int MODE>
+__global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a) {
+  constexpr bool kNorm = MODE != kModeStore;
+  pdl_launch_dependents();
+
+  __shared__ float red[2][kWarps][64];
+  __shared__ float ssq[kWarps][kMaxRows];
+  __shared__ int last_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = LOADS * 256;
+  const int kbase = warp * (LOADS * 32) + 8 * t;  // this lane's first column
+  const int stride = gridDim.x;
+
+  auto weight_ptr = [&](int tile) -> const __nv_bfloat16* {
+    int row;
+    if (MODE == kModeNormSwiglu) row = ((g & 1) ? a.gate_rows : 0) + tile * 4 + (g >> 1);
+    else row = tile * kTileRows + g;
+    return a.w + (size_t)row * K + kbase;
+  };
+
+  // ---- weight prefetch, independent of the previous kernel ----
+  uint4 wbuf[DEPTH][LOADS];
+  int tile = blockIdx.x;
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    const int tl = tile + d * stride;
+    if (tl < a.n_tiles) {
+      const __nv_bfloat16* p = weight_ptr(tl);
+#pragma unroll
+      for (int j = 0; j < LOADS; ++j) wbuf[d][j] = ldg_stream(p + 32 * j);
+    }
+  }
+  uint4 nw[kNorm ? LOADS : 1];
+  if (kNorm) {
+#pragma unroll
+    for (int j = 0; j < LOADS; ++j) nw[j] = ldg_stream(a.norm_w + kbase + 32 * j);
+  }
+
+  pdl_wait();
+
+  // ---- prologue: this lane's fragments of x[batch g] ----
+  uint4 xa[LOADS];
+  const bool live = g < a.rows;
+  if (!kNorm) {
+#pragma unroll
+    for (int j = 0; j < LOADS; ++j)
+      xa[j] = live ? ldg_cg(a.x + (size_t)g * K + kbase + 32 * j) : make_uint4(0, 0, 0, 0);
+  } else {
+    float xs[LOADS][8];
+    float ss = 0.f;
+    if (live) {
+      const size_t xrow = a.ids ? (size_t)a.ids[g] : (size_t)g;
+      uint4 hv[LOADS], rv[LOADS];
+#pragma unroll
+      for (int j = 0; j < LOADS; ++j) {
+        hv[j] = ldg_cg(a.x + xrow * K + kbase + 32 * j);
+        rv[j] = a.res_in ? ldg_cg(a.res_in + (size_t)g * K + kbase + 32 * j) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < LOADS; ++j) {
+        float hf[8], rf[8];
+        unpack8(hv[j], hf);
+        unpack8(rv[j], rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xs[j][e] = hf[e] + rf[e];
+          ss += xs[j][e] * xs[j][e];
+        }
+        if (a.res_out && blockIdx.x == 0) {
+          uint4 o;
+          o.x = pack_bf16(xs[j][0], xs[j][1]); o.y = pack_bf16(xs[j][2], xs[j][3]);
+          o.z = pack_bf16(xs[j][4], xs[j][5]); o.w = pack_bf16(xs[j][6], xs[j][7]);
+          *reinterpret_cast<uint4*>(a.res_out + (size_t)g * K + kbase + 32 * j) = o;
+        }
+      }
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    if (t == 0) ssq[warp][g] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) tot += ssq[w][g];
+    const float rstd = 1.0f / sqrtf(tot / (float)K + a.eps);
+#pragma unroll
+    for (int j = 0; j < LOADS; ++j) {
+      float wf[8], y[8];
+      unpack8(nw[j], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = live ? round_bf16(xs[j][e] * rstd) * wf[e] : 0.f;
+      xa[j].x = pack_bf16(y[0], y[1]); xa[j].y = pack_bf16(y[2], y[3]);
+      xa[j].z = pack_bf16(y[4], y[5]); xa[j].w = pack_bf16(y[6], y[7]);
+    }
+  }
+
+  // ---- main loop over this CTA's tiles ----
+  const int eb = tid >> 3, er = tid & 7;  // epilogue thread -> (batch row, tile row)
+  float best_v = -INFINITY;
+  int best_i = 0x7fffffff;
+  int it = 0;
+  while (tile < a.n_tiles) {
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (tile < a.n_tiles) {
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) {
+          mma_bf16_16816(c0, xa[j].x, xa[j].y, wbuf[d][j].x, wbuf[d][j].y);
+          mma_bf16_16816(c1, xa[j].z, xa[j].w, wbuf[d][j].z, wbuf[d][j].w);
+        }
+        const int nxt = tile + DEPTH * stride;
+        if (nxt < a.n_tiles) {
+          const __nv_bfloat16* p = weight_ptr(nxt);
+#pragma unroll
+          for (int j = 0; j < LOADS; ++j) wbuf[d][j] = ldg_stream(p + 32 * j);
+        }
+        float* r = red[it & 1][warp];
+        *reinterpret_cast<float2*>(r + 2 * lane) = make_float2(c0[0] + c1[0], c0[1] + c1[1]);
+        __syncthreads();
+        if (tid < 64) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) v += red[it & 1][w][tid];
+          v = round_bf16(v);
+          if (MODE == kModeStore || MODE == kModeNormStore) {
+            if (eb < a.rows) a.out[(size_t)eb * a.out_stride + tile * kTileRows + er] = __float2bfloat16_rn(v);
+          } else if (MODE == kModeNormSwiglu) {
+            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+            if (!(er & 1) && eb < a.rows) {
+              const float act = v / (1.0f + expf(-v)) * up;
+              a.out[(size_t)eb * a.out_stride + tile * 4 + (er >> 1)] = __float2bfloat16_rn(act);
+            }
+          } else {
+            const int idx = tile * kTileRows + er;
+            if (eb < a.rows) {
+              if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + idx] = v;
+              if (v > best_v || (v == best_v && idx < best_i)) { best_v = v; best_i = idx; }
+            }
+          }
+        }
+        tile += stride;
+        ++it;
+      }
+    }
+  }
+
+  if (MODE == kModeNormArgmax) {
+    // reduce over the 8 tile-row threads of each batch row, then over CTAs
+    if (tid < 64) {
+#pragma unroll
+      for (int m = 1; m < 8; m <<= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best_v, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, m);
+        if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+      }
+      if (er == 0) a.parts[blockIdx.x * kMaxRows + eb] = ArgmaxPart{best_v, best_i};
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last_flag = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (last_flag) {
+      __threadfence();
+      const int b = warp;  // one warp per batch row
+      if (b < a.rows) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int c = lane; c < (int)gridDim.x; c += 32) {
+          const int2 raw = __ldcg(reinterpret_cast<const int2*>(a.parts + c * kMaxRows + b));
+          const ArgmaxPart p{__int_as_float(raw.x), raw.y};
+          if (p.value > v || (p.value == v && p.index < i)) { v = p.value; i = p.index; }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, m);
+          const int oi = __shfl_xor_sync(0xffffffffu, i, m);
+          if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+        }
+        if (lane == 0) {
+          a.tokens[b] = i;
+          if (a.tokens_out) a.tokens_out[b] = i;
+        }
+      }
+      if (tid == 0) *a.ticket = 0u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Paged GQA decode attention with fused q/k RMSNorm + RoPE + KV-cache write.
+// grid = (splits, kv_heads, rows), 128 threads.  CTA (s, h, r) covers context
+// positions [64 s, 64 s + 64) of row r for KV head h and its two query heads.
+// ---------------------------------------------------------------------------
+struct AttnArgs {
+  const __nv_bfloat16* qkv;     // [rows, qkv_stride]: q | k | v of the new token (pre-norm)
+  int qkv_stride;
+  int q_size, kv_size;          // 2048, 1024
+  const int* positions;         // [rows]
+  const int* block_tables;      // [rows, bt_stride]
+  int bt_stride;
+  const int* row_active;        // [rows] or null
+  const __nv_bfloat16* q_norm;  // [128]
+  const __nv_bfloat16* k_norm;  // [128]
+  const float* cos_sin;         // [max_pos, 128]
+  float eps;
+  float scale;
+  __nv_bfloat16* k_cache;       // this layer: [blocks, block_size, kv_heads, 128]
+  __nv_bfloat16* v_cache;
+  int block_size;
+  int kv_heads;
+  int num_blocks;
+  int max_pos;
+  int* status;                  // [4]: code, kernel id, index, observed value
+  __nv_bfloat16* out;           // [rows, q_size]
+  float* part_o;                // [rows, kv_heads, kMaxSplits, 2, 128]
+  float2* part_ml;              // [rows, kv_heads, kMaxSplits, 2] (max, sum)
+  unsigned int* tickets;        // [rows, kv_heads]
+};
+
+__global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const AttnArgs a) {
+  pdl_launch_dependents();
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int tid = threadIdx.x;
+  int pos = a.positions[row];
+  if (pos < 0 || pos >= a.max_pos) {
+    // A position outside the RoPE table / block table: record it and carry on
+    // with a clamped value so that no address is formed from it.
+    report_status(a.status, kStatusBadPosition, kKernelAttention, row, pos);
+    pos = pos < 0 ? 0 : a.max_pos - 1;
+  }
+  const int ctx = pos + 1;
+  const int nsplits = (ctx + kAttnChunk - 1) / kAttnChunk;
+  if (split >= nsplits) return;  // split 0 always stays and orders the grid after its predecessor
+
+  __shared__ float qs[2][kHeadDim];
+  __shared__ __align__(16) __nv_bfloat16 ks[kHeadDim];
+  __shared__ __align__(16) __nv_bfloat16 vs[kHeadDim];
+  __shared__ float mred[8][2];
+  __shared__ float lred[8][2];
+  __shared__ float ored[8][2][kHeadDim];
+  __shared__ int last_flag;
+
+  const int start = split * kAttnChunk;
+  const int end = min(ctx, start + kAttnChunk);
+  const bool owner = split == nsplits - 1;  // the chunk holding the new token
+  const int pg = tid >> 4, l16 = tid & 15;  // position group, 16-byte slice of the head
+  int block = a.block_tables[row * a.bt_stride + start / a.block_size];
+  if (block < 0 || block >= a.num_blocks) {
+    report_status(a.status, kStatusBadBlock, kKernelAttention, row, block);
+    block = 0;
+  }
+  const size_t tok_stride = (size_t)a.kv_heads * kHeadDim;
+  const size_t base = ((size_t)block * a.block_size + (start % a.block_size)) * tok_stride + (size_t)kvh * kHeadDim + 8 * l16;
+
+  // ---- old KV entries: independent of the previous kernel ----
+  uint4 kreg[8], vreg[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int p = start + pg + 8 * i;
+    if (p < end && p != pos) {
+      kreg[i] = ldg_stream(a.k_cache + base + (size_t)(pg + 8 * i) * tok_stride);
+      vreg[i] = ldg_stream(a.v_cache + base + (size_t)(pg + 8 * i) * tok_stride);
+    } else {
+      kreg[i] = make_uint4(0, 0, 0, 0);
+      vreg[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  pdl_wait();
+
+  // ---- new token: q (2 heads) and k get RMSNorm + RoPE, v is copied ----
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    const __nv_bfloat16* src = a.qkv + (size_t)row * a.qkv_stride;
+    if (warp < 3) {
+      const __nv_bfloat16* vec = warp < 2 ? src + (2 * kvh + warp) * kHeadDim : src + a.q_size + kvh * kHeadDim;
+      const __nv_bfloat16* nw = warp < 2 ? a.q_norm : a.k_norm;
+      const int d = 2 * lane;  // handles d, d+1 and their RoPE partners d+64, d+65
+      const uint32_t lo = __ldcg(reinterpret_cast<const uint32_t*>(vec + d));
+      const uint32_t hi = __ldcg(reinterpret_cast<const uint32_t*>(vec + d + 64));
+      float x[4] = {bf_lo(lo), bf_hi(lo), bf_lo(hi), bf_hi(hi)};
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      const float rstd = 1.0f / sqrtf(ss / (float)kHeadDim + a.eps);
+      const uint32_t wlo = *reinterpret_cast<const uint32_t*>(nw + d);
+      const uint32_t whi = *reinterpret_cast<const uint32_t*>(nw + d + 64);
+      const float w[4] = {bf_lo(wlo), bf_hi(wlo), bf_lo(whi), bf_hi(whi)};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = round_bf16(round_bf16(x[e] * rstd) * w[e]);
+      const float* cs = a.cos_sin + (size_t)pos * kHeadDim;
+      const float2 c = *reinterpret_cast<const float2*>(cs + d);
+      const float2 s = *reinterpret_cast<const float2*>(cs + 64 + d);
+      const float y0 = round_bf16(x[0] * c.x - x[2] * s.x), y1 = round_bf16(x[1] * c.y - x[3] * s.y);
+      const float y2 = round_bf16(x[2] * c.x + x[0] * s.x), y3 = round_bf16(x[3] * c.y + x[1] * s.y);
+      if (warp < 2) {
+        qs[warp][d] = y0; qs[warp][d + 1] = y1; qs[warp][d + 64] = y2; qs[warp][d + 65] = y3;
+      } else {
+        *reinterpret_cast<uint32_t*>(ks + d) = pack_bf16(y0, y1);
+        *reinterpret_cast<uint32_t*>(ks + d + 64) = pack_bf16(y2, y3);
+      }
+    } else {
+      const __nv_bfloat16* vec = src + a.q_size + a.kv_size + kvh * kHeadDim;
+      reinterpret_cast<uint2*>(vs)[lane] = __ldcg(reinterpret_cast<const uint2*>(vec) + lane);
+    }
+  }
+  __syncthreads();
+
+  if (owner) {
+    const int pi = pos - start;  // 0..63
+    if ((pi & 7) == pg) {
+      const int i = pi >> 3;
+      const uint4 kn = reinterpret_cast<const uint4*>(ks)[l16];
+      const uint4 vn = reinterpret_cast<const uint4*>(vs)[l16];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (u == i) { kreg[u] = kn; vreg[u] = vn; }
+      if (a.row_active == nullptr || a.row_active[row] != 0) {
+        const size_t off = base + (size_t)pi * tok_stride;
+        *reinterpret_cast<uint4*>(a.k_cache + off) = kn;
+        *reinterpret_cast<uint4*>(a.v_cache + off) = vn;
+      }
+    }
+  }
+
+  // ---- scores ----
+  float q0[8], q1[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { q0[e] = qs[0][8 * l16 + e]; q1[e] = qs[1][8 * l16 + e]; }
+  float s0[8], s1[8];
+  float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float kf[8];
+    unpack8(kreg[i], kf);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { d0 += kf[e] * q0[e]; d1 += kf[e] * q1[e]; }
+#pragma unroll
+    for (int m = 8; m >= 1; m >>= 1) {
+      d0 += __shfl_xor_sync(0xffffffffu, d0, m);
+      d1 += __shfl_xor_sync(0xffffffffu, d1, m);
+    }
+    const bool valid = start + pg + 8 * i < end;
+    s0[i] = valid ? d0 * a.scale : -INFINITY;
+    s1[i] = valid ? d1 * a.scale : -INFINITY;
+    m0 = fmaxf(m0, s0[i]);
+    m1 = fmaxf(m1, s1[i]);
+  }
+  if (l16 == 0) { mred[pg][0] = m0; mred[pg][1] = m1; }
+  __syncthreads();
+#pragma unroll
+  for (int p = 0; p < 8; ++p) { m0 = fmaxf(m0, mred[p][0]); m1 = fmaxf(m1, mred[p][1]); }
+
+  // ---- softmax numerators and P.V for this thread's positions ----
+  constexpr float kLog2e = 1.4426950408889634f;
+  float o0[8], o1[8], l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { o0[e] = 0.f; o1[e] = 0.f; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float p0 = exp2f((s0[i] - m0) * kLog2e);  // -inf -> 0
+    const float p1 = exp2f((s1[i] - m1) * kLog2e);
+    l0 += p0;
+    l1 += p1;
+    float vf[8];
+    unpack8(vreg[i], vf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { o0[e] += p0 * vf[e]; o1[e] += p1 * vf[e]; }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { ored[pg][0][8 * l16 + e] = o0[e]; ored[pg][1][8 * l16 + e] = o1[e]; }
+  if (l16 == 0) { lred[pg][0] = l0; lred[pg][1] = l1; }
+  __syncthreads();
+
+  const int d = tid;  // one head-dim element per thread from here on
+  float O0 = 0.f, O1 = 0.f, L0 = 0.f, L1 = 0.f;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) { O0 += ored[p][0][d]; O1 += ored[p][1][d]; L0 += lred[p][0]; L1 += lred[p][1]; }
+
+  __nv_bfloat16* out = a.out + (size_t)row * a.q_size + (size_t)(2 * kvh) * kHeadDim;
+  if (nsplits == 1) {
+    out[d] = __float2bfloat16_rn(O0 / L0);
+    out[kHeadDim + d] = __float2bfloat16_rn(O1 / L1);
+    return;
+  }
+
+  // ---- several splits: publish the partial, the last CTA to arrive merges ----
+  const size_t pidx = ((size_t)row * a.kv_heads + kvh) * kMaxSplits;
+  float* po = a.part_o + (pidx + split) * 2 * kHeadDim;
+  po[d] = O0;
+  po[kHeadDim + d] = O1;
+  if (tid == 0) { a.part_ml[(pidx + split) * 2] = make_float2(m0, L0); a.part_ml[(pidx + split) * 2 + 1] = make_float2(m1, L1); }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) last_flag = (atomicAdd(a.tickets + row * a.kv_heads + kvh, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  float M0 = -INFINITY, M1 = -INFINITY;
+  for (int s = 0; s < nsplits; ++s) {
+    M0 = fmaxf(M0, __ldcg(&a.part_ml[(pidx + s) * 2]).x);
+    M1 = fmaxf(M1, __ldcg(&a.part_ml[(pidx + s) * 2 + 1]).x);
+  }
+  float A0 = 0.f, A1 = 0.f, S0 = 0.f, S1 = 0.f;
+  for (int s = 0; s < nsplits; ++s) {
+    const float2 ml0 = __ldcg(&a.part_ml[(pidx + s) * 2]);
+    const float2 ml1 = __ldcg(&a.part_ml[(pidx + s) * 2 + 1]);
+    const float w0 = exp2f((ml0.x - M0) * kLog2e), w1 = exp2f((ml1.x - M1) * kLog2e);
+    const float* ps = a.part_o + (pidx + s) * 2 * kHeadDim;
+    A0 += w0 * __ldcg(ps + d);
+    A1 += w1 * __ldcg(ps + kHeadDim + d);
+    S0 += w0 * ml0.y;
+    S1 += w1 * ml1.y;
+  }
+  out[d] = __float2bfloat16_rn(A0 / S0);
+  out[kHeadDim + d] = __float2bfloat16_rn(A1 / S1);
+  if (tid == 0) a.tickets[row * a.kv_heads + kvh] = 0u;
+}
+
+// Copies one step's inputs into the decoder's fixed staging buffers (so a
+// captured graph can read them from constant addresses), converting the
+// engine's int64 ids / positions to int32.
+struct StageArgs {
+  const int64_t* ids;        // null: keep the previous step's tokens
+  const int64_t* positions;
+  const int* block_tables;
+  int bt_cols, bt_stride_in, bt_stride_out;
+  const int* row_active;     // null: all active
+  int rows;
+  int* ids_out;
+  int* positions_out;
+  int* bt_out;
+  int* row_active_out;
+};
+__global__ void stage_inputs_kernel(const StageArgs a) {
+  const int tid = threadIdx.x;
+  if (tid < a.rows) {
+    if (a.ids) a.ids_out[tid] = (int)a.ids[tid];
+    a.positions_out[tid] = (int)a.positions[tid];
+    a.row_active_out[tid] = a.row_active ? a.row_active[tid] : 1;
+  }
+  for (int i = tid; i < a.rows * a.bt_cols; i += blockDim.x) {
+    const int r = i / a.bt_cols, c = i % a.bt_cols;
+    a.bt_out[r * a.bt_stride_out + c] = a.block_tables[r * a.bt_stride_in + c];
+  }
+}
+
+}  // namespace dfb

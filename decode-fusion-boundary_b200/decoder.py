@@ -1,0 +1,259 @@
+"""The decoder object behind ``decode_backend="megakernel"``.
+
+Host-side replacement of the reference's ``TaskGraphDecoder``
+(backends/megakernel/taskgraph.py:92-131 admission policy, :150-305 set-up,
+:354-529 per-step protocol).  The reference builds a per-SM instruction stream
+for one cooperative kernel; this decoder owns a native ``DfbHandle`` that runs
+the step as a chain of ordinary sm_100a kernels inside a CUDA graph.  The
+method set (``step`` / ``step_batch`` / ``decode_rows`` / ``decode_row``), the
+argument meaning (pre-decode length as position, block tables right-padded
+with block 0) and the error behaviour are the reference's.
+
+``torch`` is imported lazily so the admission policy stays importable on a
+machine without CUDA.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any
+
+from .contracts import max_pages_per_seq, row_active_mask
+
+# Compile-time row ceiling of the kernels (DFB_MAX_ROWS); the reference's
+# TG_MAX_BATCH (taskgraph.py:33).
+TG_MAX_BATCH = 8
+# Tensor-parallel sizes the backend admits.  The reference admits only 1
+# (taskgraph.py:119-122).
+SUPPORTED_TP_SIZES = (1,)
+
+
+@dataclass(frozen=True)
+class TaskGraphCompatibility:
+    supported: bool
+    reason: str = ""
+
+
+def taskgraph_compatibility(config: Any, seqs: list[Any], is_prefill: bool) -> TaskGraphCompatibility:
+    """Torch-free admission policy; one explicit reason per rejection, in the
+    reference's order (taskgraph.py:92-131)."""
+    if is_prefill:
+        return TaskGraphCompatibility(False, "Task-graph megakernel is decode-only; use the prefill backend")
+    if not seqs:
+        return TaskGraphCompatibility(False, "Task-graph megakernel needs at least one sequence")
+    if len(seqs) > TG_MAX_BATCH:
+        return TaskGraphCompatibility(
+            False,
+            f"Task-graph megakernel supports batch sizes 1..{TG_MAX_BATCH} "
+            "(TG_MAX_BATCH, the compile-time scratch/bar ceiling)")
+    max_num_seqs = getattr(config, "max_num_seqs", None)
+    if isinstance(max_num_seqs, int) and max_num_seqs < len(seqs):
+        return TaskGraphCompatibility(False, f"batch {len(seqs)} exceeds max_num_seqs={max_num_seqs}")
+    if getattr(config, "tensor_parallel_size", 1) not in SUPPORTED_TP_SIZES:
+        return TaskGraphCompatibility(False, "Task-graph megakernel requires tensor_parallel_size=1")
+    for seq in seqs:
+        if bool(getattr(seq, "is_greedy", False)):
+            continue
+        temperature = getattr(seq, "temperature", None)
+        if temperature is None or temperature > 1e-10:
+            return TaskGraphCompatibility(False, "Task-graph megakernel supports greedy sampling only")
+    return TaskGraphCompatibility(True)
+
+
+class StreamDecoder:
+    """Owns the native decoder handle and runs one decode step per call."""
+
+    def __init__(self, weights, k_cache, v_cache, block_size: int, num_cache_blocks: int,
+                 max_model_len: int = 2048, attn_splits: int = 1, fusion_groups: int = 1,
+                 verbose: bool = False, debug_bounds: bool = False, use_graph: bool = True,
+                 use_pdl: bool = True):
+        import torch
+
+        from . import native
+
+        self._torch = torch
+        self._native = native
+        self._lib = native.lib()  # raises if the CUDA library has not been built
+        if not torch.cuda.is_available():
+            raise RuntimeError("Megakernel requires a CUDA device")
+        g = weights.geom
+        if max_model_len != g.max_model_len or block_size != g.block_size:
+            raise ValueError("weights geometry disagrees with max_model_len / block_size")
+        weights.validate()
+        for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+            want = (g.layers, num_cache_blocks, block_size, g.kv_heads, g.head_dim)
+            if tuple(cache.shape) != want or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
+                raise RuntimeError(f"{name} must be a contiguous bf16 tensor of shape {want}")
+        self._weights = weights  # keeps the tensors alive
+        self._k_cache, self._v_cache = k_cache, v_cache
+        self._max_rows = TG_MAX_BATCH
+        self._max_pages = max_pages_per_seq(max_model_len, block_size)
+        self._block_size = block_size
+        self._max_model_len = max_model_len
+        self._vocab = g.vocab
+        # ``attn_splits`` / ``fusion_groups`` configure the reference's schedule
+        # builder.  Here the split count follows the context length per step and
+        # the step is always one graph, so both are accepted and not used.
+        self._attn_splits, self._fusion_groups = int(attn_splits), int(fusion_groups)
+        self._verbose, self._debug_bounds = bool(verbose), bool(debug_bounds)
+
+        layer_arr = (native.DfbLayerWeights * g.layers)()
+        for i, layer in enumerate(weights.layers):
+            for name, _ in native.DfbLayerWeights._fields_:
+                setattr(layer_arr[i], name, getattr(layer, name).data_ptr())
+        desc = native.DfbModelDesc(
+            abi_version=native.DFB_ABI_VERSION, hidden=g.hidden, layers=g.layers, q_heads=g.q_heads,
+            kv_heads=g.kv_heads, head_dim=g.head_dim, intermediate=g.intermediate, vocab=g.vocab,
+            max_model_len=max_model_len, block_size=block_size, num_blocks=num_cache_blocks, eps=g.eps,
+            embed=weights.embed.data_ptr(), final_norm=weights.final_norm.data_ptr(),
+            rope_cos_sin=weights.cos_sin.data_ptr(), layer_weights=layer_arr,
+            k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr())
+        handle = C.c_void_p()
+        native.check(self._lib.dfb_create(C.byref(desc), C.byref(handle)), "dfb_create")
+        self._handle = handle
+        native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_GRAPH, int(use_graph)), "dfb_set_option")
+        native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_PDL, int(use_pdl)), "dfb_set_option")
+
+        # persistent per-step buffers: no allocation on the step path
+        self._result = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cuda")
+        self._result_host = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32).pin_memory()
+        self._row_active = torch.ones(self._max_rows, dtype=torch.int32, device="cuda")
+        self._h_ids = (C.c_int64 * self._max_rows)()
+        self._h_pos = (C.c_int64 * self._max_rows)()
+        self._h_bt = (C.c_int32 * (self._max_rows * self._max_pages))()
+        self._h_out = (C.c_int32 * self._max_rows)()
+        self._step = native.DfbStepDesc()
+
+    # -- lifecycle -----------------------------------------------------------
+    def close(self) -> None:
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.dfb_destroy(handle)
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_option(self, option: int, value: int) -> None:
+        self._native.check(self._lib.dfb_set_option(self._handle, option, value), "dfb_set_option")
+
+    def status(self):
+        st = self._native.DfbStatus()
+        code = self._lib.dfb_read_status(self._handle, C.byref(st))
+        return code, st
+
+    def _stream(self) -> int:
+        return self._torch.cuda.current_stream().cuda_stream
+
+    def _raise_device_status(self) -> None:
+        _, st = self.status()
+        raise RuntimeError(
+            f"megakernel decode step reported device status {st.device_status} "
+            f"(kernel {st.detail[0]}, index {st.detail[1]}, value {st.detail[2]})")
+
+    # -- decode --------------------------------------------------------------
+    def enqueue_rows(self, input_ids, positions, block_tables, active_rows=None, max_context: int = 0,
+                     out_logits=None) -> None:
+        """Enqueue one step on the current stream without reading the result
+        (device-resident loops; ``input_ids=None`` feeds the previous tokens
+        back).  ``tokens_device()`` holds the token ids once the stream is done."""
+        torch = self._torch
+        rows = int(positions.numel())
+        if rows > self._max_rows:
+            raise RuntimeError(
+                f"decode_rows got {rows} rows but this decoder is sized for {self._max_rows} (TG_MAX_BATCH); "
+                "the backend's compatibility check should have rejected this batch upstream")
+        cols = int(block_tables.size(1))
+        if cols > self._max_pages:
+            raise ValueError(
+                f"block table has {cols} columns but the task-graph page_table stride is {self._max_pages} "
+                "(max_model_len // block_size)")
+        if positions.dtype != torch.int64 or (input_ids is not None and input_ids.dtype != torch.int64):
+            raise TypeError("input_ids and positions must be int64 CUDA tensors")
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise TypeError("block_tables must be an int32 CUDA tensor with unit column stride")
+        s = self._step
+        s.rows, s.block_table_cols, s.block_table_stride = rows, cols, int(block_tables.stride(0))
+        s.max_context = int(max_context)
+        s.input_ids = input_ids.data_ptr() if input_ids is not None else None
+        s.positions = positions.data_ptr()
+        s.block_tables = block_tables.data_ptr()
+        if active_rows is not None:
+            mask = row_active_mask(active_rows, rows)
+            self._row_active[:rows].copy_(torch.tensor(mask, dtype=torch.int32))
+            s.row_active = self._row_active.data_ptr()
+        else:
+            s.row_active = None
+        s.out_tokens = self._result.data_ptr()
+        s.out_logits = out_logits.data_ptr() if out_logits is not None else None
+        self._native.check(self._lib.dfb_decode_step(self._handle, C.byref(s), self._stream()), "dfb_decode_step")
+
+    def tokens_device(self):
+        return self._result
+
+    def decode_rows(self, input_ids, positions, block_tables, active_rows=None) -> list[int]:
+        """One decode step for every row.  ``input_ids`` / ``positions`` are 1-D
+        int64 CUDA tensors, ``block_tables`` the padded ``[rows, <= max_pages]``
+        int32 CUDA tensor of ``ModelRunner.prepare_block_tables``; returns one
+        token id per row after exactly one device-to-host read."""
+        rows = int(input_ids.numel())
+        if rows == 0:
+            return []
+        self.enqueue_rows(input_ids, positions, block_tables, active_rows)
+        self._result_host.copy_(self._result, non_blocking=True)
+        self._torch.cuda.current_stream().synchronize()
+        out = self._result_host.tolist()
+        if out[self._native.DFB_MAX_ROWS]:
+            self._raise_device_status()
+        return out[:rows]
+
+    def decode_host(self, token_ids, positions, block_tables, active_rows=None) -> list[int]:
+        """One step from HOST data (lists of ints; one block-table list per
+        row): one packed host-to-device copy, the step, one device-to-host
+        copy, one synchronisation -- all inside the native call."""
+        rows = len(token_ids)
+        if rows == 0:
+            return []
+        if rows > self._max_rows:
+            raise RuntimeError(f"decode_host got {rows} rows; the decoder is sized for {self._max_rows}")
+        cols = max(len(t) for t in block_tables)
+        if cols > self._max_pages:
+            raise ValueError(
+                f"block table has {cols} columns but the task-graph page_table stride is {self._max_pages} "
+                "(max_model_len // block_size)")
+        for r in range(rows):
+            self._h_ids[r] = int(token_ids[r])
+            self._h_pos[r] = int(positions[r])
+            table = block_tables[r]
+            base = r * cols
+            for c in range(cols):
+                self._h_bt[base + c] = int(table[c]) if c < len(table) else 0
+        active = None
+        if active_rows is not None:
+            active = (C.c_int32 * rows)(*row_active_mask(active_rows, rows))
+        code = self._lib.dfb_decode_step_host(self._handle, rows, self._h_ids, self._h_pos, self._h_bt, cols,
+                                              active, self._h_out, self._stream())
+        if code == -4:
+            self._raise_device_status()
+        self._native.check(code, "dfb_decode_step_host")
+        return [int(self._h_out[r]) for r in range(rows)]
+
+    def decode_row(self, token_id: int, position: int, block_table) -> int:
+        """Single-row path of ``ModelRunner`` (batch 1): takes the scheduler's
+        host block table directly."""
+        if self._torch.is_tensor(block_table):
+            block_table = block_table.tolist()
+        table = list(block_table)[: self._max_pages]
+        return self.decode_host([int(token_id)], [int(position)], [table])[0]
+
+    # -- the one-step interface MegakernelBackend calls -----------------------
+    def step(self, token_id: int, position: int | None = None, block_table=None) -> int:
+        if position is None or block_table is None:
+            raise ValueError("task-graph decode requires position and block_table")
+        return self.decode_row(token_id, position, block_table)
+
+    def step_batch(self, input_token_ids, positions, block_tables) -> list[int]:
+        return self.decode_rows(input_token_ids, positions, block_tables)

@@ -1,0 +1,131 @@
+"""ctypes binding of ``libdfb_decode.so`` (the C ABI in ``include/dfb_decode.h``).
+
+The library is built in-tree by :func:`build` (``nvcc`` for sm_100a).  Loading
+fails loudly when it is missing: there is no Python or CPU fallback behind
+these calls.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "libdfb_decode.so"
+SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
+HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
+
+DFB_ABI_VERSION = 1
+DFB_MAX_ROWS = 8
+DFB_ATTN_CHUNK = 64
+DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS = 1, 2, 3
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+EXPORTS = (
+    "dfb_create", "dfb_destroy", "dfb_set_option", "dfb_decode_step", "dfb_decode_step_host",
+    "dfb_read_status", "dfb_error_string", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
+    "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
+)
+
+
+class DfbLayerWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("ln_in", "wqkv", "q_norm", "k_norm", "wo", "ln_post", "wgu", "wd")]
+
+
+class DfbModelDesc(C.Structure):
+    _fields_ = [
+        ("abi_version", C.c_int32), ("hidden", C.c_int32), ("layers", C.c_int32), ("q_heads", C.c_int32),
+        ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("intermediate", C.c_int32), ("vocab", C.c_int32),
+        ("max_model_len", C.c_int32), ("block_size", C.c_int32), ("num_blocks", C.c_int32), ("eps", C.c_float),
+        ("embed", C.c_void_p), ("final_norm", C.c_void_p), ("rope_cos_sin", C.c_void_p),
+        ("layer_weights", C.POINTER(DfbLayerWeights)), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+    ]
+
+
+class DfbStepDesc(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("block_table_cols", C.c_int32), ("block_table_stride", C.c_int32),
+        ("max_context", C.c_int32), ("input_ids", C.c_void_p), ("positions", C.c_void_p),
+        ("block_tables", C.c_void_p), ("row_active", C.c_void_p), ("out_tokens", C.c_void_p),
+        ("out_logits", C.c_void_p),
+    ]
+
+
+class DfbStatus(C.Structure):
+    _fields_ = [("device_status", C.c_int32), ("detail", C.c_int32 * 3), ("steps", C.c_int64),
+                ("kernels_per_step", C.c_int64)]
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    return any(p.stat().st_mtime > built for p in SOURCES + HEADERS if p.exists())
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the CUDA library for sm_100a next to this file."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: cannot build libdfb_decode.so")
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB_PATH), *map(str, SOURCES)]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{proc.stdout}\n{proc.stderr}")
+    if verbose:
+        print(proc.stderr)
+    return LIB_PATH
+
+
+_LIB = None
+
+
+def lib() -> C.CDLL:
+    """Load the library (once).  Raises if it has not been built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`; "
+            "the megakernel decode backend has no fallback implementation"
+        )
+    L = C.CDLL(str(LIB_PATH))
+    vp, i32, f32 = C.c_void_p, C.c_int32, C.c_float
+    L.dfb_create.argtypes = [C.POINTER(DfbModelDesc), C.POINTER(vp)]
+    L.dfb_destroy.argtypes = [vp]
+    L.dfb_destroy.restype = None
+    L.dfb_set_option.argtypes = [vp, C.c_int, C.c_int]
+    L.dfb_decode_step.argtypes = [vp, C.POINTER(DfbStepDesc), vp]
+    L.dfb_decode_step_host.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp]
+    L.dfb_read_status.argtypes = [vp, C.POINTER(DfbStatus)]
+    L.dfb_error_string.argtypes = [C.c_int]
+    L.dfb_error_string.restype = C.c_char_p
+    L.dfb_launch_rmsnorm_qkv.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
+    L.dfb_launch_attention.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, vp]
+    L.dfb_launch_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    L.dfb_launch_rmsnorm_gateup_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
+    L.dfb_launch_lmhead_argmax.argtypes = [vp, vp, vp, vp, vp, i32, vp]
+    for name in EXPORTS:
+        if name not in ("dfb_destroy", "dfb_error_string"):
+            getattr(L, name).restype = C.c_int
+    _LIB = L
+    return L
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().dfb_error_string(code).decode()
+        raise RuntimeError(f"{what} failed: {msg} (code {code})")

@@ -1,0 +1,170 @@
+/*
+ * dfb_decode.h -- C ABI of the B200 (sm_100a) Qwen3 greedy decode step.
+ *
+ * This is the native boundary behind nano-vLLM's decode_backend="megakernel"
+ * switch.  It replaces the reference project's native entry points
+ *
+ *   extern "C" cudaError_t tg_launch_decode(const tg::TgLaunchDesc*, cudaStream_t)
+ *       src/nanovllm/backends/megakernel/csrc/torch_bindings.cpp:27-31
+ *       src/nanovllm/backends/megakernel/csrc/taskgraph_kernel.cu:1927-1987
+ *   extern "C" void tg_launch_zero_regions(const TgZeroRegion*, int, int, cudaStream_t)
+ *       src/nanovllm/backends/megakernel/csrc/taskgraph_kernel.cu:2015-2023
+ *
+ * and the POD launch descriptor src/nanovllm/backends/megakernel/csrc/tg_abi.h:97-174.
+ * Like that header it compiles without CUDA headers: device addresses are plain
+ * pointers, the stream is an opaque pointer, there are no torch types, no
+ * exceptions, and every call returns an int status (0 = success, a positive
+ * value = the cudaError_t that failed, a negative value = a DFB_E_* code).
+ *
+ * The library has no CPU fallback: every entry point either runs the CUDA path
+ * or returns an error.
+ */
+#ifndef DFB_DECODE_H_
+#define DFB_DECODE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFB_ABI_VERSION 1
+#define DFB_MAX_ROWS 8          /* TG_MAX_BATCH, backends/megakernel/taskgraph.py:33 */
+#define DFB_ATTN_CHUNK 64       /* context positions handled by one attention CTA */
+
+/* negative status codes */
+#define DFB_E_BAD_ARG (-1)      /* null pointer, rows out of range, bad stride ... */
+#define DFB_E_GEOMETRY (-2)     /* model shape the kernels are not built for */
+#define DFB_E_ABI (-3)          /* abi_version mismatch */
+#define DFB_E_DEVICE_STATUS (-4)/* a kernel reported an error in the status word */
+#define DFB_E_TOO_LARGE (-5)    /* request exceeds a fixed capacity */
+
+typedef void* dfb_stream_t;     /* a cudaStream_t */
+typedef struct DfbHandle DfbHandle;
+
+/* Per-layer weight pointers (device, bf16, [out, in] row-major).  Replaces the
+ * 11-pointer-per-layer blob of backends/megakernel/weights.py:172-183, keeping
+ * nano-vLLM's fused qkv_proj / gate_up_proj tensors instead of splitting them. */
+typedef struct DfbLayerWeights {
+  const void* ln_in;    /* [hidden]                          input_layernorm.weight */
+  const void* wqkv;     /* [q_size + 2*kv_size, hidden]      self_attn.qkv_proj.weight (q|k|v rows) */
+  const void* q_norm;   /* [head_dim] */
+  const void* k_norm;   /* [head_dim] */
+  const void* wo;       /* [hidden, q_size]                  self_attn.o_proj.weight */
+  const void* ln_post;  /* [hidden]                          post_attention_layernorm.weight */
+  const void* wgu;      /* [2*intermediate, hidden]          mlp.gate_up_proj.weight (gate|up rows) */
+  const void* wd;       /* [hidden, intermediate]            mlp.down_proj.weight */
+} DfbLayerWeights;
+
+/* Model + paged KV cache description (cf. tg_abi.h:97-174 geometry fields and
+ * backends/megakernel/cache.py:16-119 for the cache layout). */
+typedef struct DfbModelDesc {
+  int32_t abi_version;      /* DFB_ABI_VERSION */
+  int32_t hidden;           /* 1024 */
+  int32_t layers;           /* 28 (any value >= 1 is accepted) */
+  int32_t q_heads;          /* 16 */
+  int32_t kv_heads;         /* 8 */
+  int32_t head_dim;         /* 128 */
+  int32_t intermediate;     /* 3072 */
+  int32_t vocab;            /* 151936 (any multiple of 8) */
+  int32_t max_model_len;    /* rows of rope_cos_sin; <= 2048 */
+  int32_t block_size;       /* tokens per KV block; multiple of DFB_ATTN_CHUNK */
+  int32_t num_blocks;       /* physical blocks in the cache */
+  float eps;                /* RMSNorm epsilon */
+  const void* embed;        /* bf16 [vocab, hidden]; also the tied LM head */
+  const void* final_norm;   /* bf16 [hidden] */
+  const float* rope_cos_sin;/* fp32 [max_model_len, head_dim]: cos | sin halves */
+  const DfbLayerWeights* layer_weights; /* HOST array of `layers` entries (copied) */
+  void* k_cache;            /* bf16 [layers, num_blocks, block_size, kv_heads, head_dim] */
+  void* v_cache;            /* same shape; engine-owned, shared with prefill */
+} DfbModelDesc;
+
+/* One decode step; all pointers are DEVICE pointers.  Mirrors the per-step
+ * inputs of TaskGraphDecoder.decode_rows (backends/megakernel/taskgraph.py:354-445). */
+typedef struct DfbStepDesc {
+  int32_t rows;               /* 1..DFB_MAX_ROWS */
+  int32_t block_table_cols;   /* valid columns of block_tables */
+  int32_t block_table_stride; /* elements between rows of block_tables */
+  int32_t max_context;        /* upper bound of positions[r]+1 if the host knows it, else 0
+                                 (then block_table_cols*block_size is used) */
+  const int64_t* input_ids;   /* [rows]; NULL = feed back the previous step's tokens */
+  const int64_t* positions;   /* [rows] pre-decode length of each row (= RoPE position) */
+  const int32_t* block_tables;/* [rows, stride] physical block ids, right-padded with 0 */
+  const int32_t* row_active;  /* [rows] or NULL (= all active); 0 skips the KV write only */
+  int32_t* out_tokens;        /* NULL, or int32[DFB_MAX_ROWS + 4]: greedy token ids in [0, rows) and the
+                                 decoder's status word (see DfbStatus) in [DFB_MAX_ROWS, DFB_MAX_ROWS + 4),
+                                 so one device-to-host read returns both */
+  float* out_logits;          /* [rows, vocab] or NULL; bf16-rounded logits as fp32 (parity checks) */
+} DfbStepDesc;
+
+typedef struct DfbStatus {
+  int32_t device_status;      /* 0 = ok; otherwise the first error code a kernel recorded */
+  int32_t detail[3];          /* kernel id, index, observed value */
+  int64_t steps;              /* decode steps enqueued so far */
+  int64_t kernels_per_step;   /* kernels of this library launched by one step */
+} DfbStatus;
+
+/* options for dfb_set_option */
+#define DFB_OPT_USE_GRAPH 1   /* 1 (default): replay a captured CUDA graph per (rows, split bucket) */
+#define DFB_OPT_USE_PDL 2     /* 1 (default): chain kernels with programmatic dependent launch */
+#define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
+
+/* Build a decoder for one model on the current device: validates the geometry,
+ * copies the pointer tables, allocates the activation scratch (a few MB).
+ * Replaces TaskGraphDecoder.__init__ (taskgraph.py:150-305). */
+int dfb_create(const DfbModelDesc* desc, DfbHandle** out);
+void dfb_destroy(DfbHandle* h);
+int dfb_set_option(DfbHandle* h, int option, int value);
+
+/* Enqueue one decode step on `stream` (no host synchronisation, no allocation
+ * after the first call for a given (rows, bucket)).  Replaces tg_launch_decode +
+ * tg_launch_zero_regions + the three staging copies of taskgraph.py:395-413. */
+int dfb_decode_step(DfbHandle* h, const DfbStepDesc* step, dfb_stream_t stream);
+
+/* Same step with HOST buffers: copies ids / positions / block tables to the
+ * device, runs the step, copies the token ids back and synchronises `stream`.
+ * This is the call behind MegakernelBackend.decode (backend.py:240-258): one
+ * H2D, one D2H, one sync per step.  block_tables is [rows, cols] row-major.
+ * Returns DFB_E_DEVICE_STATUS if a kernel recorded an error during the step. */
+int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
+                         const int32_t* block_tables, int32_t cols, const int32_t* row_active,
+                         int32_t* out_tokens, dfb_stream_t stream);
+
+/* Read (and clear) the device status word; synchronises nothing by itself, so
+ * call it after the stream has been synchronised. */
+int dfb_read_status(DfbHandle* h, DfbStatus* out);
+const char* dfb_error_string(int code);
+
+/* ---- standalone, non-cooperative launches of each kernel -------------------
+ * One plain launch per call, so each kernel can be profiled or checked alone.
+ * All pointers are device pointers; `rows` <= DFB_MAX_ROWS.  They compute what
+ * the same-named step of the reference torch path computes (file:line in
+ * src/nanovllm/). */
+
+/* models/qwen3.py:153-156 + :79.  x = h (+ residual); residual_out = bf16(x);
+ * qkv = RMSNorm(x; ln_w) @ wqkv^T.  If `ids` is non-NULL, h is gathered from the
+ * rows ids[r] of `h` (an embedding table) and `residual` must be NULL. */
+int dfb_launch_rmsnorm_qkv(const void* h, const int32_t* ids, const void* residual, void* residual_out,
+                           const void* ln_w, const void* wqkv, void* qkv_out, int32_t rows, int32_t hidden,
+                           int32_t qkv_rows, float eps, dfb_stream_t stream);
+/* models/qwen3.py:84-88 + layers/attention.py:33-40,72-74: q/k RMSNorm, RoPE,
+ * KV write at positions[r], paged GQA decode attention over [0, positions[r]]. */
+int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int32_t* positions,
+                         const int32_t* block_tables, int32_t block_table_stride, const int32_t* row_active,
+                         void* attn_out, int32_t rows, int32_t max_context, dfb_stream_t stream);
+/* layers/linear.py:152-153: out[rows, n] = x[rows, k] @ w[n, k]^T (o_proj, down_proj). */
+int dfb_launch_linear(const void* x, const void* w, void* out, int32_t rows, int32_t n, int32_t k,
+                      dfb_stream_t stream);
+/* models/qwen3.py:158 + :115-117: add+RMSNorm, gate/up projection, SiLU(gate)*up. */
+int dfb_launch_rmsnorm_gateup_swiglu(const void* h, const void* residual, void* residual_out, const void* ln_w,
+                                     const void* wgu, void* act_out, int32_t rows, int32_t hidden,
+                                     int32_t intermediate, float eps, dfb_stream_t stream);
+/* models/qwen3.py:186,216-220 + layers/sampler.py:9,15: final add+RMSNorm, tied
+ * LM head, bf16-rounded logits, greedy argmax (lowest index wins ties). */
+int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,
+                             float* out_logits, int32_t rows, dfb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFB_DECODE_H_ */

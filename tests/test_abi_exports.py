@@ -1,0 +1,54 @@
+"""The C-ABI library loads and exports every function include/dfb_decode.h
+declares; the ctypes structures have the header's layout.  No GPU work."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+from dfb_b200 import native
+
+HEADER = Path(__file__).resolve().parents[1] / "include" / "dfb_decode.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return set(re.findall(r"\b(dfb_[a-z_0-9]+)\s*\(", text))
+
+
+def test_library_exports_every_declared_symbol():
+    native.build()
+    lib = native.lib()
+    names = declared_functions()
+    assert names == set(native.EXPORTS)
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_constants_match_header():
+    text = HEADER.read_text()
+    for name in ("DFB_ABI_VERSION", "DFB_MAX_ROWS", "DFB_ATTN_CHUNK", "DFB_OPT_USE_GRAPH", "DFB_OPT_USE_PDL",
+                 "DFB_OPT_LMHEAD_CTAS"):
+        value = int(re.search(rf"#define {name}\s+(\d+)", text).group(1))
+        assert getattr(native, name) == value
+
+
+def test_struct_layouts():
+    assert C.sizeof(native.DfbLayerWeights) == 64
+    assert C.sizeof(native.DfbModelDesc) == 12 * 4 + 6 * 8
+    assert native.DfbModelDesc.embed.offset == 48
+    assert C.sizeof(native.DfbStepDesc) == 16 + 6 * 8
+    assert C.sizeof(native.DfbStatus) == 32
+
+
+def test_argument_errors_need_no_device():
+    lib = native.lib()
+    handle = C.c_void_p()
+    assert lib.dfb_create(None, C.byref(handle)) == -1
+    bad = native.DfbModelDesc(abi_version=99)
+    assert lib.dfb_create(C.byref(bad), C.byref(handle)) == -3
+    bad = native.DfbModelDesc(abi_version=native.DFB_ABI_VERSION, hidden=512)
+    assert lib.dfb_create(C.byref(bad), C.byref(handle)) == -2
+    assert handle.value is None
+    assert lib.dfb_decode_step(None, None, None) == -1
+    assert lib.dfb_error_string(-2) == b"dfb: unsupported model geometry"
+    assert lib.dfb_error_string(0) == b"success"

@@ -1,0 +1,151 @@
+"""The whole decode step through the C ABI against the oracle, on small models
+with the Qwen3-0.6B layer shape (the oracle finishes these in seconds)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import qwen3_decode as O
+from tests import harness as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(report):
+    assert report["device_status"] == 0, report
+    assert report["tokens_match_or_tie"], report
+    assert report["max_abs_logit_diff"] <= H.LOGIT_ATOL, report
+    assert report["mean_abs_logit_diff"] <= H.LOGIT_MEAN_ATOL, report
+    assert report["max_abs_kv_diff"] <= 2.0 ** -5, report
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_step_matches_oracle_for_every_batch_size(cuda_device, rows):
+    lens = [3, 70, 250, 129, 64, 1, 300, 17][:rows]
+    r = H.run_parity_case(layers=2, vocab=4096, prompt_lens=lens, steps=3, seed=rows)
+    _check(r)
+    assert r["kernels_per_step"] == 2 * 5 + 1
+
+
+@pytest.mark.parametrize("prompt", [254, 255, 256, 257])
+def test_block_boundary(cuda_device, prompt):
+    """Decode across the 256-token block boundary (the reference's
+    tests/test_kv_block_boundary.py cases, on the device)."""
+    _check(H.run_parity_case(layers=2, vocab=2048, prompt_lens=[prompt], steps=4, seed=11))
+
+
+def test_scattered_block_tables(cuda_device):
+    perm = np.random.Generator(np.random.Philox(key=4)).permutation(16).tolist()
+    _check(H.run_parity_case(layers=2, vocab=2048, prompt_lens=[600, 40, 257], steps=3, seed=12,
+                             block_permutation=perm))
+
+
+def test_max_context(cuda_device):
+    """The last admissible position: context 2048 after the step."""
+    _check(H.run_parity_case(layers=1, vocab=1024, prompt_lens=[2044, 1], steps=3, seed=13))
+
+
+@pytest.mark.parametrize("use_graph,use_pdl", [(False, False), (False, True), (True, False)])
+def test_launch_modes_agree(cuda_device, use_graph, use_pdl):
+    """Plain launches, PDL launches and graph replay must give the same result."""
+    _check(H.run_parity_case(layers=3, vocab=2048, prompt_lens=[5, 130], steps=3, seed=14,
+                             use_graph=use_graph, use_pdl=use_pdl))
+
+
+def test_host_buffer_step(cuda_device):
+    """dfb_decode_step_host: H2D + step + D2H inside the call."""
+    r = H.run_parity_case(layers=2, vocab=2048, prompt_lens=[9, 300, 64], steps=4, seed=15, host_path=True)
+    assert r["device_status"] == 0 and r["tokens_match_or_tie"], r
+    assert r["max_abs_kv_diff"] <= 2.0 ** -5, r
+
+
+def _setup(rows_lens, seed, layers=2, vocab=2048, steps=4):
+    g = H.oracle_geometry(layers=layers, vocab=vocab)
+    w = O.make_weights(g, seed=seed, norm="random").to(torch.bfloat16)
+    cos_sin = O.rope_cos_sin_table(g)
+    rng = np.random.Generator(np.random.Philox(key=seed))
+    prompts = [rng.integers(0, g.vocab, n).tolist() for n in rows_lens]
+    tables, nblocks = O.allocate_blocks([n + steps for n in rows_lens], g.block_size)
+    kv = O.new_kv_cache(g, nblocks, torch.bfloat16)
+    first = [int(O.greedy(O.prefill(w, kv, cos_sin, p, t))) for p, t in zip(prompts, tables)]
+    return g, w, kv, tables, first
+
+
+def test_batch_equals_independent_rows(cuda_device):
+    """B rows in one launch == B single-row launches, bit for bit (the
+    reference's tests/test_taskgraph_bs2.py:235-248)."""
+    lens = [40, 300, 7]
+    g, w, kv, tables, first = _setup(lens, seed=16)
+    kv_a, kv_b = kv.cuda(), kv.cuda()
+    dec_a, dec_b = H.make_decoder(w, kv_a), H.make_decoder(w, kv_b)
+    la = torch.zeros(3, g.vocab, device="cuda")
+    lb = torch.zeros(1, g.vocab, device="cuda")
+    cur = list(first)
+    cl = [n + 1 for n in lens]
+    for _ in range(3):
+        pos = [n - 1 for n in cl]
+        dec_a.enqueue_rows(torch.tensor(cur, device="cuda"), torch.tensor(pos, device="cuda"),
+                           H.padded_tables(tables, cl, g.block_size), out_logits=la)
+        torch.cuda.synchronize()
+        tok_a = dec_a.tokens_device()[:3].tolist()
+        for r in range(3):
+            dec_b.enqueue_rows(torch.tensor([cur[r]], device="cuda"), torch.tensor([pos[r]], device="cuda"),
+                               H.padded_tables([tables[r]], [cl[r]], g.block_size), out_logits=lb)
+            torch.cuda.synchronize()
+            assert torch.equal(la[r], lb[0])
+            assert dec_b.tokens_device()[0].item() == tok_a[r]
+        cur, cl = tok_a, [n + 1 for n in cl]
+    assert torch.equal(kv_a, kv_b)
+    dec_a.close(); dec_b.close()
+
+
+def test_deterministic_and_feedback(cuda_device):
+    """Same inputs twice -> identical tokens; device-side token feedback
+    (input_ids=None) follows the same trajectory as passing the ids."""
+    lens = [33, 100]
+    g, w, kv, tables, first = _setup(lens, seed=17, steps=8)
+    runs = []
+    for feedback in (False, False, True):
+        kvg = kv.cuda()
+        dec = H.make_decoder(w, kvg)
+        cur, cl, out = list(first), [n + 1 for n in lens], []
+        for s in range(8):
+            ids = torch.tensor(cur, device="cuda") if (s == 0 or not feedback) else None
+            toks = None
+            dec.enqueue_rows(ids, torch.tensor([n - 1 for n in cl], device="cuda"),
+                             H.padded_tables(tables, cl, g.block_size))
+            torch.cuda.synchronize()
+            cur = dec.tokens_device()[:2].tolist()
+            out.append(cur)
+            cl = [n + 1 for n in cl]
+        runs.append((out, kvg.cpu()))
+        dec.close()
+    assert runs[0][0] == runs[1][0] == runs[2][0]
+    assert torch.equal(runs[0][1], runs[1][1]) and torch.equal(runs[0][1], runs[2][1])
+
+
+def test_bad_block_id_is_reported_not_followed(cuda_device):
+    """An out-of-range block id sets the status word; the kernel substitutes
+    block 0 instead of forming an address from it."""
+    g, w, kv, tables, first = _setup([10], seed=18)
+    dec = H.make_decoder(w, kv.cuda())
+    with pytest.raises(RuntimeError, match="device status 2"):
+        dec.decode_host([first[0]], [10], [[999999]])
+    # the decoder stays usable and the word was cleared
+    assert dec.decode_host([first[0]], [10], [tables[0]])
+    code, st = dec.status()
+    assert code == 0
+    dec.close()
+
+
+def test_capacity_errors(cuda_device):
+    g, w, kv, tables, first = _setup([10], seed=19)
+    dec = H.make_decoder(w, kv.cuda())
+    with pytest.raises(RuntimeError, match="sized for 8"):
+        dec.decode_host([1] * 9, [1] * 9, [[0]] * 9)
+    with pytest.raises(ValueError, match="page_table stride is 8"):
+        dec.decode_host([1], [1], [[0] * 9])
+    with pytest.raises(RuntimeError, match="bad argument"):
+        dec.decode_host([1], [5000], [[0]])          # position beyond max_model_len
+    assert dec.decode_rows(torch.zeros(0, dtype=torch.int64, device="cuda"), None, None) == []
+    dec.close()
