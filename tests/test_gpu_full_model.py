@@ -1,0 +1,147 @@
+"""Full Qwen3-0.6B geometry on the GPU: against the golden fixture produced by
+the reference's torch model (bf16, teacher forced), against the oracle over 64
+greedy steps (BASELINE config 1 in bf16), and size-independent properties at the
+benchmark's sizes."""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import qwen3_decode as O
+from tests import harness as H
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+sys.path.insert(0, str(GOLDEN))
+import make_golden as G  # noqa: E402  (case definitions only)
+
+
+@pytest.fixture(scope="module")
+def full(cuda_device):
+    w = O.make_weights(O.QWEN3_06B, seed=0, norm="ones").to(torch.bfloat16)
+    return w, H.to_decoder_weights(w)
+
+
+def _decoder(dw, kv_gpu, g):
+    from dfb_b200.decoder import StreamDecoder
+    return StreamDecoder(dw, kv_gpu[0], kv_gpu[1], block_size=g.block_size, num_cache_blocks=kv_gpu.shape[2],
+                         max_model_len=g.max_pos)
+
+
+def test_golden_bf16_teacher_forced(full):
+    """The CUDA step against logits the REFERENCE model produced (fixture)."""
+    w, dw = full
+    g = w.geom
+    z = np.load(GOLDEN / "qwen3_06b_bf16_forced8.npz")
+    prompts, forced = G.forced_case(g)
+    cos_sin = O.rope_cos_sin_table(g)
+    lengths = [len(p) + G.FORCED_STEPS for p in prompts]
+    tables, nblocks = O.allocate_blocks(lengths, g.block_size)
+    kv = O.new_kv_cache(g, nblocks, torch.bfloat16)
+    for p, t in zip(prompts, tables):
+        O.prefill(w, kv, cos_sin, p, t, fused_rounding=False)      # prefill stays off the CUDA path
+    kv_gpu = kv.cuda()
+    dec = _decoder(dw, kv_gpu, g)
+    logits = torch.zeros(2, g.vocab, device="cuda")
+    lens = [len(p) + 1 for p in prompts]
+    probe = torch.from_numpy(z["probe_index"]).long()
+    worst = 0.0
+    for s in range(G.FORCED_STEPS):
+        dec.enqueue_rows(torch.tensor(forced[s], device="cuda"), torch.tensor([n - 1 for n in lens], device="cuda"),
+                         H.padded_tables(tables, lens, g.block_size), out_logits=logits)
+        torch.cuda.synchronize()
+        got = logits.cpu()
+        worst = max(worst, float((got[:, probe] - torch.from_numpy(z["probe_logits"][s])).abs().max()))
+        toks = dec.tokens_device()[:2].tolist()
+        for r in range(2):
+            ref_tok = int(z["tokens"][s + 1, r])
+            top_i, top_v = z["top_index"][s, r], z["top_logits"][s, r]
+            if toks[r] != ref_tok:   # only a tie within rounding may differ
+                assert toks[r] in top_i.tolist(), (s, r, toks[r], top_i)
+                gap = float(top_v[0] - top_v[top_i.tolist().index(toks[r])])
+                assert gap <= H.TOKEN_GAP_ATOL, (s, r, gap)
+        lens = [n + 1 for n in lens]
+    assert worst <= H.LOGIT_ATOL, worst
+    dec.close()
+
+
+def test_config1_bf16_greedy64_vs_oracle(full):
+    """Prompt of 32 ids, 64 greedy decode steps, batch 1, block 256: tokens equal
+    to the oracle's (up to ties within rounding, which are then teacher-forced
+    to the oracle's choice) and logits within tolerance at every step."""
+    w, dw = full
+    g = w.geom
+    prompt = G.config1_prompt(g)
+    cos_sin = O.rope_cos_sin_table(g)
+    tables, nblocks = O.allocate_blocks([len(prompt) + 65], g.block_size)
+    kv = O.new_kv_cache(g, nblocks, torch.bfloat16)
+    cur = [int(O.greedy(O.prefill(w, kv, cos_sin, prompt, tables[0])))]
+    kv_gpu = kv.cuda()
+    dec = _decoder(dw, kv_gpu, g)
+    logits = torch.zeros(1, g.vocab, device="cuda")
+    n = len(prompt) + 1
+    worst, mean_worst, identical = 0.0, 0.0, 0
+    for s in range(64):
+        want_logits, want_tok = O.decode_step(w, kv, cos_sin, cur, [n - 1], tables)
+        dec.enqueue_rows(torch.tensor(cur, device="cuda"), torch.tensor([n - 1], device="cuda"),
+                         H.padded_tables(tables, [n], g.block_size), out_logits=logits)
+        torch.cuda.synchronize()
+        d = (logits.cpu() - want_logits.float()).abs()
+        worst, mean_worst = max(worst, float(d.max())), max(mean_worst, float(d.mean()))
+        got = int(dec.tokens_device()[0])
+        identical += got == int(want_tok[0])
+        assert H.token_gap_ok(want_logits[0].float(), got, int(want_tok[0])), (s, got, int(want_tok[0]))
+        cur, n = [int(want_tok[0])], n + 1
+    print(f"config1 bf16: max|dlogit|={worst:.4f} mean={mean_worst:.5f} identical tokens {identical}/64")
+    assert worst <= H.LOGIT_ATOL and mean_worst <= H.LOGIT_MEAN_ATOL
+    assert float((kv_gpu.cpu().float() - kv.float()).abs().max()) <= 2.0 ** -4
+    dec.close()
+
+
+def test_full_size_properties_batch8_long_context(full):
+    """BASELINE config 4 sizes (batch 8, contexts in [256, 2048], scattered
+    blocks): properties that need no oracle run -- determinism, batch ==
+    independent rows, and each row's logits depend only on its own KV blocks."""
+    w, dw = full
+    g = w.geom
+    rng = np.random.Generator(np.random.Philox(key=77))
+    ctx = rng.integers(256, 2048, 8).tolist()
+    perm = rng.permutation(64).tolist()
+    tables, _ = O.allocate_blocks([2048] * 8, g.block_size, perm)
+    kv = torch.empty(2, g.layers, 64, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv.normal_(0, 1, generator=torch.Generator(device="cuda").manual_seed(5))
+    kv0 = kv.clone()
+    ids = torch.from_numpy(rng.integers(0, g.vocab, 8)).cuda()
+    pos = torch.tensor([c - 1 for c in ctx], device="cuda")
+    bt = H.padded_tables(tables, ctx, g.block_size)
+    dec = _decoder(dw, kv, g)
+    la, lb = torch.zeros(8, g.vocab, device="cuda"), torch.zeros(8, g.vocab, device="cuda")
+    dec.enqueue_rows(ids, pos, bt, out_logits=la)
+    torch.cuda.synchronize()
+    tok_a = dec.tokens_device()[:8].tolist()
+    kv_after = kv.clone()
+    kv.copy_(kv0)
+    dec.enqueue_rows(ids, pos, bt)              # graph path, no logits
+    torch.cuda.synchronize()
+    assert dec.tokens_device()[:8].tolist() == tok_a
+    assert torch.equal(kv, kv_after)
+    # only the 8 new (row, position) slots changed
+    changed = (kv_after != kv0).any(dim=-1).any(dim=-1).any(dim=0).any(dim=0)   # [blocks, block_size]
+    want = torch.zeros_like(changed)
+    for r in range(8):
+        p = ctx[r] - 1
+        want[tables[r][p // g.block_size], p % g.block_size] = True
+    assert torch.equal(changed, want)
+    # rows one at a time
+    for r in (0, 3, 7):
+        kv.copy_(kv0)
+        dec.enqueue_rows(ids[r:r + 1], pos[r:r + 1], bt[r:r + 1].contiguous(), out_logits=lb)
+        torch.cuda.synchronize()
+        assert torch.equal(lb[0], la[r])
+    code, st = dec.status()
+    assert code == 0
+    dec.close()
