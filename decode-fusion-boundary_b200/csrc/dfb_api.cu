@@ -26,15 +26,18 @@ typedef __nv_bfloat16 bf16;
 struct Launcher {
   cudaStream_t stream;
   bool pdl;
+  unsigned long long* trace = nullptr;  // base of the timeline buffer or null
   int count = 0;
   int err = 0;
+  unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   template <typename Args>
-  void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true) {
+  void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true,
+              size_t smem = 0) {
     if (err) return;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -60,6 +63,8 @@ struct DfbHandle {
   bool use_graph = true;
   bool use_pdl = true;
   int lmhead_ctas = 0;
+  bool trace_on = false;
+  unsigned long long* trace = nullptr;  // [kMaxTraceKernels, 4] globaltimer ns
   // device scratch (one slab)
   void* slab = nullptr;
   int* stage = nullptr;          // ids[8] | positions[8] | row_active[8] | block_tables[8, max_pages]
@@ -94,44 +99,76 @@ struct DfbHandle {
 
 namespace {
 
+constexpr int kMaxTraceKernels = 1024;
+
 int loads_for_k(int k) { return (k % 256 == 0) ? k / 256 : 0; }
 
+// One CTA per SM at most, and at most half of an SM's registers per CTA, so
+// that the CTAs of two consecutive kernels are resident together: the
+// successor prefetches its weights while the predecessor computes.
+int sm_count_cached() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
+
 // ---- kernel launch wrappers -------------------------------------------------
+// Launch one instantiation of the GEMV kernel; its dynamic shared memory (the
+// weight stages) exceeds 48 KB, which needs a one-time opt-in per function.
+template <int LOADS, int WARPS, int STAGES, int MODE>
+void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
+  static bool configured = false;
+  constexpr int smem = GemvSmem<LOADS, WARPS>::bytes(STAGES);
+  auto kernel = stream_gemv_kernel<LOADS, WARPS, STAGES, MODE>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { L.err = (int)e; return; }
+    configured = true;
+  }
+  a.trace = L.next_trace();
+  L.launch(kernel, dim3(grid), dim3(WARPS * 32), a, allow_pdl, smem);
+}
+
 int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_in, bf16* res_out, const bf16* ln_w,
-                    const bf16* w, bf16* out, int rows, int hidden, int n, float eps, bool allow_pdl) {
+                    const bf16* w, bf16* out, int rows, int hidden, int n, float eps, int* status, bool allow_pdl) {
   if (hidden != 1024 || n % kTileRows) return DFB_E_GEOMETRY;
   GemvArgs a = {};
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = hidden;
   a.x = x; a.ids = ids; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
-  a.out = out; a.out_stride = n;
-  const int grid = a.n_tiles < 256 ? a.n_tiles : 256;
-  L.launch(stream_gemv_kernel<4, 2, kModeNormStore>, dim3(grid), dim3(kThreads), a, allow_pdl);
+  a.out = out; a.out_stride = n; a.status = status;
+  launch_gemv<4, 8, 4, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
   return L.err;
 }
 
-int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows, int n, int k) {
+int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows, int n, int k, int* status) {
   if (n % kTileRows) return DFB_E_GEOMETRY;
   GemvArgs a = {};
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = k; a.x = x; a.out = out; a.out_stride = n;
-  const int grid = a.n_tiles < 296 ? a.n_tiles : 296;
+  a.status = status;
+  const int grid = grid_for(a.n_tiles);
   switch (loads_for_k(k)) {
-    case 4: L.launch(stream_gemv_kernel<4, 2, kModeStore>, dim3(grid), dim3(kThreads), a); break;
-    case 8: L.launch(stream_gemv_kernel<8, 1, kModeStore>, dim3(grid), dim3(kThreads), a); break;
-    case 12: L.launch(stream_gemv_kernel<12, 1, kModeStore>, dim3(grid), dim3(kThreads), a); break;
+    case 4: launch_gemv<4, 8, 4, kModeStore>(L, a, grid); break;
+    case 8: launch_gemv<8, 8, 2, kModeStore>(L, a, grid); break;
+    case 12: launch_gemv<12, 8, 2, kModeStore>(L, a, grid); break;
     default: return DFB_E_GEOMETRY;
   }
   return L.err;
 }
 
 int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out, const bf16* ln_w, const bf16* wgu,
-                  bf16* act, int rows, int hidden, int inter, float eps) {
+                  bf16* act, int rows, int hidden, int inter, float eps, int* status) {
   if (hidden != 1024 || inter % 4) return DFB_E_GEOMETRY;
   GemvArgs a = {};
   a.w = wgu; a.n_tiles = inter / 4; a.rows = rows; a.k = hidden;
   a.x = h; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
-  a.out = act; a.out_stride = inter; a.gate_rows = inter;
-  const int grid = a.n_tiles < 256 ? a.n_tiles : 256;
-  L.launch(stream_gemv_kernel<4, 3, kModeNormSwiglu>, dim3(grid), dim3(kThreads), a);
+  a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
+  launch_gemv<4, 8, 6, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
   return L.err;
 }
 
@@ -141,11 +178,11 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   GemvArgs a = {};
   a.w = (const bf16*)m.embed; a.n_tiles = m.vocab / kTileRows; a.rows = rows; a.k = m.hidden;
   a.x = hid; a.res_in = res_in; a.norm_w = (const bf16*)m.final_norm; a.eps = m.eps;
-  a.logits_out = logits_out; a.vocab = m.vocab;
+  a.logits_out = logits_out; a.vocab = m.vocab; a.status = h->status;
   a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens; a.tokens_out = tokens_out;
-  int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 2 * h->sm_count;
+  int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
   if (grid > a.n_tiles) grid = a.n_tiles;
-  L.launch(stream_gemv_kernel<4, 3, kModeNormArgmax>, dim3(grid), dim3(kThreads), a);
+  launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid);
   return L.err;
 }
 
@@ -161,6 +198,7 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   a.v_cache = (bf16*)m.v_cache + (size_t)layer * h->kv_layer_elems;
   a.block_size = m.block_size; a.kv_heads = m.kv_heads; a.num_blocks = m.num_blocks; a.max_pos = m.max_model_len;
   a.out = out; a.part_o = h->part_o; a.part_ml = h->part_ml; a.tickets = h->tickets; a.status = h->status;
+  a.trace = L.next_trace();
   L.launch(paged_attention_kernel, dim3(nsplit, m.kv_heads, rows), dim3(kAttnThreads), a);
   return L.err;
 }
@@ -177,7 +215,7 @@ int split_bucket(const DfbHandle* h, int max_context) {
 // The whole step as one chain of 5 kernels per layer + the LM head.
 int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
   const DfbModelDesc& m = h->m;
-  Launcher L{stream, h->use_pdl};
+  Launcher L{stream, h->use_pdl, h->trace_on ? h->trace : nullptr};
   int rc = 0;
   int cur = 0;  // index of the residual buffer holding the current residual
   for (int l = 0; l < m.layers && !rc; ++l) {
@@ -186,22 +224,22 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
       // embedding rows are gathered by token id; the residual starts as the embedding itself.
       // No PDL on the first kernel: it must observe the staged inputs of this step.
       rc = launch_norm_qkv(L, (const bf16*)m.embed, h->st_ids(), nullptr, h->res[cur], (const bf16*)w.ln_in,
-                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, false);
+                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, h->status, false);
     } else {
       rc = launch_norm_qkv(L, h->hbuf, nullptr, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_in,
-                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, true);
+                           (const bf16*)w.wqkv, h->qkv, rows, m.hidden, h->qkv_rows(), m.eps, h->status, true);
       cur ^= 1;
     }
     if (rc) break;
     rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, h->st_active(), h->attn, rows, nsplit);
     if (rc) break;
-    rc = launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size());
+    rc = launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status);
     if (rc) break;
     rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
-                       rows, m.hidden, m.intermediate, m.eps);
+                       rows, m.hidden, m.intermediate, m.eps, h->status);
     cur ^= 1;
     if (rc) break;
-    rc = launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate);
+    rc = launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status);
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
   h->kernels_per_step = L.count;
@@ -287,6 +325,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_pml = carve(sizeof(float2) * kMaxRows * d->kv_heads * kMaxSplits * 2);
   const size_t o_tk = carve(sizeof(unsigned) * (kMaxRows * d->kv_heads + 1));
   const size_t o_parts = carve(sizeof(ArgmaxPart) * kMaxRows * 4096);
+  const size_t o_trace = carve(sizeof(unsigned long long) * 8 * kMaxTraceKernels);
   const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
@@ -299,7 +338,8 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   h->res[0] = (bf16*)(s + o_r0); h->res[1] = (bf16*)(s + o_r1);
   h->qkv = (bf16*)(s + o_qkv); h->attn = (bf16*)(s + o_attn); h->act = (bf16*)(s + o_act);
   h->part_o = (float*)(s + o_po); h->part_ml = (float2*)(s + o_pml); h->tickets = (unsigned*)(s + o_tk);
-  h->parts = (ArgmaxPart*)(s + o_parts); h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
+  h->parts = (ArgmaxPart*)(s + o_parts); h->trace = (unsigned long long*)(s + o_trace);
+  h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
   *out = h;
   return 0;
 }
@@ -319,6 +359,11 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
   switch (option) {
     case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
     case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
+    case DFB_OPT_TRACE:
+      h->trace_on = value != 0;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
     case DFB_OPT_LMHEAD_CTAS:
       if (value < 0 || value > 4096) return DFB_E_BAD_ARG;
       h->lmhead_ctas = value;
@@ -411,6 +456,18 @@ int dfb_read_status(DfbHandle* h, DfbStatus* out) {
   return st[0] ? DFB_E_DEVICE_STATUS : 0;
 }
 
+int dfb_read_trace(DfbHandle* h, uint64_t* out, int32_t max_kernels) {
+  if (!h || !out || max_kernels < 1) return DFB_E_BAD_ARG;
+  int n = h->kernels_per_step < max_kernels ? h->kernels_per_step : max_kernels;
+  if (n > kMaxTraceKernels) n = kMaxTraceKernels;
+  DFB_CUDA(cudaMemcpy(out, h->trace, sizeof(uint64_t) * 8 * n, cudaMemcpyDeviceToHost));
+  // re-arm: minima (words 0 and 3) start at the largest value, maxima at zero
+  std::vector<unsigned long long> init(8 * kMaxTraceKernels, 0ull);
+  for (int i = 0; i < kMaxTraceKernels; ++i) { init[8 * i] = ~0ull; init[8 * i + 3] = ~0ull; }
+  DFB_CUDA(cudaMemcpy(h->trace, init.data(), sizeof(unsigned long long) * init.size(), cudaMemcpyHostToDevice));
+  return n;
+}
+
 // ---- standalone launchers ----------------------------------------------------
 int dfb_launch_rmsnorm_qkv(const void* hh, const int32_t* ids, const void* residual, void* residual_out,
                            const void* ln_w, const void* wqkv, void* qkv_out, int32_t rows, int32_t hidden,
@@ -419,7 +476,7 @@ int dfb_launch_rmsnorm_qkv(const void* hh, const int32_t* ids, const void* resid
   if (ids && residual) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
   return launch_norm_qkv(L, (const bf16*)hh, ids, (const bf16*)residual, (bf16*)residual_out, (const bf16*)ln_w,
-                         (const bf16*)wqkv, (bf16*)qkv_out, rows, hidden, qkv_rows, eps, false);
+                         (const bf16*)wqkv, (bf16*)qkv_out, rows, hidden, qkv_rows, eps, nullptr, false);
 }
 
 int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int32_t* positions,
@@ -436,7 +493,7 @@ int dfb_launch_linear(const void* x, const void* w, void* out, int32_t rows, int
                       dfb_stream_t stream) {
   if (!x || !w || !out || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
-  return launch_linear(L, (const bf16*)x, (const bf16*)w, (bf16*)out, rows, n, k);
+  return launch_linear(L, (const bf16*)x, (const bf16*)w, (bf16*)out, rows, n, k, nullptr);
 }
 
 int dfb_launch_rmsnorm_gateup_swiglu(const void* hh, const void* residual, void* residual_out, const void* ln_w,
@@ -445,7 +502,7 @@ int dfb_launch_rmsnorm_gateup_swiglu(const void* hh, const void* residual, void*
   if (!hh || !residual || !ln_w || !wgu || !act_out || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
   return launch_gateup(L, (const bf16*)hh, (const bf16*)residual, (bf16*)residual_out, (const bf16*)ln_w,
-                       (const bf16*)wgu, (bf16*)act_out, rows, hidden, intermediate, eps);
+                       (const bf16*)wgu, (bf16*)act_out, rows, hidden, intermediate, eps, nullptr);
 }
 
 int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,

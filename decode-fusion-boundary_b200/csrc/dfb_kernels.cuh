@@ -23,8 +23,6 @@
 
 namespace dfb {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
 constexpr int kMaxRows = 8;
 constexpr int kTileRows = 8;          // weight rows per tile = N of mma.m16n8k16
 constexpr int kAttnThreads = 128;
@@ -66,6 +64,8 @@ struct GemvArgs {
   unsigned int* ticket;          // argmax: arrival counter (self-resetting)
   int* tokens;                   // argmax: [rows] result (feedback buffer)
   int* tokens_out;               // argmax: optional second copy
+  unsigned long long* trace;     // optional timeline slot of this launch (8 words) or null
+  int* status;                   // [4] device status word or null
 };
 
 // ---------------------------------------------------------------------------
@@ -107,6 +107,20 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
+// Optional timeline: per kernel {earliest CTA start, latest return from the
+// dependency wait, latest CTA end, earliest wait return} in globaltimer ns.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_min(unsigned long long* slot, int i) {
+  if (slot) atomicMin(slot + i, global_ns());
+}
+__device__ __forceinline__ void trace_max(unsigned long long* slot, int i) {
+  if (slot) atomicMax(slot + i, global_ns());
+}
+
 // Device-side error reporting: the first error of a step wins; the kernel goes
 // on with a safe substitute value and the host reads the word after the step.
 constexpr int kStatusBadPosition = 1;
@@ -121,23 +135,77 @@ __device__ __forceinline__ void report_status(int* status, int code, int kernel,
 }
 
 // ---------------------------------------------------------------------------
-// Weight-streaming skinny GEMM.
-//
-// One tile = 8 weight rows x K.  The 8 warps of a CTA split K: warp w owns
-// columns [w*K/8, (w+1)*K/8) = LOADS blocks of 32 columns.  In block j, lane
-// (g = lane/4, t = lane%4) loads the 16 bytes W[row g][32j + 8t .. +7] and the
-// matching 16 bytes of x[batch g]; word pairs (0,1) and (2,3) feed two
-// m16n8k16 MMAs with the batch on M and the weight rows on N.  The k order
-// inside an MMA is a fixed permutation applied to both operands, which a dot
-// product does not care about.  x fragments are loaded once per CTA and stay in
-// registers; weights are double/triple buffered in registers (DEPTH tiles in
-// flight), and the first DEPTH tiles are requested BEFORE the dependency wait.
+// mbarrier + bulk-copy (TMA, untiled) helpers
 // ---------------------------------------------------------------------------
-template <int LOADS, int DEPTH, int MODE>
-__global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a) {
-  constexpr bool kNorm = MODE != kModeStore;
-  pdl_launch_dependents();
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// global -> shared bulk copy; 16-byte aligned addresses, size a multiple of 16
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kMbarSpinLimit polls (each poll may itself block
+// for a short hardware-defined time) and lets the caller report the failure.
+constexpr int kMbarSpinLimit = 400000;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < kMbarSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+constexpr int kStatusCopyTimeout = 3;
+constexpr int kKernelGemv = 1;
 
+// ---------------------------------------------------------------------------
+// Weight-streaming skinny GEMM, weights staged through shared memory by TMA.
+//
+// One tile = 8 weight rows x K.  A CTA owns tiles blockIdx.x, +gridDim.x, ...
+// Each tile is fetched by 8 bulk copies (one per row) into a shared-memory stage
+// whose rows are padded by 64 bytes, which makes the fragment reads below free
+// of bank conflicts.  The first STAGES tiles are requested BEFORE the dependency
+// wait: the copies run in the async proxy, so they neither hold registers nor
+// queue in front of the latency-critical activation loads that follow the wait.
+//
+// The WARPS warps split K: warp w owns columns [w*K/WARPS, (w+1)*K/WARPS) =
+// LOADS blocks of 32.  In block j, lane (g = lane/4, t = lane%4) reads the 16
+// bytes W[row g][32j + 8t .. +7] from the stage and holds the matching 16 bytes
+// of x[batch g] in registers; word pairs (0,1) and (2,3) feed two m16n8k16 MMAs
+// with the batch on M and the weight rows on N.  The k order inside an MMA is a
+// fixed permutation applied to both operands, which a dot product ignores.
+// ---------------------------------------------------------------------------
+template <int LOADS, int WARPS>
+struct GemvSmem {
+  static constexpr int kK = LOADS * 32 * WARPS;
+  static constexpr int kRowStride = 2 * kK + 64;      // bytes
+  static constexpr int kStageBytes = kTileRows * kRowStride;
+  static constexpr int bytes(int stages) { return stages * kStageBytes + 8 * stages + 16; }
+};
+
+template <int LOADS, int WARPS, int STAGES, int MODE>
+__global__ void __launch_bounds__(WARPS * 32, LOADS <= 4 ? 3 : 2)
+stream_gemv_kernel(const GemvArgs a) {
+  constexpr bool kNorm = MODE != kModeStore;
+  constexpr int kWarps = WARPS;
+  using SM = GemvSmem<LOADS, WARPS>;
+  constexpr int K = SM::kK;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_min(a.trace, 0);
+
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  unsigned char* stage_base = dyn_smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(dyn_smem + STAGES * SM::kStageBytes);
   __shared__ float red[2][kWarps][64];
   __shared__ float ssq[kWarps][kMaxRows];
   __shared__ int last_flag;
@@ -145,27 +213,36 @@ __global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a)
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int K = LOADS * 256;
   const int kbase = warp * (LOADS * 32) + 8 * t;  // this lane's first column
   const int stride = gridDim.x;
 
-  auto weight_ptr = [&](int tile) -> const __nv_bfloat16* {
+  // row `r` of tile `tile` in global memory
+  auto weight_row = [&](int tile, int r) -> const __nv_bfloat16* {
     int row;
-    if (MODE == kModeNormSwiglu) row = ((g & 1) ? a.gate_rows : 0) + tile * 4 + (g >> 1);
-    else row = tile * kTileRows + g;
-    return a.w + (size_t)row * K + kbase;
+    if (MODE == kModeNormSwiglu) row = ((r & 1) ? a.gate_rows : 0) + tile * 4 + (r >> 1);
+    else row = tile * kTileRows + r;
+    return a.w + (size_t)row * K;
+  };
+  // warp 0: request tile `tile` into stage `s`
+  auto request_tile = [&](int tile, int s) {
+    if (lane == 0) mbar_expect_tx(&full[s], kTileRows * 2 * K);
+    __syncwarp();
+    if (lane < kTileRows)
+      bulk_g2s(stage_base + s * SM::kStageBytes + lane * SM::kRowStride, weight_row(tile, lane), 2 * K, &full[s]);
   };
 
   // ---- weight prefetch, independent of the previous kernel ----
-  uint4 wbuf[DEPTH][LOADS];
-  int tile = blockIdx.x;
+  if (warp == 0) {
+    if (lane == 0) {
 #pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
-    const int tl = tile + d * stride;
-    if (tl < a.n_tiles) {
-      const __nv_bfloat16* p = weight_ptr(tl);
+      for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
 #pragma unroll
-      for (int j = 0; j < LOADS; ++j) wbuf[d][j] = ldg_stream(p + 32 * j);
+    for (int s = 0; s < STAGES; ++s) {
+      const int tl = blockIdx.x + s * stride;
+      if (tl < a.n_tiles) request_tile(tl, s);
     }
   }
   uint4 nw[kNorm ? LOADS : 1];
@@ -173,8 +250,10 @@ __global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a)
 #pragma unroll
     for (int j = 0; j < LOADS; ++j) nw[j] = ldg_stream(a.norm_w + kbase + 32 * j);
   }
+  __syncthreads();  // the barriers are initialised before anyone polls them
 
   pdl_wait();
+  if (threadIdx.x == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
 
   // ---- prologue: this lane's fragments of x[batch g] ----
   uint4 xa[LOADS];
@@ -231,55 +310,64 @@ __global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a)
     }
   }
 
+  if (threadIdx.x == 0) trace_max(a.trace, 4);
   // ---- main loop over this CTA's tiles ----
   const int eb = tid >> 3, er = tid & 7;  // epilogue thread -> (batch row, tile row)
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   int it = 0;
-  while (tile < a.n_tiles) {
+  bool copy_ok = true;
+  for (int tile = blockIdx.x; tile < a.n_tiles; tile += stride, ++it) {
+    const int s = it % STAGES;
+    if (!mbar_wait_bounded(&full[s], (it / STAGES) & 1)) { copy_ok = false; break; }
+    const unsigned char* wrow = stage_base + s * SM::kStageBytes + g * SM::kRowStride + 2 * kbase;
+    float c[4][4];
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      if (tile < a.n_tiles) {
-        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
 #pragma unroll
-        for (int j = 0; j < LOADS; ++j) {
-          mma_bf16_16816(c0, xa[j].x, xa[j].y, wbuf[d][j].x, wbuf[d][j].y);
-          mma_bf16_16816(c1, xa[j].z, xa[j].w, wbuf[d][j].z, wbuf[d][j].w);
+    for (int j = 0; j < LOADS; ++j) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(wrow + 64 * j);
+      mma_bf16_16816(c[(2 * j) & 3], xa[j].x, xa[j].y, wv.x, wv.y);
+      mma_bf16_16816(c[(2 * j + 1) & 3], xa[j].z, xa[j].w, wv.z, wv.w);
+    }
+    if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 5);
+    float* r = red[it & 1][warp];
+    *reinterpret_cast<float2*>(r + 2 * lane) =
+        make_float2((c[0][0] + c[1][0]) + (c[2][0] + c[3][0]), (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]));
+    __syncthreads();  // every warp is done with stage s
+    if (warp == 0) {
+      const int nxt = tile + STAGES * stride;
+      if (nxt < a.n_tiles) request_tile(nxt, s);
+    }
+    if (tid < 64) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v += red[it & 1][w][tid];
+      v = round_bf16(v);
+      if (MODE == kModeStore || MODE == kModeNormStore) {
+        if (eb < a.rows) a.out[(size_t)eb * a.out_stride + tile * kTileRows + er] = __float2bfloat16_rn(v);
+      } else if (MODE == kModeNormSwiglu) {
+        const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+        if (!(er & 1) && eb < a.rows) {
+          const float act = v / (1.0f + expf(-v)) * up;
+          a.out[(size_t)eb * a.out_stride + tile * 4 + (er >> 1)] = __float2bfloat16_rn(act);
         }
-        const int nxt = tile + DEPTH * stride;
-        if (nxt < a.n_tiles) {
-          const __nv_bfloat16* p = weight_ptr(nxt);
-#pragma unroll
-          for (int j = 0; j < LOADS; ++j) wbuf[d][j] = ldg_stream(p + 32 * j);
+      } else {
+        const int idx = tile * kTileRows + er;
+        if (eb < a.rows) {
+          if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + idx] = v;
+          if (v > best_v || (v == best_v && idx < best_i)) { best_v = v; best_i = idx; }
         }
-        float* r = red[it & 1][warp];
-        *reinterpret_cast<float2*>(r + 2 * lane) = make_float2(c0[0] + c1[0], c0[1] + c1[1]);
-        __syncthreads();
-        if (tid < 64) {
-          float v = 0.f;
-#pragma unroll
-          for (int w = 0; w < kWarps; ++w) v += red[it & 1][w][tid];
-          v = round_bf16(v);
-          if (MODE == kModeStore || MODE == kModeNormStore) {
-            if (eb < a.rows) a.out[(size_t)eb * a.out_stride + tile * kTileRows + er] = __float2bfloat16_rn(v);
-          } else if (MODE == kModeNormSwiglu) {
-            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
-            if (!(er & 1) && eb < a.rows) {
-              const float act = v / (1.0f + expf(-v)) * up;
-              a.out[(size_t)eb * a.out_stride + tile * 4 + (er >> 1)] = __float2bfloat16_rn(act);
-            }
-          } else {
-            const int idx = tile * kTileRows + er;
-            if (eb < a.rows) {
-              if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + idx] = v;
-              if (v > best_v || (v == best_v && idx < best_i)) { best_v = v; best_i = idx; }
-            }
-          }
-        }
-        tile += stride;
-        ++it;
       }
     }
+    if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 6);
+  }
+  if (!copy_ok) {
+    // A bulk copy never completed: record it, give the copies in flight one more
+    // bounded chance to land, and leave without touching the outputs further.
+    report_status(a.status, kStatusCopyTimeout, kKernelGemv, blockIdx.x, it);
+#pragma unroll 1
+    for (int s = 0; s < STAGES; ++s) mbar_wait_bounded(&full[s], 0);
   }
 
   if (MODE == kModeNormArgmax) {
@@ -299,12 +387,11 @@ __global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a)
     __syncthreads();
     if (last_flag) {
       __threadfence();
-      const int b = warp;  // one warp per batch row
-      if (b < a.rows) {
+      for (int b = warp; b < a.rows; b += kWarps) {  // one warp per batch row
         float v = -INFINITY;
         int i = 0x7fffffff;
-        for (int c = lane; c < (int)gridDim.x; c += 32) {
-          const int2 raw = __ldcg(reinterpret_cast<const int2*>(a.parts + c * kMaxRows + b));
+        for (int c2 = lane; c2 < (int)gridDim.x; c2 += 32) {
+          const int2 raw = __ldcg(reinterpret_cast<const int2*>(a.parts + c2 * kMaxRows + b));
           const ArgmaxPart p{__int_as_float(raw.x), raw.y};
           if (p.value > v || (p.value == v && p.index < i)) { v = p.value; i = p.index; }
         }
@@ -322,6 +409,7 @@ __global__ void __launch_bounds__(kThreads) stream_gemv_kernel(const GemvArgs a)
       if (tid == 0) *a.ticket = 0u;
     }
   }
+  if (threadIdx.x == 0) trace_max(a.trace, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -353,12 +441,14 @@ struct AttnArgs {
   float* part_o;                // [rows, kv_heads, kMaxSplits, 2, 128]
   float2* part_ml;              // [rows, kv_heads, kMaxSplits, 2] (max, sum)
   unsigned int* tickets;        // [rows, kv_heads]
+  unsigned long long* trace;    // optional timeline slot of this launch or null
 };
 
 __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const AttnArgs a) {
   pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x;
+  if (tid == 0) trace_min(a.trace, 0);
   int pos = a.positions[row];
   if (pos < 0 || pos >= a.max_pos) {
     // A position outside the RoPE table / block table: record it and carry on
@@ -405,6 +495,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   }
 
   pdl_wait();
+  if (tid == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
 
   // ---- new token: q (2 heads) and k get RMSNorm + RoPE, v is copied ----
   {
@@ -520,6 +611,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   if (nsplits == 1) {
     out[d] = __float2bfloat16_rn(O0 / L0);
     out[kHeadDim + d] = __float2bfloat16_rn(O1 / L1);
+    if (tid == 0) trace_max(a.trace, 2);
     return;
   }
 
@@ -533,7 +625,10 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   __syncthreads();
   if (tid == 0) last_flag = (atomicAdd(a.tickets + row * a.kv_heads + kvh, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
   __syncthreads();
-  if (!last_flag) return;
+  if (!last_flag) {
+    if (tid == 0) trace_max(a.trace, 2);
+    return;
+  }
   __threadfence();
   float M0 = -INFINITY, M1 = -INFINITY;
   for (int s = 0; s < nsplits; ++s) {
@@ -553,7 +648,10 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   }
   out[d] = __float2bfloat16_rn(A0 / S0);
   out[kHeadDim + d] = __float2bfloat16_rn(A1 / S1);
-  if (tid == 0) a.tickets[row * a.kv_heads + kvh] = 0u;
+  if (tid == 0) {
+    a.tickets[row * a.kv_heads + kvh] = 0u;
+    trace_max(a.trace, 2);
+  }
 }
 
 // Copies one step's inputs into the decoder's fixed staging buffers (so a

@@ -145,6 +145,19 @@ class StreamDecoder:
         code = self._lib.dfb_read_status(self._handle, C.byref(st))
         return code, st
 
+    def read_trace(self):
+        """Timeline of the last traced step: rows of ``(start, wait_done_last,
+        end, wait_done_first, prologue_done, first_tile_mma_done, first_tile_done, 0)``
+        in ns per kernel, in launch order; also re-arms
+        the buffer (call once before the step to arm it)."""
+        import numpy as np
+
+        buf = np.zeros((1024, 8), dtype=np.uint64)
+        n = self._lib.dfb_read_trace(self._handle, buf.ctypes.data, 1024)
+        if n < 0:
+            self._native.check(n, "dfb_read_trace")
+        return buf[:n]
+
     def _stream(self) -> int:
         return self._torch.cuda.current_stream().cuda_stream
 

@@ -21,7 +21,7 @@ HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR.parent / "include" / "d
 DFB_ABI_VERSION = 1
 DFB_MAX_ROWS = 8
 DFB_ATTN_CHUNK = 64
-DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS = 1, 2, 3
+DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -30,7 +30,7 @@ NVCC_FLAGS = [
 
 EXPORTS = (
     "dfb_create", "dfb_destroy", "dfb_set_option", "dfb_decode_step", "dfb_decode_step_host",
-    "dfb_read_status", "dfb_error_string", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
+    "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
 )
 
@@ -111,6 +111,7 @@ def lib() -> C.CDLL:
     L.dfb_decode_step.argtypes = [vp, C.POINTER(DfbStepDesc), vp]
     L.dfb_decode_step_host.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_read_status.argtypes = [vp, C.POINTER(DfbStatus)]
+    L.dfb_read_trace.argtypes = [vp, vp, i32]
     L.dfb_error_string.argtypes = [C.c_int]
     L.dfb_error_string.restype = C.c_char_p
     L.dfb_launch_rmsnorm_qkv.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]

@@ -108,6 +108,7 @@ typedef struct DfbStatus {
 #define DFB_OPT_USE_GRAPH 1   /* 1 (default): replay a captured CUDA graph per (rows, split bucket) */
 #define DFB_OPT_USE_PDL 2     /* 1 (default): chain kernels with programmatic dependent launch */
 #define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
+#define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
  * copies the pointer tables, allocates the activation scratch (a few MB).
@@ -134,6 +135,16 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
  * call it after the stream has been synchronised. */
 int dfb_read_status(DfbHandle* h, DfbStatus* out);
 const char* dfb_error_string(int code);
+
+/* Timeline of the last traced step (DFB_OPT_TRACE): for each of its kernels, in
+ * launch order, eight uint64 words of globaltimer ns: {earliest CTA start,
+ * latest return from the dependency wait, latest CTA end, earliest return from
+ * the wait, latest end of the prologue, latest end of the first tile's MMAs,
+ * latest end of the first tile, 0} (`out` holds 8 * max_kernels words).  Returns the number of kernels written (<= max_kernels) or a negative
+ * code, and re-arms the buffer; call it once before the traced step to arm it.
+ * This is the per-task-time-versus-CTA-count diagnostic the reference ran as an
+ * SM-count sweep (TG_NUM_SMS, backends/megakernel/taskgraph.py:68-83). */
+int dfb_read_trace(DfbHandle* h, uint64_t* out, int32_t max_kernels);
 
 /* ---- standalone, non-cooperative launches of each kernel -------------------
  * One plain launch per call, so each kernel can be profiled or checked alone.
