@@ -2,8 +2,10 @@
 // per-step kernel chain (programmatic dependent launch), CUDA-graph cache,
 // host-buffer step, standalone launchers.
 #include "dfb_kernels.cuh"
+#include "dfb_persistent.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -13,10 +15,20 @@
 
 using namespace dfb;
 
-#define DFB_CUDA(expr)                          \
-  do {                                          \
-    cudaError_t e_ = (expr);                    \
-    if (e_ != cudaSuccess) return (int)e_;      \
+// With DFB_DEBUG set in the environment every failing CUDA call is reported on
+// stderr with its source line.
+static bool dfb_debug() {
+  static int on = -1;
+  if (on < 0) on = getenv("DFB_DEBUG") ? 1 : 0;
+  return on == 1;
+}
+#define DFB_CUDA(expr)                                                                          \
+  do {                                                                                          \
+    cudaError_t e_ = (expr);                                                                    \
+    if (e_ != cudaSuccess) {                                                                    \
+      if (dfb_debug()) fprintf(stderr, "dfb: %s -> %s (line %d)\n", #expr, cudaGetErrorString(e_), __LINE__); \
+      return (int)e_;                                                                           \
+    }                                                                                           \
   } while (0)
 
 namespace {
@@ -45,7 +57,19 @@ struct Launcher {
     cfg.attrs = attr;
     cfg.numAttrs = (pdl && allow_pdl) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
-    if (e != cudaSuccess) err = (int)e;
+    if (e != cudaSuccess) {
+      err = (int)e;
+      if (dfb_debug())
+      {
+        cudaFuncAttributes fa = {};
+        cudaFuncGetAttributes(&fa, (const void*)kernel);
+        int occ = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)kernel, (int)block.x, smem);
+        fprintf(stderr, "dfb: launch %d failed: %s (grid %u, block %u, smem %zu; regs %d, static smem %zu, "
+                "max threads %d, max dyn smem %d, occupancy %d)\n", count, cudaGetErrorString(e), grid.x, block.x, smem,
+                fa.numRegs, fa.sharedSizeBytes, fa.maxThreadsPerBlock, fa.maxDynamicSharedSizeBytes, occ);
+      }
+    }
     ++count;
   }
 };
@@ -64,6 +88,12 @@ struct DfbHandle {
   bool use_pdl = true;
   int lmhead_ctas = 0;
   bool trace_on = false;
+  int step_mode = 1;             // 1: one persistent kernel per step; 0: chain of per-op kernels
+  int persist_ctas = 0;          // grid of the persistent kernel (0 = one CTA per SM)
+  int trace_entries = 0;         // timeline entries written by the last traced step
+  PLayerWeights* d_layers = nullptr;
+  uint2 *x_qkv = nullptr, *x_attn = nullptr, *x_hattn = nullptr, *x_act = nullptr, *x_hmlp = nullptr;
+  unsigned int* epoch = nullptr;
   unsigned long long* trace = nullptr;  // [kMaxTraceKernels, 4] globaltimer ns
   // device scratch (one slab)
   void* slab = nullptr;
@@ -243,17 +273,45 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
   h->kernels_per_step = L.count;
+  h->trace_entries = L.count;
   return rc ? rc : L.err;
 }
 
+// The whole step as one persistent kernel (dfb_persistent.cuh).
+int enqueue_persistent(DfbHandle* h, int rows, cudaStream_t stream, float* logits_out) {
+  const DfbModelDesc& m = h->m;
+  PersistArgs a = {};
+  a.layers = h->d_layers; a.n_layers = m.layers; a.rows = rows; a.q_heads = m.q_heads; a.kv_heads = m.kv_heads;
+  a.intermediate = m.intermediate; a.vocab = m.vocab; a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim);
+  a.embed = (const bf16*)m.embed; a.final_norm = (const bf16*)m.final_norm; a.cos_sin = m.rope_cos_sin;
+  a.ids = h->st_ids(); a.positions = h->st_pos(); a.block_tables = h->st_bt(); a.bt_stride = h->max_pages;
+  a.row_active = h->st_active();
+  a.k_cache = (bf16*)m.k_cache; a.v_cache = (bf16*)m.v_cache; a.kv_layer_elems = h->kv_layer_elems;
+  a.block_size = m.block_size; a.num_blocks = m.num_blocks; a.max_pos = m.max_model_len;
+  a.x_qkv = h->x_qkv; a.x_attn = h->x_attn; a.x_hattn = h->x_hattn; a.x_act = h->x_act; a.x_hmlp = h->x_hmlp;
+  a.part_o = h->part_o; a.part_ml = h->part_ml; a.tickets = h->tickets; a.parts = h->parts; a.tokens = h->tokens;
+  a.logits_out = logits_out; a.epoch = h->epoch; a.status = h->status;
+  a.trace = h->trace_on ? h->trace : nullptr;
+  int grid = h->persist_ctas > 0 ? h->persist_ctas : h->sm_count;
+  if (grid > h->sm_count) grid = h->sm_count;   // every CTA must be resident at once
+  Launcher L{stream, false};
+  L.launch(decode_step_persistent_kernel, dim3(grid), dim3(kPThreads), a, false, kPDynSmem);
+  h->kernels_per_step = 1;
+  h->trace_entries = 5 * m.layers + 1;
+  return L.err;
+}
+
 int run_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
-  if (!h->use_graph || logits_out) return enqueue_step(h, rows, nsplit, stream, logits_out);
-  const int key = rows * 64 + nsplit + (h->use_pdl ? 4096 : 0);
+  const bool persistent = h->step_mode == 1;
+  if (!h->use_graph || logits_out)
+    return persistent ? enqueue_persistent(h, rows, stream, logits_out) : enqueue_step(h, rows, nsplit, stream, logits_out);
+  const int key = persistent ? 8192 + rows : rows * 64 + nsplit + (h->use_pdl ? 4096 : 0);
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
     cudaGraph_t graph = nullptr;
     DFB_CUDA(cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_step(h, rows, nsplit, h->capture_stream, nullptr);
+    int rc = persistent ? enqueue_persistent(h, rows, h->capture_stream, nullptr)
+                        : enqueue_step(h, rows, nsplit, h->capture_stream, nullptr);
     cudaError_t e = cudaStreamEndCapture(h->capture_stream, &graph);
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) return (int)e;
@@ -323,7 +381,14 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_act = carve(sizeof(bf16) * kMaxRows * d->intermediate);
   const size_t o_po = carve(sizeof(float) * kMaxRows * d->kv_heads * kMaxSplits * 2 * kHeadDim);
   const size_t o_pml = carve(sizeof(float2) * kMaxRows * d->kv_heads * kMaxSplits * 2);
-  const size_t o_tk = carve(sizeof(unsigned) * (kMaxRows * d->kv_heads + 1));
+  const size_t o_tk = carve(sizeof(unsigned) * (2 * kMaxRows * d->kv_heads + 1));
+  const size_t o_layers = carve(sizeof(PLayerWeights) * d->layers);
+  const size_t o_xqkv = carve(sizeof(uint2) * kMaxRows * h->qkv_rows() / 2);
+  const size_t o_xattn = carve(sizeof(uint2) * kMaxRows * h->q_size() / 2);
+  const size_t o_xhattn = carve(sizeof(uint2) * kMaxRows * d->hidden / 2);
+  const size_t o_xact = carve(sizeof(uint2) * kMaxRows * d->intermediate / 2);
+  const size_t o_xhmlp = carve(sizeof(uint2) * kMaxRows * d->hidden / 2);
+  const size_t o_epoch = carve(sizeof(unsigned) * 4);
   const size_t o_parts = carve(sizeof(ArgmaxPart) * kMaxRows * 4096);
   const size_t o_trace = carve(sizeof(unsigned long long) * 8 * kMaxTraceKernels);
   const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
@@ -339,6 +404,18 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   h->qkv = (bf16*)(s + o_qkv); h->attn = (bf16*)(s + o_attn); h->act = (bf16*)(s + o_act);
   h->part_o = (float*)(s + o_po); h->part_ml = (float2*)(s + o_pml); h->tickets = (unsigned*)(s + o_tk);
   h->parts = (ArgmaxPart*)(s + o_parts); h->trace = (unsigned long long*)(s + o_trace);
+  h->d_layers = (PLayerWeights*)(s + o_layers);
+  h->x_qkv = (uint2*)(s + o_xqkv); h->x_attn = (uint2*)(s + o_xattn); h->x_hattn = (uint2*)(s + o_xhattn);
+  h->x_act = (uint2*)(s + o_xact); h->x_hmlp = (uint2*)(s + o_xhmlp); h->epoch = (unsigned int*)(s + o_epoch);
+  {
+    static_assert(sizeof(PLayerWeights) == sizeof(DfbLayerWeights), "layer pointer tables must have one layout");
+    const unsigned one = 1u;   // tags are built from the epoch and must never be zero
+    e = cudaMemcpy(h->d_layers, h->layers.data(), sizeof(PLayerWeights) * d->layers, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(h->epoch, &one, sizeof(one), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_step_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPDynSmem);
+    if (e != cudaSuccess) { dfb_destroy(h); return (int)e; }
+  }
   h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
   *out = h;
   return 0;
@@ -359,6 +436,16 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
   switch (option) {
     case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
     case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
+    case DFB_OPT_STEP_MODE:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      h->step_mode = value;
+      return 0;
+    case DFB_OPT_PERSIST_CTAS:
+      if (value < 0 || value > 4096) return DFB_E_BAD_ARG;
+      h->persist_ctas = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
     case DFB_OPT_TRACE:
       h->trace_on = value != 0;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
@@ -458,7 +545,7 @@ int dfb_read_status(DfbHandle* h, DfbStatus* out) {
 
 int dfb_read_trace(DfbHandle* h, uint64_t* out, int32_t max_kernels) {
   if (!h || !out || max_kernels < 1) return DFB_E_BAD_ARG;
-  int n = h->kernels_per_step < max_kernels ? h->kernels_per_step : max_kernels;
+  int n = h->trace_entries < max_kernels ? h->trace_entries : max_kernels;
   if (n > kMaxTraceKernels) n = kMaxTraceKernels;
   DFB_CUDA(cudaMemcpy(out, h->trace, sizeof(uint64_t) * 8 * n, cudaMemcpyDeviceToHost));
   // re-arm: minima (words 0 and 3) start at the largest value, maxima at zero

@@ -67,7 +67,7 @@ class StreamDecoder:
     def __init__(self, weights, k_cache, v_cache, block_size: int, num_cache_blocks: int,
                  max_model_len: int = 2048, attn_splits: int = 1, fusion_groups: int = 1,
                  verbose: bool = False, debug_bounds: bool = False, use_graph: bool = True,
-                 use_pdl: bool = True):
+                 use_pdl: bool = True, persistent: bool = True):
         import torch
 
         from . import native
@@ -114,6 +114,7 @@ class StreamDecoder:
         self._handle = handle
         native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_GRAPH, int(use_graph)), "dfb_set_option")
         native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_PDL, int(use_pdl)), "dfb_set_option")
+        native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_STEP_MODE, int(persistent)), "dfb_set_option")
 
         # persistent per-step buffers: no allocation on the step path
         self._result = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cuda")

@@ -108,6 +108,8 @@ typedef struct DfbStatus {
 #define DFB_OPT_USE_GRAPH 1   /* 1 (default): replay a captured CUDA graph per (rows, split bucket) */
 #define DFB_OPT_USE_PDL 2     /* 1 (default): chain kernels with programmatic dependent launch */
 #define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
+#define DFB_OPT_STEP_MODE 5   /* 1 (default): the step is one persistent kernel; 0: a chain of per-op kernels */
+#define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

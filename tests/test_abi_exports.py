@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
 def test_constants_match_header():
     text = HEADER.read_text()
     for name in ("DFB_ABI_VERSION", "DFB_MAX_ROWS", "DFB_ATTN_CHUNK", "DFB_OPT_USE_GRAPH", "DFB_OPT_USE_PDL",
-                 "DFB_OPT_LMHEAD_CTAS"):
+                 "DFB_OPT_LMHEAD_CTAS", "DFB_OPT_TRACE", "DFB_OPT_STEP_MODE", "DFB_OPT_PERSIST_CTAS"):
         value = int(re.search(rf"#define {name}\s+(\d+)", text).group(1))
         assert getattr(native, name) == value
 

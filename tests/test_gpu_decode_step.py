@@ -19,12 +19,15 @@ def _check(report):
     assert report["max_abs_kv_diff"] <= 2.0 ** -5, report
 
 
+@pytest.mark.parametrize("persistent", [True, False])
 @pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 6, 7, 8])
-def test_step_matches_oracle_for_every_batch_size(cuda_device, rows):
+def test_step_matches_oracle_for_every_batch_size(cuda_device, rows, persistent):
+    """Both step implementations: the persistent kernel (default) and the chain
+    of per-op kernels."""
     lens = [3, 70, 250, 129, 64, 1, 300, 17][:rows]
-    r = H.run_parity_case(layers=2, vocab=4096, prompt_lens=lens, steps=3, seed=rows)
+    r = H.run_parity_case(layers=2, vocab=4096, prompt_lens=lens, steps=3, seed=rows, persistent=persistent)
     _check(r)
-    assert r["kernels_per_step"] == 2 * 5 + 1
+    assert r["kernels_per_step"] == (1 if persistent else 2 * 5 + 1)
 
 
 @pytest.mark.parametrize("prompt", [254, 255, 256, 257])
@@ -45,11 +48,61 @@ def test_max_context(cuda_device):
     _check(H.run_parity_case(layers=1, vocab=1024, prompt_lens=[2044, 1], steps=3, seed=13))
 
 
-@pytest.mark.parametrize("use_graph,use_pdl", [(False, False), (False, True), (True, False)])
-def test_launch_modes_agree(cuda_device, use_graph, use_pdl):
-    """Plain launches, PDL launches and graph replay must give the same result."""
+@pytest.mark.parametrize("use_graph,use_pdl,persistent", [
+    (False, False, False), (False, True, False), (True, False, False), (True, True, False), (False, False, True)])
+def test_launch_modes_agree(cuda_device, use_graph, use_pdl, persistent):
+    """Plain launches, PDL launches, graph replay and the persistent kernel
+    outside a graph must all give the same result."""
     _check(H.run_parity_case(layers=3, vocab=2048, prompt_lens=[5, 130], steps=3, seed=14,
-                             use_graph=use_graph, use_pdl=use_pdl))
+                             use_graph=use_graph, use_pdl=use_pdl, persistent=persistent))
+
+
+def test_persistent_and_chained_steps_agree(cuda_device):
+    """The two step implementations split K differently across warps for o_proj
+    and down_proj (another summation order), so they agree to bf16 rounding, not
+    bit for bit."""
+    lens = [40, 300, 7, 64]
+    g, w, kv, tables, first = _setup(lens, seed=21, layers=3)
+    outs = []
+    for persistent in (True, False):
+        kvg = kv.cuda()
+        dec = H.make_decoder(w, kvg, persistent=persistent)
+        logits = torch.zeros(4, g.vocab, device="cuda")
+        cur, cl, seen = list(first), [n + 1 for n in lens], []
+        for _ in range(3):
+            dec.enqueue_rows(torch.tensor(cur, device="cuda"), torch.tensor([n - 1 for n in cl], device="cuda"),
+                             H.padded_tables(tables, cl, g.block_size), out_logits=logits)
+            torch.cuda.synchronize()
+            seen.append(logits.clone())
+            cur, cl = dec.tokens_device()[:4].tolist(), [n + 1 for n in cl]
+        outs.append((seen, kvg.clone()))
+        dec.close()
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert float((a - b).abs().max()) <= H.LOGIT_ATOL
+    assert float((outs[0][1].float() - outs[1][1].float()).abs().max()) <= 2.0 ** -5
+
+
+@pytest.mark.parametrize("ctas", [1, 7, 64, 147])
+def test_persistent_kernel_with_fewer_ctas(cuda_device, ctas):
+    """The persistent kernel is correct for any grid size (the CTA-count sweep
+    of the reference's TG_NUM_SMS diagnostic relies on it)."""
+    from dfb_b200 import native
+    lens = [130, 9]
+    g, w, kv, tables, first = _setup(lens, seed=22, layers=2)
+    res = []
+    for n in (0, ctas):
+        kvg = kv.cuda()
+        dec = H.make_decoder(w, kvg)
+        dec.set_option(native.DFB_OPT_PERSIST_CTAS, n)
+        logits = torch.zeros(2, g.vocab, device="cuda")
+        dec.enqueue_rows(torch.tensor(first, device="cuda"), torch.tensor(lens, device="cuda"),
+                         H.padded_tables(tables, [n_ + 1 for n_ in lens], g.block_size), out_logits=logits)
+        torch.cuda.synchronize()
+        code, st = dec.status()
+        assert code == 0
+        res.append((logits.clone(), dec.tokens_device()[:2].tolist()))
+        dec.close()
+    assert torch.equal(res[0][0], res[1][0]) and res[0][1] == res[1][1]
 
 
 def test_host_buffer_step(cuda_device):
