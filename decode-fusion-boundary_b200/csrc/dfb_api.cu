@@ -545,9 +545,9 @@ int dfb_read_status(DfbHandle* h, DfbStatus* out) {
 
 int dfb_read_trace(DfbHandle* h, uint64_t* out, int32_t max_kernels) {
   if (!h || !out || max_kernels < 1) return DFB_E_BAD_ARG;
-  int n = h->trace_entries < max_kernels ? h->trace_entries : max_kernels;
-  if (n > kMaxTraceKernels) n = kMaxTraceKernels;
+  int n = max_kernels > kMaxTraceKernels ? kMaxTraceKernels : max_kernels;
   DFB_CUDA(cudaMemcpy(out, h->trace, sizeof(uint64_t) * 8 * n, cudaMemcpyDeviceToHost));
+  if (h->trace_entries < n) n = h->trace_entries;
   // re-arm: minima (words 0 and 3) start at the largest value, maxima at zero
   std::vector<unsigned long long> init(8 * kMaxTraceKernels, 0ull);
   for (int i = 0; i < kMaxTraceKernels; ++i) { init[8 * i] = ~0ull; init[8 * i + 3] = ~0ull; }

@@ -157,6 +157,7 @@ class StreamDecoder:
         n = self._lib.dfb_read_trace(self._handle, buf.ctypes.data, 1024)
         if n < 0:
             self._native.check(n, "dfb_read_trace")
+        self.trace_detail = buf[512:576].reshape(32, 16).copy()   # clock64 marks of CTA 0 (persistent kernel)
         return buf[:n]
 
     def _stream(self) -> int:
