@@ -3,6 +3,7 @@
 // host-buffer step, standalone launchers.
 #include "dfb_kernels.cuh"
 #include "dfb_persistent.cuh"
+#include "dfb_rowgemv.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -165,6 +166,15 @@ void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
   L.launch(kernel, dim3(grid), dim3(WARPS * 32), a, allow_pdl, smem);
 }
 
+// FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
+template <int K, int RPW, int MODE>
+void launch_row(Launcher& L, GemvArgs& a, int rows, int grid, bool allow_pdl = true) {
+  a.trace = L.next_trace();
+  if (rows == 1) L.launch(row_gemv_kernel<K, RPW, 1, MODE>, dim3(grid), dim3(kRowThreads), a, allow_pdl);
+  else L.launch(row_gemv_kernel<K, RPW, 2, MODE>, dim3(grid), dim3(kRowThreads), a, allow_pdl);
+}
+bool g_row_path = true;   // DFB_OPT_ROW_GEMV: use the FP32 path for rows <= 2
+
 int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_in, bf16* res_out, const bf16* ln_w,
                     const bf16* w, bf16* out, int rows, int hidden, int n, float eps, int* status, bool allow_pdl) {
   if (hidden != 1024 || n % kTileRows) return DFB_E_GEOMETRY;
@@ -172,6 +182,11 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = hidden;
   a.x = x; a.ids = ids; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = out; a.out_stride = n; a.status = status;
+  if (g_row_path && rows <= 2 && n % 16 == 0) {
+    a.n_tiles = n / 16;
+    launch_row<1024, 2, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
+    return L.err;
+  }
   launch_gemv<4, 8, 4, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
   return L.err;
 }
@@ -181,6 +196,12 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
   GemvArgs a = {};
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = k; a.x = x; a.out = out; a.out_stride = n;
   a.status = status;
+  if (g_row_path && rows <= 2 && (k == 2048 || k == 3072)) {
+    a.n_tiles = n / 8;
+    if (k == 2048) launch_row<2048, 1, kModeStore>(L, a, rows, a.n_tiles);
+    else launch_row<3072, 1, kModeStore>(L, a, rows, a.n_tiles);
+    return L.err;
+  }
   const int grid = grid_for(a.n_tiles);
   switch (loads_for_k(k)) {
     case 4: launch_gemv<4, 8, 4, kModeStore>(L, a, grid); break;
@@ -198,6 +219,11 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   a.w = wgu; a.n_tiles = inter / 4; a.rows = rows; a.k = hidden;
   a.x = h; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
+  if (g_row_path && rows <= 2 && inter % 8 == 0) {
+    a.n_tiles = inter / 8;
+    launch_row<1024, 2, kModeNormSwiglu>(L, a, rows, a.n_tiles);
+    return L.err;
+  }
   launch_gemv<4, 8, 6, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
   return L.err;
 }
@@ -210,6 +236,13 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   a.x = hid; a.res_in = res_in; a.norm_w = (const bf16*)m.final_norm; a.eps = m.eps;
   a.logits_out = logits_out; a.vocab = m.vocab; a.status = h->status;
   a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens; a.tokens_out = tokens_out;
+  if (g_row_path && rows <= 2 && m.vocab % 16 == 0) {
+    a.n_tiles = m.vocab / 16;
+    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    launch_row<1024, 2, kModeNormArgmax>(L, a, rows, grid);
+    return L.err;
+  }
   int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
   if (grid > a.n_tiles) grid = a.n_tiles;
   launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid);
@@ -436,6 +469,11 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
   switch (option) {
     case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
     case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
+    case DFB_OPT_ROW_GEMV:
+      g_row_path = value != 0;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
     case DFB_OPT_STEP_MODE:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
       h->step_mode = value;

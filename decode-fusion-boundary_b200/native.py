@@ -16,13 +16,13 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libdfb_decode.so"
 SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
-HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
+HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
 
 DFB_ABI_VERSION = 1
 DFB_MAX_ROWS = 8
 DFB_ATTN_CHUNK = 64
 DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
-DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS = 5, 6
+DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS, DFB_OPT_ROW_GEMV = 5, 6, 7
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
