@@ -14,8 +14,8 @@ resident on the device (CUDA events around K back-to-back steps, tokens fed
 back on the device); ``e2e`` is the same metric through the user-facing
 ``MegakernelBackend.decode`` / ``decode_batch`` call with host inputs, i.e. one
 host-to-device copy, the step, one device-to-host copy and one synchronisation
-per step; ``roofline`` is the step kernel (algorithmic weight + KV bytes over the
-device time per step); ``cpu_baseline`` is the CPU oracle (a port of the reference torch path)
+per step; ``roofline`` is the LM-head + argmax kernel (the largest single kernel)
+timed alone, ``step_floor`` relates the whole step to its byte floor; ``cpu_baseline`` is the CPU oracle (a port of the reference torch path)
 timed on the host cores for a bounded number of steps.
 
 ``--impl reference`` times that CPU path alone with all host threads.
@@ -42,12 +42,9 @@ sys.path.insert(0, str(ROOT))
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one step-kernel launch.  Captured
-# with Nsight Compute on an 8-layer / 32768-token-vocabulary model of the same
-# layer shape (326.3 MB measured for 318.8 MB of algorithmic bytes, see profiles/)
-# and scaled to the full model by the algorithmic bytes, which is what the traffic
-# is proportional to (every weight byte is read once).
-STEP_DRAM_TRAFFIC_BYTES = int(1_192_099_840 * 326.293 / 318.8)
+# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head launch, from the
+# Nsight Compute capture summarised under profiles/ (batch 1, full vocabulary).
+LMHEAD_DRAM_TRAFFIC_BYTES = 316_430_080
 
 
 def measured_peaks():
@@ -288,7 +285,10 @@ def run_own_arm(args):
     code, st = dec.status()
     kernels_per_step = int(st.kernels_per_step) + 1   # + the input staging kernel
     step_kernel = ("decode_step_persistent_kernel (whole step: 28 layers + LM head + argmax)"
-                   if int(st.kernels_per_step) == 1 else "chain of stream_gemv_kernel / paged_attention_kernel")
+                   if int(st.kernels_per_step) == 1 else
+                   f"chain of {int(st.kernels_per_step)} kernels in one CUDA graph with programmatic dependent launch")
+    lm_kernel = ("row_gemv_kernel<1024,NB,NormArgmax> (LM head + greedy argmax, FP32 pipe)" if B <= 2 else
+                 "stream_gemv_kernel<4,8,6,NormArgmax> (LM head + greedy argmax, mma.sync)")
 
     peak, peak_kind = measured_peaks()
     lm_bytes = g.lm_head_bytes() + 2 * g.hidden
@@ -307,15 +307,11 @@ def run_own_arm(args):
                 "h2d_bytes_per_step": 4 * (24 + 8 * g.max_pages) if B == 1 else 8 * B * 2 + 4 * B * g.max_pages,
                 "d2h_bytes_per_step": 48, "api": "MegakernelBackend.decode" if B == 1 else "MegakernelBackend.decode_batch"},
         "gpu_launches": kernels_per_step * K,
-        # the dominant kernel is the step kernel itself: its algorithmic bytes are the
-        # step's weight + KV bytes, its duration the device time per step measured above
-        "roofline": {"kernel": step_kernel, "bound": "hbm", "achieved": step_bytes / (us_per_step * 1e3),
-                     "peak": peak, "unit": "GB/s", "frac": step_bytes / (us_per_step * 1e3) / peak,
-                     "traffic": STEP_DRAM_TRAFFIC_BYTES, "bytes_per_launch": step_bytes,
-                     "us_per_launch": us_per_step, "peak_source": peak_kind},
-        "lmhead_kernel": {"kernel": "stream_gemv_kernel<4,8,6,NormArgmax> (standalone LM head + greedy argmax)",
-                          "achieved": lm_bytes / (lm_ms * 1e6), "unit": "GB/s", "frac": lm_bytes / (lm_ms * 1e6) / peak,
-                          "bytes_per_launch": lm_bytes, "us_per_launch": 1e3 * lm_ms},
+        # the dominant kernel is the LM head + argmax kernel (26% of the step's bytes in one launch), timed alone
+        "roofline": {"kernel": lm_kernel, "bound": "hbm", "achieved": lm_bytes / (lm_ms * 1e6), "peak": peak,
+                     "unit": "GB/s", "frac": lm_bytes / (lm_ms * 1e6) / peak, "traffic": LMHEAD_DRAM_TRAFFIC_BYTES,
+                     "bytes_per_launch": lm_bytes, "us_per_launch": 1e3 * lm_ms, "peak_source": peak_kind},
+        "step_kernels": step_kernel,
         "clocks": clocks,
         "device_status": int(st.device_status),
     }

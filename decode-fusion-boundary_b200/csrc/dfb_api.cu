@@ -89,7 +89,7 @@ struct DfbHandle {
   bool use_pdl = true;
   int lmhead_ctas = 0;
   bool trace_on = false;
-  int step_mode = 1;             // 1: one persistent kernel per step; 0: chain of per-op kernels
+  int step_mode = 0;             // 0: chain of per-op kernels (default); 1: one persistent kernel per step
   int persist_ctas = 0;          // grid of the persistent kernel (0 = one CTA per SM)
   int trace_entries = 0;         // timeline entries written by the last traced step
   PLayerWeights* d_layers = nullptr;
@@ -167,11 +167,11 @@ void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
 }
 
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
-template <int K, int RPW, int MODE>
+template <int K, int MODE>
 void launch_row(Launcher& L, GemvArgs& a, int rows, int grid, bool allow_pdl = true) {
   a.trace = L.next_trace();
-  if (rows == 1) L.launch(row_gemv_kernel<K, RPW, 1, MODE>, dim3(grid), dim3(kRowThreads), a, allow_pdl);
-  else L.launch(row_gemv_kernel<K, RPW, 2, MODE>, dim3(grid), dim3(kRowThreads), a, allow_pdl);
+  if (rows == 1) L.launch(row_gemv_kernel<K, 1, MODE>, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl);
+  else L.launch(row_gemv_kernel<K, 2, MODE>, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl);
 }
 bool g_row_path = true;   // DFB_OPT_ROW_GEMV: use the FP32 path for rows <= 2
 
@@ -184,7 +184,7 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   a.out = out; a.out_stride = n; a.status = status;
   if (g_row_path && rows <= 2 && n % 16 == 0) {
     a.n_tiles = n / 16;
-    launch_row<1024, 2, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
+    launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
     return L.err;
   }
   launch_gemv<4, 8, 4, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
@@ -198,8 +198,8 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
   a.status = status;
   if (g_row_path && rows <= 2 && (k == 2048 || k == 3072)) {
     a.n_tiles = n / 8;
-    if (k == 2048) launch_row<2048, 1, kModeStore>(L, a, rows, a.n_tiles);
-    else launch_row<3072, 1, kModeStore>(L, a, rows, a.n_tiles);
+    if (k == 2048) launch_row<2048, kModeStore>(L, a, rows, a.n_tiles);
+    else launch_row<3072, kModeStore>(L, a, rows, a.n_tiles);
     return L.err;
   }
   const int grid = grid_for(a.n_tiles);
@@ -221,7 +221,7 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
   if (g_row_path && rows <= 2 && inter % 8 == 0) {
     a.n_tiles = inter / 8;
-    launch_row<1024, 2, kModeNormSwiglu>(L, a, rows, a.n_tiles);
+    launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
   launch_gemv<4, 8, 6, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
@@ -240,7 +240,7 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
-    launch_row<1024, 2, kModeNormArgmax>(L, a, rows, grid);
+    launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
     return L.err;
   }
   int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;

@@ -2,63 +2,65 @@
 //
 // mma.sync issues only about one m16n8k16 per 38 cycles per SM sub-partition on
 // this part, and a batch of one or two rows wastes most of each MMA anyway, so
-// for rows <= 2 every projection is a classic row-parallel GEMV:
-//   * a warp owns whole weight rows (RPW = 2: one row per half-warp, K = 1024;
-//     RPW = 1: one row per warp, K = 2048 / 3072), lanes interleave 16-byte
-//     chunks of the row, so global loads are fully coalesced 128-bit loads;
-//   * the row's weights are requested into registers BEFORE the dependency wait
-//     (programmatic dependent launch), so they stream while the previous kernel
-//     is still running;
-//   * x (after the fused residual add + RMSNorm, done by all 256 threads, 4
-//     elements each) is kept in shared memory as fp32;
-//   * products are accumulated in fp32, reduced with shuffles, rounded once to
-//     bf16, and the epilogue (store / SwiGLU / logits + greedy argmax) runs in the
-//     lane that holds the sum.  No shared-memory reduction, no tensor cores.
-// Registers stay low (about 64), so three CTAs of 8 warps share an SM: the
-// occupancy hides the instruction latency that dominates these tiny kernels.
+// for rows <= 2 every projection runs on the FP32 pipe:
+//   * a CTA owns RC consecutive weight rows (16 at K = 1024, 8 at K = 2048 and
+//     3072) and its warps split K: warp w owns columns [w*S, (w+1)*S) with
+//     S = 128 or 256, so a lane needs only 8 values of x per batch row, kept in
+//     registers, and multiplies them with the same 16-byte chunk of 8 rows;
+//   * the weight chunks (8 x 16 bytes per lane, fully coalesced) are requested
+//     BEFORE the dependency wait (programmatic dependent launch), so they stream
+//     while the previous kernel is still running;
+//   * the residual add + RMSNorm is done by the whole CTA, 4 elements per thread;
+//   * per-row partial sums are reduced with a halving butterfly of shuffles, then
+//     across warps through shared memory, rounded once to bf16; the epilogue
+//     (store / SwiGLU / logits + greedy argmax) is done by one thread per row.
 #pragma once
 
 #include "dfb_kernels.cuh"
 
 namespace dfb {
 
-constexpr int kRowThreads = 256;
-constexpr int kRowWarps = 8;
+template <int K>
+struct RowCfg {
+  static constexpr int kWarps = K == 3072 ? 12 : 8;
+  static constexpr int kSlice = K / kWarps;            // columns per warp: 128 or 256
+  static constexpr int kLanesPerRow = kSlice / 8;      // 16 or 32 lanes cover the slice
+  static constexpr int kHalves = 32 / kLanesPerRow;    // row halves handled side by side: 2 or 1
+  static constexpr int kRows = 8 * kHalves;            // rows per CTA and group: 16 or 8
+  static constexpr int kThreads = kWarps * 32;
+};
 
-template <int K, int RPW, int NB, int MODE>
-__global__ void __launch_bounds__(kRowThreads, 3) row_gemv_kernel(const GemvArgs a) {
+template <int K, int NB, int MODE>
+__global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_gemv_kernel(const GemvArgs a) {
+  using C = RowCfg<K>;
   constexpr bool kNorm = MODE != kModeStore;
-  constexpr int LPR = 32 / RPW;            // lanes per row
-  constexpr int NL = K / LPR / 8;          // 16-byte weight chunks per lane
-  constexpr int RPC = kRowWarps * RPW;     // rows (or gate/up pairs * 2) per CTA and group
+  constexpr int W = C::kWarps, LPR = C::kLanesPerRow, RC = C::kRows;
   static_assert(!kNorm || K == 1024, "the fused norm covers the hidden size only");
   pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
   __shared__ __align__(16) float xs[NB][K];
-  __shared__ float ssq[kRowWarps][NB];
-  __shared__ float cta_v[kRowWarps][NB];
-  __shared__ int cta_i[kRowWarps][NB];
+  __shared__ float ssq[W][NB];
+  __shared__ float red[W][NB][RC];
   __shared__ int last_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int half = lane / LPR, lr = lane % LPR;   // row slot inside the warp, lane inside the row
+  const int hr = lane / LPR, lc = lane % LPR;      // row half, 16-byte chunk inside the warp's slice
+  const int col = warp * C::kSlice + 8 * lc;       // this lane's 8 columns
   const int n_groups = a.n_tiles;
 
-  // weights of group `grp` for this lane: row r, chunks lr + LPR * j
-  auto weight_row = [&](int grp) -> const __nv_bfloat16* {
-    if (MODE == kModeNormSwiglu) {
-      const int i = grp * kRowWarps + warp;                       // gate / up pair index
-      return a.w + (size_t)(half ? a.gate_rows + i : i) * K;
-    }
-    return a.w + (size_t)(grp * RPC + warp * RPW + half) * K;
+  // weight row i (0..7) of this lane's half in group `grp`
+  auto weight_ptr = [&](int grp, int i) -> const __nv_bfloat16* {
+    int row;
+    if (MODE == kModeNormSwiglu) row = (hr ? a.gate_rows : 0) + grp * 8 + i;   // half 0: gate rows, half 1: up rows
+    else row = grp * RC + hr * 8 + i;
+    return a.w + (size_t)row * K + col;
   };
-  uint4 wreg[NL];
+  uint4 wreg[8];
   int grp = blockIdx.x;
   if (grp < n_groups) {
-    const __nv_bfloat16* p = weight_row(grp) + 8 * lr;
 #pragma unroll
-    for (int j = 0; j < NL; ++j) wreg[j] = ldg_stream(p + 8 * LPR * j);
+    for (int i = 0; i < 8; ++i) wreg[i] = ldg_stream(weight_ptr(grp, i));
   }
   uint2 nwv = make_uint2(0, 0);
   if (kNorm) nwv = *reinterpret_cast<const uint2*>(a.norm_w + 4 * tid);
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(kRowThreads, 3) row_gemv_kernel(const GemvArgs
     for (int b = 0; b < NB; ++b) {
       float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < kRowWarps; ++w) tot += ssq[w][b];
+      for (int w = 0; w < W; ++w) tot += ssq[w][b];
       const float rstd = 1.0f / sqrtf(tot / (float)K + a.eps);
       float4 y;
       y.x = round_bf16(round_bf16(x[b][0] * rstd) * w0); y.y = round_bf16(round_bf16(x[b][1] * rstd) * w1);
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(kRowThreads, 3) row_gemv_kernel(const GemvArgs
   } else {
 #pragma unroll
     for (int b = 0; b < NB; ++b)
-      for (int c = tid; c < K / 8; c += kRowThreads) {
+      for (int c = tid; c < K / 8; c += C::kThreads) {
         float f[8];
         if (b < a.rows) {
           const uint4 v = ldg_cg(a.x + (size_t)b * K + 8 * c);
@@ -124,91 +126,103 @@ __global__ void __launch_bounds__(kRowThreads, 3) row_gemv_kernel(const GemvArgs
   __syncthreads();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
   if (probe) { c1 = clock64(); a.trace[5] = (unsigned long long)(c1 - c0); }
-  float best_v[NB];
-  int best_i[NB];
+
+  // this lane's 8 values of x per batch row
+  float xr[NB][8];
 #pragma unroll
-  for (int b = 0; b < NB; ++b) { best_v[b] = -INFINITY; best_i[b] = 0x7fffffff; }
+  for (int b = 0; b < NB; ++b) {
+    const float4 x0 = *reinterpret_cast<const float4*>(&xs[b][col]);
+    const float4 x1 = *reinterpret_cast<const float4*>(&xs[b][col + 4]);
+    xr[b][0] = x0.x; xr[b][1] = x0.y; xr[b][2] = x0.z; xr[b][3] = x0.w;
+    xr[b][4] = x1.x; xr[b][5] = x1.y; xr[b][6] = x1.z; xr[b][7] = x1.w;
+  }
+
+  float best_v = -INFINITY;   // epilogue thread (b, r): running argmax of its rows
+  int best_i = 0x7fffffff;
+  const int eb = tid / RC, er = tid % RC;   // epilogue thread -> (batch row, row of the group), tid < RC * NB
 
   // ---- row groups of this CTA ----
-  for (; grp < n_groups; grp += gridDim.x) {
-    float acc[NB][4];
+  for (int it = 0; grp < n_groups; grp += gridDim.x, ++it) {
+    // 8 rows x 8 columns per lane: partial dot products p[b][i]
+    float p[NB][8];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) { acc[b][0] = 0.f; acc[b][1] = 0.f; acc[b][2] = 0.f; acc[b][3] = 0.f; }
-#pragma unroll
-    for (int j = 0; j < NL; ++j) {
+    for (int i = 0; i < 8; ++i) {
       float wf[8];
-      unpack8(wreg[j], wf);
-      const int col = 8 * (lr + LPR * j);
+      unpack8(wreg[i], wf);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        const float4 x0 = *reinterpret_cast<const float4*>(&xs[b][col]);
-        const float4 x1 = *reinterpret_cast<const float4*>(&xs[b][col + 4]);
-        acc[b][0] = fmaf(wf[0], x0.x, acc[b][0]); acc[b][1] = fmaf(wf[1], x0.y, acc[b][1]);
-        acc[b][2] = fmaf(wf[2], x0.z, acc[b][2]); acc[b][3] = fmaf(wf[3], x0.w, acc[b][3]);
-        acc[b][0] = fmaf(wf[4], x1.x, acc[b][0]); acc[b][1] = fmaf(wf[5], x1.y, acc[b][1]);
-        acc[b][2] = fmaf(wf[6], x1.z, acc[b][2]); acc[b][3] = fmaf(wf[7], x1.w, acc[b][3]);
+        float s0 = wf[0] * xr[b][0], s1 = wf[1] * xr[b][1];
+        s0 = fmaf(wf[2], xr[b][2], s0); s1 = fmaf(wf[3], xr[b][3], s1);
+        s0 = fmaf(wf[4], xr[b][4], s0); s1 = fmaf(wf[5], xr[b][5], s1);
+        s0 = fmaf(wf[6], xr[b][6], s0); s1 = fmaf(wf[7], xr[b][7], s1);
+        p[b][i] = s0 + s1;
       }
     }
     // request the next group's weights as soon as the registers are free
     const int nxt = grp + gridDim.x;
     if (nxt < n_groups) {
-      const __nv_bfloat16* p = weight_row(nxt) + 8 * lr;
 #pragma unroll
-      for (int j = 0; j < NL; ++j) wreg[j] = ldg_stream(p + 8 * LPR * j);
+      for (int i = 0; i < 8; ++i) wreg[i] = ldg_stream(weight_ptr(nxt, i));
     }
-    float v[NB];
+    // halving butterfly over the lanes of a row half: afterwards lane lc holds the
+    // sum over the warp's slice for row (lc & 7)
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
-      float s = (acc[b][0] + acc[b][1]) + (acc[b][2] + acc[b][3]);
+      float q4[4], q2[2], q1;
+      const bool k4 = lc & 4, k2 = lc & 2, k1 = lc & 1;
 #pragma unroll
-      for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-      v[b] = round_bf16(s);
+      for (int k = 0; k < 4; ++k) {
+        const float mine = k4 ? p[b][4 + k] : p[b][k], other = k4 ? p[b][k] : p[b][4 + k];
+        q4[k] = mine + __shfl_xor_sync(0xffffffffu, other, 4);
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const float mine = k2 ? q4[2 + k] : q4[k], other = k2 ? q4[k] : q4[2 + k];
+        q2[k] = mine + __shfl_xor_sync(0xffffffffu, other, 2);
+      }
+      {
+        const float mine = k1 ? q2[1] : q2[0], other = k1 ? q2[0] : q2[1];
+        q1 = mine + __shfl_xor_sync(0xffffffffu, other, 1);
+      }
+      q1 += __shfl_xor_sync(0xffffffffu, q1, 8);
+      if (LPR == 32) q1 += __shfl_xor_sync(0xffffffffu, q1, 16);
+      if (lc < 8) red[warp][b][hr * 8 + lc] = q1;
     }
-    if (probe && grp == (int)blockIdx.x) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
+    if (probe && it == 0) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
+    __syncthreads();
+    float v = 0.f;
+    if (tid < RC * NB) {
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[w][eb][er];
+      v = round_bf16(v);
+    }
     if (MODE == kModeNormSwiglu) {
-      // lanes 0-15 hold gate_i, lanes 16-31 hold up_i
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        const float up = __shfl_xor_sync(0xffffffffu, v[b], 16);
-        if (lane == 0 && b < a.rows)
-          a.out[(size_t)b * a.out_stride + grp * kRowWarps + warp] = __float2bfloat16_rn(v[b] / (1.0f + expf(-v[b])) * up);
-      }
-    } else {
-      const int row = grp * RPC + warp * RPW + half;
-      if (lr == 0) {
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          if (b < a.rows) {
-            if (MODE == kModeNormArgmax) {
-              if (a.logits_out) a.logits_out[(size_t)b * a.vocab + row] = v[b];
-              if (v[b] > best_v[b] || (v[b] == best_v[b] && row < best_i[b])) { best_v[b] = v[b]; best_i[b] = row; }
-            } else {
-              a.out[(size_t)b * a.out_stride + row] = __float2bfloat16_rn(v[b]);
-            }
-          }
-        }
+      // rows 0-7 of the group are gate rows, rows 8-15 the matching up rows
+      const float up = __shfl_down_sync(0xffffffffu, v, 8);
+      if (tid < RC * NB && er < 8 && eb < a.rows)
+        a.out[(size_t)eb * a.out_stride + grp * 8 + er] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+    } else if (tid < RC * NB && eb < a.rows) {
+      const int row = grp * RC + er;
+      if (MODE == kModeNormArgmax) {
+        if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + row] = v;
+        if (v > best_v || (v == best_v && row < best_i)) { best_v = v; best_i = row; }
+      } else {
+        a.out[(size_t)eb * a.out_stride + row] = __float2bfloat16_rn(v);
       }
     }
+    if (nxt < n_groups) __syncthreads();   // `red` is reused by the next group
   }
 
   if (MODE == kModeNormArgmax) {
-    // half-warp leaders -> warp -> CTA -> grid (the last CTA to arrive finishes)
+    // threads (b, r) -> one partial per batch row and CTA -> grid (the last CTA to arrive finishes)
+    if (tid < 32) {
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      if (RPW == 2) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best_v[b], 16);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i[b], 16);
-        if (ov > best_v[b] || (ov == best_v[b] && oi < best_i[b])) { best_v[b] = ov; best_i[b] = oi; }
+      for (int m = RC / 2; m >= 1; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best_v, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, m);
+        if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
       }
-      if (lane == 0) { cta_v[warp][b] = best_v[b]; cta_i[warp][b] = best_i[b]; }
-    }
-    __syncthreads();
-    if (tid < NB) {
-      float v = cta_v[0][tid];
-      int i = cta_i[0][tid];
-      for (int w = 1; w < kRowWarps; ++w)
-        if (cta_v[w][tid] > v || (cta_v[w][tid] == v && cta_i[w][tid] < i)) { v = cta_v[w][tid]; i = cta_i[w][tid]; }
-      a.parts[blockIdx.x * kMaxRows + tid] = ArgmaxPart{v, i};
+      if (tid < RC * NB && er == 0) a.parts[blockIdx.x * kMaxRows + eb] = ArgmaxPart{best_v, best_i};
     }
     __threadfence();
     __syncthreads();
@@ -216,11 +230,11 @@ __global__ void __launch_bounds__(kRowThreads, 3) row_gemv_kernel(const GemvArgs
     __syncthreads();
     if (last_flag) {
       __threadfence();
-      for (int b = warp; b < a.rows; b += kRowWarps) {
+      for (int b = warp; b < a.rows; b += W) {
         float v = -INFINITY;
         int i = 0x7fffffff;
-        for (int c2 = lane; c2 < (int)gridDim.x; c2 += 32) {
-          const int2 raw = __ldcg(reinterpret_cast<const int2*>(a.parts + c2 * kMaxRows + b));
+        for (int c3 = lane; c3 < (int)gridDim.x; c3 += 32) {
+          const int2 raw = __ldcg(reinterpret_cast<const int2*>(a.parts + c3 * kMaxRows + b));
           const float pv = __int_as_float(raw.x);
           if (pv > v || (pv == v && raw.y < i)) { v = pv; i = raw.y; }
         }

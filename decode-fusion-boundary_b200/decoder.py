@@ -67,7 +67,7 @@ class StreamDecoder:
     def __init__(self, weights, k_cache, v_cache, block_size: int, num_cache_blocks: int,
                  max_model_len: int = 2048, attn_splits: int = 1, fusion_groups: int = 1,
                  verbose: bool = False, debug_bounds: bool = False, use_graph: bool = True,
-                 use_pdl: bool = True, persistent: bool = True):
+                 use_pdl: bool = True, persistent: bool = False):
         import torch
 
         from . import native

@@ -4,13 +4,14 @@
 Every kernel of the library is an ordinary launch, so Nsight Compute can
 capture any of them from this driver, e.g. (one GPU, small case):
 
-    python decode-fusion-boundary_b200/profile_step.py --layers 4 --vocab 32768 --steps 4
-    ncu --set full --clock-control none -k regex:decode_step_persistent -s 2 -c 1 \\
-        -o prof python decode-fusion-boundary_b200/profile_step.py --layers 4 --vocab 32768 --steps 4
+    python decode-fusion-boundary_b200/profile_step.py --layers 1 --lmhead-only 4
+    ncu --set full --clock-control none -k regex:row_gemv_kernel -s 1 -c 2 \\
+        -o prof python decode-fusion-boundary_b200/profile_step.py --layers 1 --lmhead-only 4
 
-``--mode chained`` runs the step as the chain of per-op kernels
-(``stream_gemv_kernel`` / ``paged_attention_kernel``), ``--no-graph`` launches
-them directly instead of replaying a CUDA graph.  Weights are seeded random
+``--mode chained`` (default) runs the step as the chain of per-op kernels
+(``row_gemv_kernel`` for one or two rows, ``stream_gemv_kernel`` above that,
+``paged_attention_kernel``), ``--mode persistent`` as the single persistent
+kernel; ``--no-graph`` launches directly instead of replaying a CUDA graph.  Weights are seeded random
 values; the KV history is random; nothing here checks results (the tests do).
 """
 
@@ -30,7 +31,9 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=1, help="context length before the first step")
     ap.add_argument("--steps", type=int, default=4)
-    ap.add_argument("--mode", choices=["persistent", "chained"], default="persistent")
+    ap.add_argument("--mode", choices=["persistent", "chained"], default="chained")
+    ap.add_argument("--lmhead-only", type=int, default=0, metavar="N",
+                    help="instead of whole steps, launch the standalone LM-head + argmax kernel N times")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--ctas", type=int, default=0, help="grid of the persistent kernel (0 = one per SM)")
     args = ap.parse_args()
@@ -53,6 +56,17 @@ def main() -> None:
         dec.set_option(native.DFB_OPT_PERSIST_CTAS, args.ctas)
     tables = torch.tensor([list(range(r * pages, (r + 1) * pages)) for r in range(B)], dtype=torch.int32, device="cuda")
     ids = torch.randint(0, g.vocab, (B,), dtype=torch.int64, device="cuda")
+    if args.lmhead_only:
+        hid = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
+        res = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(args.lmhead_only):
+            native.check(native.lib().dfb_launch_lmhead_argmax(dec._handle, hid.data_ptr(), res.data_ptr(), None, None,
+                                                               B, stream), "dfb_launch_lmhead_argmax")
+        torch.cuda.synchronize()
+        print(f"lm head launches={args.lmhead_only} rows={B} vocab={g.vocab}")
+        dec.close()
+        return
     for s in range(args.steps):
         ctx = args.prompt + s
         pos = torch.full((B,), ctx - 1, dtype=torch.int64, device="cuda")

@@ -108,7 +108,7 @@ typedef struct DfbStatus {
 #define DFB_OPT_USE_GRAPH 1   /* 1 (default): replay a captured CUDA graph per (rows, split bucket) */
 #define DFB_OPT_USE_PDL 2     /* 1 (default): chain kernels with programmatic dependent launch */
 #define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
-#define DFB_OPT_STEP_MODE 5   /* 1 (default): the step is one persistent kernel; 0: a chain of per-op kernels */
+#define DFB_OPT_STEP_MODE 5   /* 0 (default): the step is a chain of per-op kernels; 1: one persistent kernel */
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
 #define DFB_OPT_ROW_GEMV 7    /* 1 (default): one- and two-row batches use the FP32 row-parallel GEMV kernels
                                  in the kernel chain; 0: always the tensor-core kernels (process-wide) */

@@ -72,7 +72,7 @@ def token_gap_ok(oracle_logits: torch.Tensor, got: int, want: int, atol=TOKEN_GA
 
 def run_parity_case(layers=2, vocab=4096, prompt_lens=(3, 70, 250), steps=4, seed=3, norm="random",
                     block_permutation=None, use_graph=True, use_pdl=True, host_path=False, max_pos=2048,
-                    check_kv=True, persistent=True):
+                    check_kv=True, persistent=False):
     """Prefill by the oracle, then ``steps`` teacher-forced decode steps on both
     sides; returns the worst differences seen."""
     g = oracle_geometry(layers=layers, vocab=vocab, max_pos=max_pos)

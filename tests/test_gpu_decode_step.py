@@ -22,8 +22,8 @@ def _check(report):
 @pytest.mark.parametrize("persistent", [True, False])
 @pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_step_matches_oracle_for_every_batch_size(cuda_device, rows, persistent):
-    """Both step implementations: the persistent kernel (default) and the chain
-    of per-op kernels."""
+    """Both step implementations: the chain of per-op kernels (default) and the
+    persistent kernel."""
     lens = [3, 70, 250, 129, 64, 1, 300, 17][:rows]
     r = H.run_parity_case(layers=2, vocab=4096, prompt_lens=lens, steps=3, seed=rows, persistent=persistent)
     _check(r)
@@ -92,7 +92,7 @@ def test_persistent_kernel_with_fewer_ctas(cuda_device, ctas):
     res = []
     for n in (0, ctas):
         kvg = kv.cuda()
-        dec = H.make_decoder(w, kvg)
+        dec = H.make_decoder(w, kvg, persistent=True)
         dec.set_option(native.DFB_OPT_PERSIST_CTAS, n)
         logits = torch.zeros(2, g.vocab, device="cuda")
         dec.enqueue_rows(torch.tensor(first, device="cuda"), torch.tensor(lens, device="cuda"),

@@ -136,12 +136,16 @@ def test_full_size_properties_batch8_long_context(full):
         p = ctx[r] - 1
         want[tables[r][p // g.block_size], p % g.block_size] = True
     assert torch.equal(changed, want)
-    # rows one at a time
+    # rows one at a time (single rows run on the FP32 pipe, the batch of 8 on the
+    # tensor cores: agreement to bf16 rounding, same KV slot written)
     for r in (0, 3, 7):
         kv.copy_(kv0)
         dec.enqueue_rows(ids[r:r + 1], pos[r:r + 1], bt[r:r + 1].contiguous(), out_logits=lb)
         torch.cuda.synchronize()
-        assert torch.equal(lb[0], la[r])
+        assert float((lb[0] - la[r]).abs().max()) <= H.LOGIT_ATOL
+        p = ctx[r] - 1
+        blk, off = tables[r][p // g.block_size], p % g.block_size
+        assert float((kv[:, :, blk, off].float() - kv_after[:, :, blk, off].float()).abs().max()) <= 2.0 ** -4
     code, st = dec.status()
     assert code == 0
     dec.close()
