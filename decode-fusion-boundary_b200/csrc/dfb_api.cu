@@ -637,4 +637,60 @@ int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* re
   return launch_lmhead(L, h, (const bf16*)hidden_in, (const bf16*)residual, rows, out_tokens, out_logits);
 }
 
+// ---- LM head + argmax without any allocation -----------------------------------
+// The per-CTA argmax partials, the arrival ticket and the result live in this
+// fixed array instead of a decoder's cudaMalloc'ed slab.  Every device that loads
+// the library holds it (about 66 KB) until the process exits.
+constexpr int kNoAllocMaxCtas = 1024;
+constexpr int kNoAllocMaxVocab = 262144;
+constexpr size_t kNoAllocPartsBytes = sizeof(ArgmaxPart) * kMaxRows * kNoAllocMaxCtas;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartsBytes + 256];
+
+int dfb_lmhead_argmax_noalloc(const void* embed, const void* final_norm, const void* hidden_in, const void* residual,
+                              int32_t rows, int32_t hidden, int32_t vocab, float eps, int32_t* out_tokens,
+                              float* out_logits, dfb_stream_t stream_) {
+  if (!embed || !final_norm || !hidden_in || !residual || !out_tokens) return DFB_E_BAD_ARG;
+  if (rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
+  if (hidden != 1024 || vocab < 16 || vocab % 16) return DFB_E_GEOMETRY;
+  if (vocab > kNoAllocMaxVocab) return DFB_E_TOO_LARGE;
+  // One-time set-up per device, with that device current: in host code the array's
+  // name is only a stand-in, the kernel needs the address the runtime reports.
+  static unsigned char* scratch_of_device[64] = {};
+  int dev = 0;
+  DFB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return DFB_E_TOO_LARGE;
+  if (!scratch_of_device[dev]) {
+    void* p = nullptr;
+    DFB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (!p) return (int)cudaErrorInvalidSymbol;
+    scratch_of_device[dev] = (unsigned char*)p;
+  }
+  unsigned char* scratch = scratch_of_device[dev];
+  cudaStream_t stream = (cudaStream_t)stream_;
+  unsigned int* ticket = (unsigned int*)(scratch + kNoAllocPartsBytes);
+  int* tokens = (int*)(scratch + kNoAllocPartsBytes + 64);
+  // the array keeps the previous call's contents: the ticket must start at zero
+  DFB_CUDA(cudaMemsetAsync(ticket, 0, sizeof(unsigned int), stream));
+  GemvArgs a = {};
+  a.w = (const bf16*)embed; a.rows = rows; a.k = hidden;
+  a.x = (const bf16*)hidden_in; a.res_in = (const bf16*)residual; a.norm_w = (const bf16*)final_norm; a.eps = eps;
+  a.logits_out = out_logits; a.vocab = vocab;
+  a.parts = (ArgmaxPart*)scratch; a.ticket = ticket; a.tokens = tokens; a.tokens_out = out_tokens;
+  Launcher L{stream, false};
+  if (rows <= 2) {
+    a.n_tiles = vocab / 16;
+    int grid = 3 * sm_count_cached();
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    if (grid > kNoAllocMaxCtas) grid = kNoAllocMaxCtas;
+    launch_row<1024, kModeNormArgmax>(L, a, rows, grid, false);
+  } else {
+    a.n_tiles = vocab / kTileRows;
+    int grid = sm_count_cached();
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    if (grid > kNoAllocMaxCtas) grid = kNoAllocMaxCtas;
+    launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid, false);
+  }
+  return L.err;
+}
+
 }  // extern "C"

@@ -33,6 +33,7 @@ EXPORTS = (
     "dfb_create", "dfb_destroy", "dfb_set_option", "dfb_decode_step", "dfb_decode_step_host",
     "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
+    "dfb_lmhead_argmax_noalloc",
 )
 
 
@@ -120,6 +121,7 @@ def lib() -> C.CDLL:
     L.dfb_launch_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     L.dfb_launch_rmsnorm_gateup_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
     L.dfb_launch_lmhead_argmax.argtypes = [vp, vp, vp, vp, vp, i32, vp]
+    L.dfb_lmhead_argmax_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, f32, vp, vp, vp]
     for name in EXPORTS:
         if name not in ("dfb_destroy", "dfb_error_string"):
             getattr(L, name).restype = C.c_int

@@ -179,6 +179,31 @@ int dfb_launch_rmsnorm_gateup_swiglu(const void* h, const void* residual, void* 
 int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,
                              float* out_logits, int32_t rows, dfb_stream_t stream);
 
+/* Final add+RMSNorm, tied LM head and greedy argmax WITHOUT any allocation.
+ * (No counterpart in the reference: its LM head always runs inside a decoder
+ * that allocated its scratch at start-up.)
+ *
+ * Who needs it: a caller that may not call cudaMalloc at the point where it wants
+ * the next token -- an engine that handed almost all free device memory to its
+ * KV cache at start-up (nano-vLLM sizes the cache from gpu_memory_utilization),
+ * so a later allocation can fail; a caller inside a region where its own policy
+ * forbids allocation after warm-up; or one that has no DfbHandle at all.  The
+ * scratch this kernel needs (one argmax partial per CTA and batch row, an arrival
+ * ticket, the result) lives in a fixed array inside the library instead: about
+ * 66 KB on every device that loads the library, held until the process exits.
+ *
+ * Limits: rows 1..DFB_MAX_ROWS, hidden 1024, vocab a multiple of 16 and at most
+ * 262,144 (DFB_E_TOO_LARGE beyond that), at most 1024 CTAs.  `out_logits` may be
+ * NULL.  The first call on a device looks up the array's device address (once per
+ * device, with that device current); make that first call before any stream
+ * capture.  All calls share the one array and it keeps the last call's contents
+ * (the ticket is cleared on `stream` at every call), so two calls whose kernels
+ * overlap on the GPU race: keep them on one stream or order them yourself.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int dfb_lmhead_argmax_noalloc(const void* embed, const void* final_norm, const void* hidden_in, const void* residual,
+                              int32_t rows, int32_t hidden, int32_t vocab, float eps, int32_t* out_tokens,
+                              float* out_logits, dfb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
