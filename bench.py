@@ -226,7 +226,8 @@ def run_own_arm(args):
     weights = random_init_weights(g, seed=0, norm="ones", device="cuda")
     model, hf = nano_model_view(weights)
     pages = g.max_pages
-    kv = torch.zeros(2, g.layers, B * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv_rows = 8 if args.sweep else B      # the sweep goes up to batch 8
+    kv = torch.zeros(2, g.layers, kv_rows * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
     if P > 1:
         kv.normal_(0, 1)  # a random KV history stands in for the prefill of the prompt
     tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
@@ -320,8 +321,13 @@ def run_own_arm(args):
         line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": f"{done} decode steps of the same workload ({dt:.1f} s) by the fp32 CPU "
                                           "oracle, a port of the reference torch path"}
+    if args.torch_arm and world == 1:
+        try:
+            line["torch_cudagraph"] = torch_cudagraph_arm(weights, g, B, P, W, K)
+        except Exception as exc:   # the comparison arm must never break the bench line
+            line["torch_cudagraph"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     if args.sweep and world == 1:
-        line["sweep"] = sweep(dec, torch, g, peak)
+        line["sweep"] = sweep(dec, torch, g, peak, weights if args.torch_arm else None)
     if rank == 0:
         print(json.dumps(line), flush=True)
     dec.close()
@@ -329,7 +335,140 @@ def run_own_arm(args):
         _DIST.destroy_process_group()
 
 
-def sweep(dec, torch, g, peak):
+def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=True):
+    """The reference's torch decode path restated on torch / cuBLAS ops, the way its
+    CUDA-graph arm runs it (engine/model_runner.py:292-313,379-416: the graph covers
+    the 28 layers, the LM head GEMM and the greedy sampler run outside it), on the
+    same weights and workload.  A comparison arm only: it uses library kernels
+    (cuBLAS, FlashAttention if it runs on this GPU, else SDPA) and is not part of
+    the backend.  Returns a dict with the device us/step."""
+    import torch
+    import torch.nn.functional as F
+
+    B, dev, bs = batch, "cuda", g.block_size
+    eps, scale = g.eps, g.head_dim ** -0.5
+    pages = g.max_pages
+    kv = torch.zeros(2, g.layers, B * pages, bs, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device=dev)
+    if prompt > 1:
+        kv.normal_(0, 1)
+    cos_sin = weights.cos_sin
+
+    def rms(x, w):
+        xf = x.float()
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        return xf.to(x.dtype) * w
+
+    def add_rms(x, res, w):
+        xf = x.float() + res.float()
+        res = xf.to(x.dtype)
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        return xf.to(x.dtype) * w, res
+
+    def rope(positions, q, k):
+        cs = cos_sin[positions].unsqueeze(1)
+        cos, sin = cs.chunk(2, dim=-1)
+
+        def rot(x):
+            x1, x2 = torch.chunk(x.float(), 2, dim=-1)
+            return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+        return rot(q), rot(k)
+
+    def silu_mul(x):
+        a, b = x.chunk(2, -1)
+        return F.silu(a) * b
+
+    compiled = False
+    if use_compile:
+        try:
+            rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (rms, add_rms, rope, silu_mul))
+            compiled = True
+        except Exception:
+            compiled = False
+    attention = "flash_attn_with_kvcache"
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except Exception:
+        flash_attn_with_kvcache, attention = None, "sdpa"
+
+    st = dict(ids=torch.zeros(B, dtype=torch.int64, device=dev), pos=torch.zeros(B, dtype=torch.int64, device=dev),
+              slots=torch.zeros(B, dtype=torch.int64, device=dev), lens=torch.zeros(B, dtype=torch.int32, device=dev),
+              bt=torch.tensor([list(range(r * pages, (r + 1) * pages)) for r in range(B)], dtype=torch.int32, device=dev))
+
+    def attn(q, k, v, layer):
+        kc, vc = kv[0, layer], kv[1, layer]
+        D = g.kv_heads * g.head_dim
+        kc.view(-1, D).index_copy_(0, st["slots"], k.reshape(B, D))
+        vc.view(-1, D).index_copy_(0, st["slots"], v.reshape(B, D))
+        if attention == "flash_attn_with_kvcache":
+            return flash_attn_with_kvcache(q.unsqueeze(1), kc, vc, cache_seqlens=st["lens"], block_table=st["bt"],
+                                           softmax_scale=scale, causal=True).reshape(B, -1)
+        kk = kc[st["bt"].long()].reshape(B, pages * bs, g.kv_heads, g.head_dim).transpose(1, 2)
+        vv = vc[st["bt"].long()].reshape(B, pages * bs, g.kv_heads, g.head_dim).transpose(1, 2)
+        mask = (torch.arange(pages * bs, device=dev)[None, :] < st["lens"][:, None])[:, None, None, :]
+        o = F.scaled_dot_product_attention(q.unsqueeze(2), kk, vv, attn_mask=mask, scale=scale, enable_gqa=True)
+        return o.reshape(B, -1)
+
+    def model():
+        h = F.embedding(st["ids"], weights.embed)
+        res = None
+        for li, lw in enumerate(weights.layers):
+            if res is None:
+                x, res = rms(h, lw.ln_in), h
+            else:
+                x, res = add_rms(h, res, lw.ln_in)
+            qkv = F.linear(x, lw.wqkv)
+            q, k, v = qkv.split([g.q_size, g.kv_size, g.kv_size], dim=-1)
+            q = rms(q.reshape(B, g.q_heads, g.head_dim), lw.q_norm)
+            k = rms(k.reshape(B, g.kv_heads, g.head_dim), lw.k_norm)
+            q, k = rope(st["pos"], q, k)
+            o = attn(q, k, v.reshape(B, g.kv_heads, g.head_dim), li)
+            h = F.linear(o, lw.wo)
+            x, res = add_rms(h, res, lw.ln_post)
+            h = F.linear(silu_mul(F.linear(x, lw.wgu)), lw.wd)
+        x, _ = add_rms(h, res, weights.final_norm)
+        return x
+
+    def set_step(ctx):           # staging copies of the step's inputs, as prepare_decode does
+        st["pos"].fill_(ctx - 1)
+        st["lens"].fill_(ctx)
+        blk, off = (ctx - 1) // bs, (ctx - 1) % bs
+        st["slots"].copy_(st["bt"][:, blk].long() * bs + off)
+
+    with torch.inference_mode():
+        set_step(prompt)
+        try:
+            for _ in range(3):
+                model()
+        except Exception as exc:
+            if attention != "sdpa":
+                attention, flash_attn_with_kvcache = "sdpa", None
+                for _ in range(3):
+                    model()
+            else:
+                return {"unavailable": f"torch arm failed: {type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            hidden = model()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for s in range(warmup + steps):
+            if s == warmup:
+                torch.cuda.synchronize()
+                e0.record()
+            set_step(prompt + s)
+            graph.replay()
+            logits = F.linear(hidden, weights.embed)
+            st["ids"].copy_(logits.float().argmax(-1))
+        e1.record()
+        torch.cuda.synchronize()
+    us = 1e3 * e0.elapsed_time(e1) / steps
+    return {"device_us_per_step": us, "tok_s": B * 1e6 / us, "attention": attention, "compiled_elementwise": compiled,
+            "what": "restatement of the reference torch decode path (CUDA graph over the layers; LM head GEMM, argmax and "
+                    "input staging outside it) on torch / cuBLAS / FlashAttention library kernels, same weights and "
+                    "workload; the reference package itself is not present on the GPU box"}
+
+
+def sweep(dec, torch, g, peak, torch_arm_weights=None):
     """Extra device-time points: batch 1/2/4/8 at context 512..639 and batch 8 at
     mixed long contexts (not part of the headline line)."""
     out = []
@@ -343,8 +482,17 @@ def sweep(dec, torch, g, peak):
         ctx = [P + 8 + 59.5] * B
         by = g.step_bytes(ctx)
         us = 1e3 * ms / 120
-        out.append({"batch": B, "prompt": P, "device_us_per_step": us, "tok_s": B * 120 / (ms / 1e3),
-                    "floor_us": by / (peak * 1e3), "frac_of_floor": by / (peak * 1e3) / us})
+        entry = {"batch": B, "prompt": P, "device_us_per_step": us, "tok_s": B * 120 / (ms / 1e3),
+                 "floor_us": by / (peak * 1e3), "frac_of_floor": by / (peak * 1e3) / us}
+        if torch_arm_weights is not None:
+            try:
+                t = torch_cudagraph_arm(torch_arm_weights, g, B, P, 8, 120)
+                entry["torch_cudagraph_us_per_step"] = t.get("device_us_per_step")
+                entry["torch_attention"] = t.get("attention", t.get("unavailable"))
+            except Exception as exc:
+                entry["torch_cudagraph_us_per_step"] = None
+                entry["torch_attention"] = f"{type(exc).__name__}: {exc}"[:120]
+        out.append(entry)
     return out
 
 
@@ -357,6 +505,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=1)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--torch-arm", action="store_true",
+                    help="also time a torch / cuBLAS / CUDA-graph restatement of the reference decode path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
