@@ -167,13 +167,27 @@ void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
 }
 
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
+template <int K, int NB, int MODE>
+void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
+  static bool configured = false;
+  constexpr int smem = row_smem_bytes<K, NB>();
+  auto kernel = row_gemv_kernel<K, NB, MODE>;
+  if (!configured && smem > 32 * 1024) {   // static + dynamic shared memory beyond 48 KB needs the opt-in
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { L.err = (int)e; return; }
+  }
+  configured = true;
+  L.launch(kernel, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl, smem);
+}
 template <int K, int MODE>
 void launch_row(Launcher& L, GemvArgs& a, int rows, int grid, bool allow_pdl = true) {
   a.trace = L.next_trace();
-  if (rows == 1) L.launch(row_gemv_kernel<K, 1, MODE>, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl);
-  else L.launch(row_gemv_kernel<K, 2, MODE>, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl);
+  if (rows == 1) launch_row_nb<K, 1, MODE>(L, a, grid, allow_pdl);
+  else if (rows == 2) launch_row_nb<K, 2, MODE>(L, a, grid, allow_pdl);
+  else if (rows <= 4) launch_row_nb<K, 4, MODE>(L, a, grid, allow_pdl);
+  else launch_row_nb<K, 8, MODE>(L, a, grid, allow_pdl);
 }
-bool g_row_path = true;   // DFB_OPT_ROW_GEMV: use the FP32 path for rows <= 2
+int g_row_max_rows = 2;   // DFB_OPT_ROW_GEMV: largest batch that takes the FP32 kernels (0 = never)
 
 int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_in, bf16* res_out, const bf16* ln_w,
                     const bf16* w, bf16* out, int rows, int hidden, int n, float eps, int* status, bool allow_pdl) {
@@ -182,7 +196,7 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = hidden;
   a.x = x; a.ids = ids; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = out; a.out_stride = n; a.status = status;
-  if (g_row_path && rows <= 2 && n % 16 == 0) {
+  if (rows <= g_row_max_rows && n % 16 == 0) {
     a.n_tiles = n / 16;
     launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
     return L.err;
@@ -196,7 +210,7 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
   GemvArgs a = {};
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = k; a.x = x; a.out = out; a.out_stride = n;
   a.status = status;
-  if (g_row_path && rows <= 2 && (k == 2048 || k == 3072)) {
+  if (rows <= g_row_max_rows && (k == 2048 || k == 3072)) {
     a.n_tiles = n / 8;
     if (k == 2048) launch_row<2048, kModeStore>(L, a, rows, a.n_tiles);
     else launch_row<3072, kModeStore>(L, a, rows, a.n_tiles);
@@ -219,7 +233,7 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   a.w = wgu; a.n_tiles = inter / 4; a.rows = rows; a.k = hidden;
   a.x = h; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
-  if (g_row_path && rows <= 2 && inter % 8 == 0) {
+  if (rows <= g_row_max_rows && inter % 8 == 0) {
     a.n_tiles = inter / 8;
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
@@ -236,7 +250,7 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   a.x = hid; a.res_in = res_in; a.norm_w = (const bf16*)m.final_norm; a.eps = m.eps;
   a.logits_out = logits_out; a.vocab = m.vocab; a.status = h->status;
   a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens; a.tokens_out = tokens_out;
-  if (g_row_path && rows <= 2 && m.vocab % 16 == 0) {
+  if (rows <= g_row_max_rows && m.vocab % 16 == 0) {
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
@@ -470,7 +484,8 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
     case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
     case DFB_OPT_ROW_GEMV:
-      g_row_path = value != 0;
+      if (value < 0 || value > kMaxRows) return DFB_E_BAD_ARG;
+      g_row_max_rows = value;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int p = start + pg + 8 * i;
-    if (p < end && p != pos) {
+    if (start + 8 * i < end && p < end && p != pos) {
       kreg[i] = ldg_stream(a.k_cache + base + (size_t)(pg + 8 * i) * tok_stride);
       vreg[i] = ldg_stream(a.v_cache + base + (size_t)(pg + 8 * i) * tok_stride);
     } else {
@@ -560,6 +560,11 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
+    if (start + 8 * i >= end) {   // no position of this iteration exists (same for every thread of the CTA)
+      s0[i] = -INFINITY;
+      s1[i] = -INFINITY;
+      continue;
+    }
     float kf[8];
     unpack8(kreg[i], kf);
     float d0 = 0.f, d1 = 0.f;
@@ -588,6 +593,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   for (int e = 0; e < 8; ++e) { o0[e] = 0.f; o1[e] = 0.f; }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
+    if (start + 8 * i >= end) continue;
     const float p0 = exp2f((s0[i] - m0) * kLog2e);  // -inf -> 0
     const float p1 = exp2f((s1[i] - m1) * kLog2e);
     l0 += p0;

@@ -1,8 +1,8 @@
-// Weight-streaming GEMV for one or two batch rows on the FP32 pipe.
+// Weight-streaming GEMV for up to eight batch rows on the FP32 pipe.
 //
 // mma.sync issues only about one m16n8k16 per 38 cycles per SM sub-partition on
-// this part, and a batch of one or two rows wastes most of each MMA anyway, so
-// for rows <= 2 every projection runs on the FP32 pipe:
+// this part, and a small batch wastes most of each MMA anyway, so the
+// projections run on the FP32 pipe:
 //   * a CTA owns RC consecutive weight rows (16 at K = 1024, 8 at K = 2048 and
 //     3072) and its warps split K: warp w owns columns [w*S, (w+1)*S) with
 //     S = 128 or 256, so a lane needs only 8 values of x per batch row, kept in
@@ -22,7 +22,9 @@ namespace dfb {
 
 template <int K>
 struct RowCfg {
-  static constexpr int kWarps = K == 3072 ? 12 : 8;
+  // K <= 1536: one warp per 128 columns (also the tensor-parallel shards 256 ... 1536);
+  // K = 2048 / 3072: 8 / 12 warps of 256 columns
+  static constexpr int kWarps = K <= 1536 ? K / 128 : (K == 3072 ? 12 : 8);
   static constexpr int kSlice = K / kWarps;            // columns per warp: 128 or 256
   static constexpr int kLanesPerRow = kSlice / 8;      // 16 or 32 lanes cover the slice
   static constexpr int kHalves = 32 / kLanesPerRow;    // row halves handled side by side: 2 or 1
@@ -30,8 +32,12 @@ struct RowCfg {
   static constexpr int kThreads = kWarps * 32;
 };
 
+template <int K, int NB>
+constexpr int row_smem_bytes() { return NB * K * 4; }   // fp32 copy of x, dynamic shared memory
+
 template <int K, int NB, int MODE>
-__global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(RowCfg<K>::kThreads, (K == 3072 || K == 1536 || NB > 2) ? 2 : 3)
+row_gemv_kernel(const GemvArgs a) {
   using C = RowCfg<K>;
   constexpr bool kNorm = MODE != kModeStore;
   constexpr int W = C::kWarps, LPR = C::kLanesPerRow, RC = C::kRows;
@@ -39,7 +45,8 @@ __global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_ge
   pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
-  __shared__ __align__(16) float xs[NB][K];
+  extern __shared__ __align__(16) float xs_dyn[];
+  float (*xs)[K] = reinterpret_cast<float (*)[K]>(xs_dyn);
   __shared__ float ssq[W][NB];
   __shared__ float red[W][NB][RC];
   __shared__ int last_flag;
@@ -127,10 +134,10 @@ __global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_ge
   if (threadIdx.x == 0) trace_max(a.trace, 4);
   if (probe) { c1 = clock64(); a.trace[5] = (unsigned long long)(c1 - c0); }
 
-  // this lane's 8 values of x per batch row
-  float xr[NB][8];
+  // this lane's 8 values of x per batch row (kept in registers for one or two rows)
+  float xr[NB <= 2 ? NB : 1][8];
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
+  for (int b = 0; b < (NB <= 2 ? NB : 0); ++b) {
     const float4 x0 = *reinterpret_cast<const float4*>(&xs[b][col]);
     const float4 x1 = *reinterpret_cast<const float4*>(&xs[b][col + 4]);
     xr[b][0] = x0.x; xr[b][1] = x0.y; xr[b][2] = x0.z; xr[b][3] = x0.w;
@@ -143,50 +150,66 @@ __global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_ge
 
   // ---- row groups of this CTA ----
   for (int it = 0; grp < n_groups; grp += gridDim.x, ++it) {
-    // 8 rows x 8 columns per lane: partial dot products p[b][i]
-    float p[NB][8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float wf[8];
-      unpack8(wreg[i], wf);
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        float s0 = wf[0] * xr[b][0], s1 = wf[1] * xr[b][1];
-        s0 = fmaf(wf[2], xr[b][2], s0); s1 = fmaf(wf[3], xr[b][3], s1);
-        s0 = fmaf(wf[4], xr[b][4], s0); s1 = fmaf(wf[5], xr[b][5], s1);
-        s0 = fmaf(wf[6], xr[b][6], s0); s1 = fmaf(wf[7], xr[b][7], s1);
-        p[b][i] = s0 + s1;
-      }
-    }
-    // request the next group's weights as soon as the registers are free
+    // 8 rows x 8 columns per lane, two batch rows at a time: partial dot products
+    // p[b][i], then a halving butterfly over the lanes of a row half, after which
+    // lane lc holds the sum over the warp's slice for row (lc & 7)
+    constexpr int BP = NB < 2 ? 1 : 2;
     const int nxt = grp + gridDim.x;
-    if (nxt < n_groups) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) wreg[i] = ldg_stream(weight_ptr(nxt, i));
-    }
-    // halving butterfly over the lanes of a row half: afterwards lane lc holds the
-    // sum over the warp's slice for row (lc & 7)
+    for (int b0 = 0; b0 < NB; b0 += BP) {
+      float xv[BP][8];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      float q4[4], q2[2], q1;
-      const bool k4 = lc & 4, k2 = lc & 2, k1 = lc & 1;
+      for (int bb = 0; bb < BP; ++bb) {
+        if (NB <= 2) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float mine = k4 ? p[b][4 + k] : p[b][k], other = k4 ? p[b][k] : p[b][4 + k];
-        q4[k] = mine + __shfl_xor_sync(0xffffffffu, other, 4);
+          for (int e = 0; e < 8; ++e) xv[bb][e] = xr[NB <= 2 ? b0 + bb : 0][e];
+        } else {   // larger batches re-read x from shared memory instead of holding 8 x NB registers
+          const float4 x0 = *reinterpret_cast<const float4*>(&xs[b0 + bb][col]);
+          const float4 x1 = *reinterpret_cast<const float4*>(&xs[b0 + bb][col + 4]);
+          xv[bb][0] = x0.x; xv[bb][1] = x0.y; xv[bb][2] = x0.z; xv[bb][3] = x0.w;
+          xv[bb][4] = x1.x; xv[bb][5] = x1.y; xv[bb][6] = x1.z; xv[bb][7] = x1.w;
+        }
+      }
+      float p[BP][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float wf[8];
+        unpack8(wreg[i], wf);
+#pragma unroll
+        for (int bb = 0; bb < BP; ++bb) {
+          float s0 = wf[0] * xv[bb][0], s1 = wf[1] * xv[bb][1];
+          s0 = fmaf(wf[2], xv[bb][2], s0); s1 = fmaf(wf[3], xv[bb][3], s1);
+          s0 = fmaf(wf[4], xv[bb][4], s0); s1 = fmaf(wf[5], xv[bb][5], s1);
+          s0 = fmaf(wf[6], xv[bb][6], s0); s1 = fmaf(wf[7], xv[bb][7], s1);
+          p[bb][i] = s0 + s1;
+        }
+      }
+      if (b0 + BP >= NB && nxt < n_groups) {   // the weight registers are free: request the next group's
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wreg[i] = ldg_stream(weight_ptr(nxt, i));
       }
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const float mine = k2 ? q4[2 + k] : q4[k], other = k2 ? q4[k] : q4[2 + k];
-        q2[k] = mine + __shfl_xor_sync(0xffffffffu, other, 2);
+      for (int bb = 0; bb < BP; ++bb) {
+        float q4[4], q2[2], q1;
+        const bool k4 = lc & 4, k2 = lc & 2, k1 = lc & 1;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float mine = k4 ? p[bb][4 + k] : p[bb][k], other = k4 ? p[bb][k] : p[bb][4 + k];
+          q4[k] = mine + __shfl_xor_sync(0xffffffffu, other, 4);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const float mine = k2 ? q4[2 + k] : q4[k], other = k2 ? q4[k] : q4[2 + k];
+          q2[k] = mine + __shfl_xor_sync(0xffffffffu, other, 2);
+        }
+        {
+          const float mine = k1 ? q2[1] : q2[0], other = k1 ? q2[0] : q2[1];
+          q1 = mine + __shfl_xor_sync(0xffffffffu, other, 1);
+        }
+        q1 += __shfl_xor_sync(0xffffffffu, q1, 8);
+        if (LPR == 32) q1 += __shfl_xor_sync(0xffffffffu, q1, 16);
+        if (lc < 8) red[warp][b0 + bb][hr * 8 + lc] = q1;
       }
-      {
-        const float mine = k1 ? q2[1] : q2[0], other = k1 ? q2[0] : q2[1];
-        q1 = mine + __shfl_xor_sync(0xffffffffu, other, 1);
-      }
-      q1 += __shfl_xor_sync(0xffffffffu, q1, 8);
-      if (LPR == 32) q1 += __shfl_xor_sync(0xffffffffu, q1, 16);
-      if (lc < 8) red[warp][b][hr * 8 + lc] = q1;
     }
     if (probe && it == 0) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
     __syncthreads();
@@ -215,7 +238,7 @@ __global__ void __launch_bounds__(RowCfg<K>::kThreads, K == 3072 ? 2 : 3) row_ge
 
   if (MODE == kModeNormArgmax) {
     // threads (b, r) -> one partial per batch row and CTA -> grid (the last CTA to arrive finishes)
-    if (tid < 32) {
+    if (tid < 128) {
 #pragma unroll
       for (int m = RC / 2; m >= 1; m >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best_v, m);

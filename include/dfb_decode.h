@@ -110,8 +110,8 @@ typedef struct DfbStatus {
 #define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
 #define DFB_OPT_STEP_MODE 5   /* 0 (default): the step is a chain of per-op kernels; 1: one persistent kernel */
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
-#define DFB_OPT_ROW_GEMV 7    /* 1 (default): one- and two-row batches use the FP32 row-parallel GEMV kernels
-                                 in the kernel chain; 0: always the tensor-core kernels (process-wide) */
+#define DFB_OPT_ROW_GEMV 7    /* largest batch (0..8) that runs the projections on the FP32 GEMV kernels in the
+                                 kernel chain; larger batches use the tensor-core kernels (process-wide) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

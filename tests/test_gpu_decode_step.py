@@ -164,7 +164,7 @@ def test_batch_equals_independent_rows(cuda_device, persistent):
         assert float((kv_a.float() - kv_b.float()).abs().max()) <= 2.0 ** -5
     else:
         assert torch.equal(kv_a, kv_b)
-        dec_a.set_option(native.DFB_OPT_ROW_GEMV, 1)
+        dec_a.set_option(native.DFB_OPT_ROW_GEMV, 2)   # the default: FP32 kernels for one or two rows
     dec_a.close(); dec_b.close()
 
 
