@@ -9,7 +9,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "../../include/dfb_decode.h"
@@ -36,17 +38,41 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
+// Kernels of one chain overlap on an SM (a dependent kernel's CTAs become
+// resident while its predecessor still runs).  An SM changes its split between
+// L1 and shared memory only when it is idle, so every kernel of a chain asks
+// for the same split; otherwise a kernel that prefers another one starts late.
+// `percent` is the share of the SM's 228 KB that goes to shared memory (-1:
+// leave the choice to the driver).
+int g_carve_fp32 = 12;   // chain of FP32 GEMV kernels: little shared memory, L1 helps
+int g_carve_mma = 50;    // chain of tensor-core GEMV kernels: room for the weight stages (up to 101 KB), the rest stays L1
+void prefer_carveout(const void* fn, int percent) {
+  if (percent < 0) return;
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> last;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_pair(dev, fn);
+  auto it = last.find(key);
+  if (it != last.end() && it->second == percent) return;
+  last[key] = percent;
+  cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+}
+
 struct Launcher {
   cudaStream_t stream;
   bool pdl;
   unsigned long long* trace = nullptr;  // base of the timeline buffer or null
   int count = 0;
   int err = 0;
+  int carve = -1;  // preferred shared-memory share of every kernel this launcher launches
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   template <typename Args>
   void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true,
               size_t smem = 0) {
     if (err) return;
+    prefer_carveout((const void*)kernel, carve);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -263,6 +289,8 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   return L.err;
 }
 
+int g_attn_wide_ctas = 2 * 148;  // FP32 chain: attention grids up to this many CTAs use 256-thread CTAs
+
 int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
                      int bt_stride, const int* row_active, bf16* out, int rows, int nsplit) {
   const DfbModelDesc& m = h->m;
@@ -276,7 +304,17 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   a.block_size = m.block_size; a.kv_heads = m.kv_heads; a.num_blocks = m.num_blocks; a.max_pos = m.max_model_len;
   a.out = out; a.part_o = h->part_o; a.part_ml = h->part_ml; a.tickets = h->tickets; a.status = h->status;
   a.trace = L.next_trace();
-  L.launch(paged_attention_kernel, dim3(nsplit, m.kv_heads, rows), dim3(kAttnThreads), a);
+  // The two chains (FP32 / tensor-core GEMV kernels) prefer different shared-memory
+  // splits, so each has its own instantiation of the attention kernel.  With few
+  // CTAs most SMs are idle during attention: 256 threads then halve each thread's
+  // share of the chunk and with it the latency of the CTA.
+  const int ctas = nsplit * m.kv_heads * rows;
+  if (rows <= g_row_max_rows) {
+    if (ctas <= g_attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
+    else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
+  } else {
+    L.launch(paged_attention_kernel<128, 1>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
+  }
   return L.err;
 }
 
@@ -293,6 +331,7 @@ int split_bucket(const DfbHandle* h, int max_context) {
 int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
   const DfbModelDesc& m = h->m;
   Launcher L{stream, h->use_pdl, h->trace_on ? h->trace : nullptr};
+  L.carve = rows <= g_row_max_rows ? g_carve_fp32 : g_carve_mma;
   int rc = 0;
   int cur = 0;  // index of the residual buffer holding the current residual
   for (int l = 0; l < m.layers && !rc; ++l) {
@@ -486,6 +525,24 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_ROW_GEMV:
       if (value < 0 || value > kMaxRows) return DFB_E_BAD_ARG;
       g_row_max_rows = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_SMEM_CARVEOUT:
+      if (value < -1 || value > 100) return DFB_E_BAD_ARG;
+      g_carve_fp32 = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_SMEM_CARVEOUT_MMA:
+      if (value < -1 || value > 100) return DFB_E_BAD_ARG;
+      g_carve_mma = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_ATTN_WIDE:
+      if (value < 0) return DFB_E_BAD_ARG;
+      g_attn_wide_ctas = value;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

@@ -444,11 +444,18 @@ struct AttnArgs {
   unsigned long long* trace;    // optional timeline slot of this launch or null
 };
 
-__global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const AttnArgs a) {
+// CHAIN only separates instantiations: a function's preferred shared-memory split is
+// a property of the function, and the two kernel chains prefer different ones.
+template <int THREADS, int CHAIN>
+__global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs a) {
+  constexpr int PG = THREADS / 16;           // position groups: 16 threads share one position
+  constexpr int ITER = kAttnChunk / PG;      // positions per thread
+  constexpr int J = 2 * kHeadDim / THREADS;  // output elements per thread in the reduction and the merge
+  static_assert(THREADS == 128 || THREADS == 256, "128 or 256 threads");
   pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x;
-  if (tid == 0) trace_min(a.trace, 0);
+  if (tid == 0) { trace_min(a.trace, 0); trace_max(a.trace, 4); }
   int pos = a.positions[row];
   if (pos < 0 || pos >= a.max_pos) {
     // A position outside the RoPE table / block table: record it and carry on
@@ -463,9 +470,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   __shared__ float qs[2][kHeadDim];
   __shared__ __align__(16) __nv_bfloat16 ks[kHeadDim];
   __shared__ __align__(16) __nv_bfloat16 vs[kHeadDim];
-  __shared__ float mred[8][2];
-  __shared__ float lred[8][2];
-  __shared__ float ored[8][2][kHeadDim];
+  __shared__ float mred[PG][2];
+  __shared__ float lred[PG / 2][2];            // per warp: its two position groups are added by shuffle
+  __shared__ __align__(16) float ored[PG / 2][2][kHeadDim];
   __shared__ int last_flag;
 
   const int start = split * kAttnChunk;
@@ -481,17 +488,32 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   const size_t base = ((size_t)block * a.block_size + (start % a.block_size)) * tok_stride + (size_t)kvh * kHeadDim + 8 * l16;
 
   // ---- old KV entries: independent of the previous kernel ----
-  uint4 kreg[8], vreg[8];
+  // Iteration i covers positions start + PG i .. start + PG i + PG - 1; when
+  // none of them exists the whole CTA skips the iteration.
+  uint4 kreg[ITER], vreg[ITER];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int p = start + pg + 8 * i;
-    if (start + 8 * i < end && p < end && p != pos) {
-      kreg[i] = ldg_stream(a.k_cache + base + (size_t)(pg + 8 * i) * tok_stride);
-      vreg[i] = ldg_stream(a.v_cache + base + (size_t)(pg + 8 * i) * tok_stride);
+  for (int i = 0; i < ITER; ++i) {
+    const int p = start + pg + PG * i;
+    if (start + PG * i < end && p < end && p != pos) {
+      kreg[i] = ldg_stream(a.k_cache + base + (size_t)(pg + PG * i) * tok_stride);
+      vreg[i] = ldg_stream(a.v_cache + base + (size_t)(pg + PG * i) * tok_stride);
     } else {
       kreg[i] = make_uint4(0, 0, 0, 0);
       vreg[i] = make_uint4(0, 0, 0, 0);
     }
+  }
+
+  // constants of the new token's norm and rotation: also independent of the predecessor
+  const int warp = tid >> 5, lane = tid & 31;
+  uint32_t wlo = 0, whi = 0;
+  float2 rc = make_float2(0.f, 0.f), rs = make_float2(0.f, 0.f);
+  if (warp < 3) {
+    const __nv_bfloat16* nw = warp < 2 ? a.q_norm : a.k_norm;
+    const float* cs = a.cos_sin + (size_t)pos * kHeadDim;
+    wlo = *reinterpret_cast<const uint32_t*>(nw + 2 * lane);
+    whi = *reinterpret_cast<const uint32_t*>(nw + 2 * lane + 64);
+    rc = *reinterpret_cast<const float2*>(cs + 2 * lane);
+    rs = *reinterpret_cast<const float2*>(cs + 64 + 2 * lane);
   }
 
   pdl_wait();
@@ -499,11 +521,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 
   // ---- new token: q (2 heads) and k get RMSNorm + RoPE, v is copied ----
   {
-    const int warp = tid >> 5, lane = tid & 31;
     const __nv_bfloat16* src = a.qkv + (size_t)row * a.qkv_stride;
     if (warp < 3) {
       const __nv_bfloat16* vec = warp < 2 ? src + (2 * kvh + warp) * kHeadDim : src + a.q_size + kvh * kHeadDim;
-      const __nv_bfloat16* nw = warp < 2 ? a.q_norm : a.k_norm;
       const int d = 2 * lane;  // handles d, d+1 and their RoPE partners d+64, d+65
       const uint32_t lo = __ldcg(reinterpret_cast<const uint32_t*>(vec + d));
       const uint32_t hi = __ldcg(reinterpret_cast<const uint32_t*>(vec + d + 64));
@@ -512,14 +532,10 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 #pragma unroll
       for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
       const float rstd = 1.0f / sqrtf(ss / (float)kHeadDim + a.eps);
-      const uint32_t wlo = *reinterpret_cast<const uint32_t*>(nw + d);
-      const uint32_t whi = *reinterpret_cast<const uint32_t*>(nw + d + 64);
       const float w[4] = {bf_lo(wlo), bf_hi(wlo), bf_lo(whi), bf_hi(whi)};
 #pragma unroll
       for (int e = 0; e < 4; ++e) x[e] = round_bf16(round_bf16(x[e] * rstd) * w[e]);
-      const float* cs = a.cos_sin + (size_t)pos * kHeadDim;
-      const float2 c = *reinterpret_cast<const float2*>(cs + d);
-      const float2 s = *reinterpret_cast<const float2*>(cs + 64 + d);
+      const float2 c = rc, s = rs;
       const float y0 = round_bf16(x[0] * c.x - x[2] * s.x), y1 = round_bf16(x[1] * c.y - x[3] * s.y);
       const float y2 = round_bf16(x[2] * c.x + x[0] * s.x), y3 = round_bf16(x[3] * c.y + x[1] * s.y);
       if (warp < 2) {
@@ -528,7 +544,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
         *reinterpret_cast<uint32_t*>(ks + d) = pack_bf16(y0, y1);
         *reinterpret_cast<uint32_t*>(ks + d + 64) = pack_bf16(y2, y3);
       }
-    } else {
+    } else if (warp == 3) {
       const __nv_bfloat16* vec = src + a.q_size + a.kv_size + kvh * kHeadDim;
       reinterpret_cast<uint2*>(vs)[lane] = __ldcg(reinterpret_cast<const uint2*>(vec) + lane);
     }
@@ -537,12 +553,12 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 
   if (owner) {
     const int pi = pos - start;  // 0..63
-    if ((pi & 7) == pg) {
-      const int i = pi >> 3;
+    if ((pi % PG) == pg) {
+      const int i = pi / PG;
       const uint4 kn = reinterpret_cast<const uint4*>(ks)[l16];
       const uint4 vn = reinterpret_cast<const uint4*>(vs)[l16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < ITER; ++u)
         if (u == i) { kreg[u] = kn; vreg[u] = vn; }
       if (a.row_active == nullptr || a.row_active[row] != 0) {
         const size_t off = base + (size_t)pi * tok_stride;
@@ -556,11 +572,11 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   float q0[8], q1[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) { q0[e] = qs[0][8 * l16 + e]; q1[e] = qs[1][8 * l16 + e]; }
-  float s0[8], s1[8];
+  float s0[ITER], s1[ITER];
   float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (start + 8 * i >= end) {   // no position of this iteration exists (same for every thread of the CTA)
+  for (int i = 0; i < ITER; ++i) {
+    if (start + PG * i >= end) {   // no position of this iteration exists (same for every thread of the CTA)
       s0[i] = -INFINITY;
       s1[i] = -INFINITY;
       continue;
@@ -575,7 +591,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
       d0 += __shfl_xor_sync(0xffffffffu, d0, m);
       d1 += __shfl_xor_sync(0xffffffffu, d1, m);
     }
-    const bool valid = start + pg + 8 * i < end;
+    const bool valid = start + pg + PG * i < end;
     s0[i] = valid ? d0 * a.scale : -INFINITY;
     s1[i] = valid ? d1 * a.scale : -INFINITY;
     m0 = fmaxf(m0, s0[i]);
@@ -583,8 +599,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   }
   if (l16 == 0) { mred[pg][0] = m0; mred[pg][1] = m1; }
   __syncthreads();
+  if (tid == 0) trace_max(a.trace, 5);
 #pragma unroll
-  for (int p = 0; p < 8; ++p) { m0 = fmaxf(m0, mred[p][0]); m1 = fmaxf(m1, mred[p][1]); }
+  for (int p = 0; p < PG; ++p) { m0 = fmaxf(m0, mred[p][0]); m1 = fmaxf(m1, mred[p][1]); }
 
   // ---- softmax numerators and P.V for this thread's positions ----
   constexpr float kLog2e = 1.4426950408889634f;
@@ -592,8 +609,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 #pragma unroll
   for (int e = 0; e < 8; ++e) { o0[e] = 0.f; o1[e] = 0.f; }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (start + 8 * i >= end) continue;
+  for (int i = 0; i < ITER; ++i) {
+    if (start + PG * i >= end) continue;
     const float p0 = exp2f((s0[i] - m0) * kLog2e);  // -inf -> 0
     const float p1 = exp2f((s1[i] - m1) * kLog2e);
     l0 += p0;
@@ -603,20 +620,41 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
 #pragma unroll
     for (int e = 0; e < 8; ++e) { o0[e] += p0 * vf[e]; o1[e] += p1 * vf[e]; }
   }
+  // a warp holds two position groups (lanes 0-15 and 16-31): add them here
 #pragma unroll
-  for (int e = 0; e < 8; ++e) { ored[pg][0][8 * l16 + e] = o0[e]; ored[pg][1][8 * l16 + e] = o1[e]; }
-  if (l16 == 0) { lred[pg][0] = l0; lred[pg][1] = l1; }
+  for (int e = 0; e < 8; ++e) {
+    o0[e] += __shfl_xor_sync(0xffffffffu, o0[e], 16);
+    o1[e] += __shfl_xor_sync(0xffffffffu, o1[e], 16);
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 16);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 16);
+  if (lane < 16) {
+    float4* r0 = reinterpret_cast<float4*>(&ored[warp][0][8 * l16]);
+    float4* r1 = reinterpret_cast<float4*>(&ored[warp][1][8 * l16]);
+    r0[0] = make_float4(o0[0], o0[1], o0[2], o0[3]);
+    r0[1] = make_float4(o0[4], o0[5], o0[6], o0[7]);
+    r1[0] = make_float4(o1[0], o1[1], o1[2], o1[3]);
+    r1[1] = make_float4(o1[4], o1[5], o1[6], o1[7]);
+    if (l16 == 0) { lred[warp][0] = l0; lred[warp][1] = l1; }
+  }
   __syncthreads();
 
-  const int d = tid;  // one head-dim element per thread from here on
-  float O0 = 0.f, O1 = 0.f, L0 = 0.f, L1 = 0.f;
+  // ---- sum over the position groups: element idx = head * 128 + dim ----
+  float O[J], L[J];
 #pragma unroll
-  for (int p = 0; p < 8; ++p) { O0 += ored[p][0][d]; O1 += ored[p][1][d]; L0 += lred[p][0]; L1 += lred[p][1]; }
+  for (int j = 0; j < J; ++j) {
+    const int idx = tid + j * THREADS, h = idx >> 7, d = idx & (kHeadDim - 1);
+    O[j] = 0.f;
+    L[j] = 0.f;
+#pragma unroll
+    for (int p = 0; p < PG / 2; ++p) { O[j] += ored[p][h][d]; L[j] += lred[p][h]; }
+  }
 
+  // the two query heads of this KV head are adjacent in the output row
   __nv_bfloat16* out = a.out + (size_t)row * a.q_size + (size_t)(2 * kvh) * kHeadDim;
   if (nsplits == 1) {
-    out[d] = __float2bfloat16_rn(O0 / L0);
-    out[kHeadDim + d] = __float2bfloat16_rn(O1 / L1);
+#pragma unroll
+    for (int j = 0; j < J; ++j) out[tid + j * THREADS] = __float2bfloat16_rn(O[j] / L[j]);
     if (tid == 0) trace_max(a.trace, 2);
     return;
   }
@@ -624,36 +662,66 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(const Att
   // ---- several splits: publish the partial, the last CTA to arrive merges ----
   const size_t pidx = ((size_t)row * a.kv_heads + kvh) * kMaxSplits;
   float* po = a.part_o + (pidx + split) * 2 * kHeadDim;
-  po[d] = O0;
-  po[kHeadDim + d] = O1;
-  if (tid == 0) { a.part_ml[(pidx + split) * 2] = make_float2(m0, L0); a.part_ml[(pidx + split) * 2 + 1] = make_float2(m1, L1); }
-  __threadfence();
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int idx = tid + j * THREADS;
+    po[idx] = O[j];
+    if ((idx & (kHeadDim - 1)) == 0)  // one thread per head publishes (max, sum)
+      a.part_ml[(pidx + split) * 2 + (idx >> 7)] = make_float2((idx >> 7) ? m1 : m0, L[j]);
+  }
   __syncthreads();
-  if (tid == 0) last_flag = (atomicAdd(a.tickets + row * a.kv_heads + kvh, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
+  if (tid == 0) {
+    __threadfence();  // after the barrier: orders every thread's partial before the ticket
+    last_flag = (atomicAdd(a.tickets + row * a.kv_heads + kvh, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
+    __threadfence();
+    trace_max(a.trace, 6);
+  }
   __syncthreads();
   if (!last_flag) {
     if (tid == 0) trace_max(a.trace, 2);
     return;
   }
-  __threadfence();
-  float M0 = -INFINITY, M1 = -INFINITY;
-  for (int s = 0; s < nsplits; ++s) {
-    M0 = fmaxf(M0, __ldcg(&a.part_ml[(pidx + s) * 2]).x);
-    M1 = fmaxf(M1, __ldcg(&a.part_ml[(pidx + s) * 2 + 1]).x);
+  // Every load of the merge is issued before anything is computed, so that the
+  // merge costs one trip to L2 whatever the number of splits.
+  float pv[J][kMaxSplits];
+  const float* ps = a.part_o + pidx * 2 * kHeadDim;
+#pragma unroll
+  for (int j = 0; j < J; ++j)
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; ++s)
+      pv[j][s] = s < nsplits ? __ldcg(ps + (size_t)s * 2 * kHeadDim + tid + j * THREADS) : 0.f;
+  // `ored` is free again (every thread passed two barriers after reading it).
+  float* msm = &ored[0][0][0];        // [2 * kMaxSplits] partial maxima, index 2 s + head
+  float* lsm = msm + 2 * kMaxSplits;  // [2 * kMaxSplits] weighted partial sums
+  float* wsm = lsm + 2 * kMaxSplits;  // [2 * kMaxSplits] weights
+  if (tid < 2 * nsplits) {
+    const float2 ml = __ldcg(&a.part_ml[pidx * 2 + tid]);
+    msm[tid] = ml.x;
+    lsm[tid] = ml.y;
   }
-  float A0 = 0.f, A1 = 0.f, S0 = 0.f, S1 = 0.f;
-  for (int s = 0; s < nsplits; ++s) {
-    const float2 ml0 = __ldcg(&a.part_ml[(pidx + s) * 2]);
-    const float2 ml1 = __ldcg(&a.part_ml[(pidx + s) * 2 + 1]);
-    const float w0 = exp2f((ml0.x - M0) * kLog2e), w1 = exp2f((ml1.x - M1) * kLog2e);
-    const float* ps = a.part_o + (pidx + s) * 2 * kHeadDim;
-    A0 += w0 * __ldcg(ps + d);
-    A1 += w1 * __ldcg(ps + kHeadDim + d);
-    S0 += w0 * ml0.y;
-    S1 += w1 * ml1.y;
+  __syncthreads();
+  if (tid == 0) trace_max(a.trace, 7);
+  if (tid < 2 * nsplits) {
+    float M = -INFINITY;
+    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, msm[2 * s + (tid & 1)]);
+    const float w = exp2f((msm[tid] - M) * kLog2e);
+    lsm[tid] = w * lsm[tid];  // only this thread touches this entry before the barrier
+    wsm[tid] = w;
   }
-  out[d] = __float2bfloat16_rn(A0 / S0);
-  out[kHeadDim + d] = __float2bfloat16_rn(A1 / S1);
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int idx = tid + j * THREADS, h = idx >> 7;
+    float A = 0.f, S = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; ++s) {
+      if (s < nsplits) {
+        A += wsm[2 * s + h] * pv[j][s];
+        S += lsm[2 * s + h];
+      }
+    }
+    out[idx] = __float2bfloat16_rn(A / S);
+  }
   if (tid == 0) {
     a.tickets[row * a.kv_heads + kvh] = 0u;
     trace_max(a.trace, 2);

@@ -112,6 +112,11 @@ typedef struct DfbStatus {
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
 #define DFB_OPT_ROW_GEMV 7    /* largest batch (0..8) that runs the projections on the FP32 GEMV kernels in the
                                  kernel chain; larger batches use the tensor-core kernels (process-wide) */
+#define DFB_OPT_ATTN_WIDE 8   /* FP32 chain: attention grids of at most this many CTAs run 256-thread CTAs
+                                 instead of 128-thread ones (process-wide; default 296 = two per SM) */
+#define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
+                                        kernels of the FP32 chain ask for as shared memory (process-wide; default 12) */
+#define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chain (default 50) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
