@@ -44,6 +44,7 @@ typedef __nv_bfloat16 bf16;
 // for the same split; otherwise a kernel that prefers another one starts late.
 // `percent` is the share of the SM's 228 KB that goes to shared memory (-1:
 // leave the choice to the driver).
+int g_late_trigger = 0;  // FP32 chain: 1 = a kernel lets its successor start only after it has read its inputs
 int g_carve_fp32 = 12;   // chain of FP32 GEMV kernels: little shared memory, L1 helps
 int g_carve_mma = 50;    // chain of tensor-core GEMV kernels: room for the weight stages (up to 101 KB), the rest stays L1
 void prefer_carveout(const void* fn, int percent) {
@@ -203,7 +204,12 @@ void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
     if (e != cudaSuccess) { L.err = (int)e; return; }
   }
   configured = true;
-  L.launch(kernel, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl, smem);
+  a.late_trigger = g_late_trigger;
+  // The down projection has one CTA per SM's worth of work (128 CTAs): asking for at
+  // least 16 KB keeps two of them off one SM (with the 32 KB split of this chain),
+  // which measured 25 us per step faster at batch 1 than letting them pair up.
+  constexpr int launch_smem = (MODE == kModeStore && K == 3072 && smem < 16 * 1024) ? 16 * 1024 : smem;
+  L.launch(kernel, dim3(grid), dim3(RowCfg<K>::kThreads), a, allow_pdl, launch_smem);
 }
 template <int K, int MODE>
 void launch_row(Launcher& L, GemvArgs& a, int rows, int grid, bool allow_pdl = true) {
@@ -310,6 +316,7 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   // share of the chunk and with it the latency of the CTA.
   const int ctas = nsplit * m.kv_heads * rows;
   if (rows <= g_row_max_rows) {
+    a.late_trigger = g_late_trigger;
     if (ctas <= g_attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
     else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
   } else {
@@ -537,6 +544,12 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
       g_carve_mma = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_LATE_TRIGGER:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      g_late_trigger = value;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

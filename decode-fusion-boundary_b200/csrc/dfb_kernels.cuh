@@ -66,6 +66,7 @@ struct GemvArgs {
   int* tokens_out;               // argmax: optional second copy
   unsigned long long* trace;     // optional timeline slot of this launch (8 words) or null
   int* status;                   // [4] device status word or null
+  int late_trigger;              // 1: let the successor start only after this kernel has read its inputs
 };
 
 // ---------------------------------------------------------------------------
@@ -442,6 +443,7 @@ struct AttnArgs {
   float2* part_ml;              // [rows, kv_heads, kMaxSplits, 2] (max, sum)
   unsigned int* tickets;        // [rows, kv_heads]
   unsigned long long* trace;    // optional timeline slot of this launch or null
+  int late_trigger;             // 1: let the successor start only after this kernel has read its inputs
 };
 
 // CHAIN only separates instantiations: a function's preferred shared-memory split is
@@ -452,7 +454,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
   constexpr int ITER = kAttnChunk / PG;      // positions per thread
   constexpr int J = 2 * kHeadDim / THREADS;  // output elements per thread in the reduction and the merge
   static_assert(THREADS == 128 || THREADS == 256, "128 or 256 threads");
-  pdl_launch_dependents();
+  if (!a.late_trigger) pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x;
   if (tid == 0) { trace_min(a.trace, 0); trace_max(a.trace, 4); }
@@ -550,6 +552,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     }
   }
   __syncthreads();
+  if (a.late_trigger) pdl_launch_dependents();
 
   if (owner) {
     const int pi = pos - start;  // 0..63

@@ -42,7 +42,7 @@ row_gemv_kernel(const GemvArgs a) {
   constexpr bool kNorm = MODE != kModeStore;
   constexpr int W = C::kWarps, LPR = C::kLanesPerRow, RC = C::kRows;
   static_assert(!kNorm || K == 1024, "the fused norm covers the hidden size only");
-  pdl_launch_dependents();
+  if (!a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
   extern __shared__ __align__(16) float xs_dyn[];
@@ -131,6 +131,7 @@ row_gemv_kernel(const GemvArgs a) {
       }
   }
   __syncthreads();
+  if (a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
   if (probe) { c1 = clock64(); a.trace[5] = (unsigned long long)(c1 - c0); }
 

@@ -117,6 +117,8 @@ typedef struct DfbStatus {
 #define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
                                         kernels of the FP32 chain ask for as shared memory (process-wide; default 12) */
 #define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chain (default 50) */
+#define DFB_OPT_LATE_TRIGGER 11 /* FP32 chain: 0 (default) = a kernel lets its successor start (and request its
+                                  weights) at once, 1 = only after it has read its own inputs (process-wide) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
