@@ -68,6 +68,7 @@ struct Launcher {
   int count = 0;
   int err = 0;
   int carve = -1;  // preferred shared-memory share of every kernel this launcher launches
+  bool plain_next = false;  // the next launch follows a foreign kernel (a collective): no programmatic dependency
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   template <typename Args>
   void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true,
@@ -83,7 +84,8 @@ struct Launcher {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (pdl && allow_pdl) ? 1 : 0;
+    cfg.numAttrs = (pdl && allow_pdl && !plain_next) ? 1 : 0;
+    plain_next = false;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) {
       err = (int)e;
@@ -145,6 +147,13 @@ struct DfbHandle {
   int64_t steps = 0;
   int kernels_per_step = 0;
   int last_status[4] = {0, 0, 0, 0};  // last non-zero status word seen by a host-buffer step
+  // tensor parallel
+  DfbTensorParallel tp = {};     // size 0 or 1: single GPU
+  ArgmaxPart* best_local = nullptr;  // [8] this rank's LM-head winners
+  ArgmaxPart* best_all = nullptr;    // [ranks, 8]
+  bool full_geometry = true;     // unsharded Qwen3-0.6B shapes (what the persistent kernel is built for)
+  bool sharded() const { return tp.size > 1; }
+  const bf16* lm_head() const { return (const bf16*)m.embed + (size_t)tp.vocab_offset * m.hidden; }
   int qkv_rows() const { return (m.q_heads + 2 * m.kv_heads) * m.head_dim; }
   int q_size() const { return m.q_heads * m.head_dim; }
   int kv_size() const { return m.kv_heads * m.head_dim; }
@@ -237,19 +246,34 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   return L.err;
 }
 
+// rows of a row group of the FP32 kernel for input width k (RowCfg<K>::kRows)
+int RowRowsFor(int k) { return k <= 1536 ? 16 : 8; }
+
 int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows, int n, int k, int* status) {
   if (n % kTileRows) return DFB_E_GEOMETRY;
   GemvArgs a = {};
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = k; a.x = x; a.out = out; a.out_stride = n;
   a.status = status;
-  if (rows <= g_row_max_rows && (k == 2048 || k == 3072)) {
-    a.n_tiles = n / 8;
-    if (k == 2048) launch_row<2048, kModeStore>(L, a, rows, a.n_tiles);
-    else launch_row<3072, kModeStore>(L, a, rows, a.n_tiles);
+  // The FP32 kernels cover every input width (the full model's 2048 / 3072 and the
+  // tensor-parallel shards 256 ... 1536); the tensor-core kernels 1024, 2048 and 3072.
+  const int mma_loads = (k == 1024 || k == 2048 || k == 3072) ? loads_for_k(k) : 0;
+  if (rows <= g_row_max_rows || mma_loads == 0) {
+    a.n_tiles = n / RowRowsFor(k);
+    switch (k) {
+      case 256: launch_row<256, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 384: launch_row<384, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 512: launch_row<512, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 768: launch_row<768, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 1024: launch_row<1024, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 1536: launch_row<1536, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 2048: launch_row<2048, kModeStore>(L, a, rows, a.n_tiles); break;
+      case 3072: launch_row<3072, kModeStore>(L, a, rows, a.n_tiles); break;
+      default: return DFB_E_GEOMETRY;
+    }
     return L.err;
   }
   const int grid = grid_for(a.n_tiles);
-  switch (loads_for_k(k)) {
+  switch (mma_loads) {
     case 4: launch_gemv<4, 8, 4, kModeStore>(L, a, grid); break;
     case 8: launch_gemv<8, 8, 2, kModeStore>(L, a, grid); break;
     case 12: launch_gemv<12, 8, 2, kModeStore>(L, a, grid); break;
@@ -278,21 +302,42 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
                   float* logits_out) {
   const DfbModelDesc& m = h->m;
   GemvArgs a = {};
-  a.w = (const bf16*)m.embed; a.n_tiles = m.vocab / kTileRows; a.rows = rows; a.k = m.hidden;
+  a.w = h->lm_head(); a.n_tiles = m.vocab / kTileRows; a.rows = rows; a.k = m.hidden;
   a.x = hid; a.res_in = res_in; a.norm_w = (const bf16*)m.final_norm; a.eps = m.eps;
   a.logits_out = logits_out; a.vocab = m.vocab; a.status = h->status;
-  a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens; a.tokens_out = tokens_out;
+  a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens;
+  a.tokens_out = h->sharded() ? nullptr : tokens_out;
+  a.best_out = h->sharded() ? h->best_local : nullptr;
   if (rows <= g_row_max_rows && m.vocab % 16 == 0) {
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
-    return L.err;
+  } else {
+    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid);
   }
-  int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
-  if (grid > a.n_tiles) grid = a.n_tiles;
-  launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid);
+  if (h->sharded() && !L.err) {
+    // every rank collects the winners of all vocabulary shards and picks the same token
+    if (h->tp.all_gather(h->best_local, h->best_all, sizeof(ArgmaxPart) * kMaxRows, h->tp.dtype_int8, h->tp.comm,
+                         (dfb_stream_t)L.stream))
+      return DFB_E_COMM;
+    merge_shard_argmax_kernel<<<1, 32, 0, L.stream>>>(h->best_all, h->tp.size, rows, m.vocab, h->tokens, tokens_out);
+    ++L.count;
+    L.plain_next = true;
+  }
   return L.err;
+}
+
+// Tensor parallel: sum the ranks' partial results of a row-parallel projection in place.
+int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
+  if (!h->sharded() || L.err) return L.err;
+  if (h->tp.all_reduce(buf, buf, (size_t)rows * h->m.hidden, h->tp.dtype_bf16, h->tp.op_sum, h->tp.comm,
+                       (dfb_stream_t)L.stream))
+    return DFB_E_COMM;
+  L.plain_next = true;
+  return 0;
 }
 
 int g_attn_wide_ctas = 2 * 148;  // FP32 chain: attention grids up to this many CTAs use 256-thread CTAs
@@ -357,12 +402,14 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
     rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, h->st_active(), h->attn, rows, nsplit);
     if (rc) break;
     rc = launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status);
+    if (!rc) rc = tp_sum(L, h, h->hbuf, rows);
     if (rc) break;
     rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
                        rows, m.hidden, m.intermediate, m.eps, h->status);
     cur ^= 1;
     if (rc) break;
     rc = launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status);
+    if (!rc) rc = tp_sum(L, h, h->hbuf, rows);
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
   h->kernels_per_step = L.count;
@@ -430,6 +477,7 @@ const char* dfb_error_string(int code) {
     case DFB_E_ABI: return "dfb: ABI version mismatch";
     case DFB_E_DEVICE_STATUS: return "dfb: a kernel reported an error (see dfb_read_status)";
     case DFB_E_TOO_LARGE: return "dfb: request exceeds a fixed capacity";
+    case DFB_E_COMM: return "dfb: a tensor-parallel collective failed";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "dfb: unknown error";
   }
 }
@@ -438,9 +486,12 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   if (!d || !out) return DFB_E_BAD_ARG;
   *out = nullptr;
   if (d->abi_version != DFB_ABI_VERSION) return DFB_E_ABI;
+  // full model: q_size 2048, intermediate 3072; tensor-parallel shards: 1/2, 1/4, 1/8 of both
+  const int q_size = d->q_heads * d->head_dim, inter = d->intermediate;
+  const bool q_ok = q_size == 2048 || q_size == 1024 || q_size == 512 || q_size == 256;
+  const bool i_ok = inter == 3072 || inter == 1536 || inter == 768 || inter == 384;
   if (d->hidden != 1024 || d->head_dim != kHeadDim || d->q_heads != 2 * d->kv_heads || d->kv_heads < 1 ||
-      d->kv_heads > 8 || d->layers < 1 || d->vocab % kTileRows || d->vocab < kTileRows ||
-      d->intermediate % 256 || loads_for_k(d->intermediate) != 12 || loads_for_k(d->q_heads * d->head_dim) != 8 ||
+      d->kv_heads > 8 || d->layers < 1 || d->vocab % kTileRows || d->vocab < kTileRows || !q_ok || !i_ok ||
       d->max_model_len < 1 || d->max_model_len > kMaxSplits * kAttnChunk || d->block_size < kAttnChunk ||
       d->block_size % kAttnChunk || d->num_blocks < 1)
     return DFB_E_GEOMETRY;
@@ -449,6 +500,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   DfbHandle* h = new (std::nothrow) DfbHandle();
   if (!h) return (int)cudaErrorMemoryAllocation;
   h->m = *d;
+  h->full_geometry = q_size == 2048 && inter == 3072;
   h->layers.assign(d->layer_weights, d->layer_weights + d->layers);
   h->m.layer_weights = nullptr;
   for (const DfbLayerWeights& w : h->layers)
@@ -485,6 +537,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_parts = carve(sizeof(ArgmaxPart) * kMaxRows * 4096);
   const size_t o_trace = carve(sizeof(unsigned long long) * 8 * kMaxTraceKernels);
   const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
+  const size_t o_best = carve(sizeof(ArgmaxPart) * kMaxRows * 9);  // this rank's winners | all ranks' (up to 8)
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
@@ -510,6 +563,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
     if (e != cudaSuccess) { dfb_destroy(h); return (int)e; }
   }
   h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
+  h->best_local = (ArgmaxPart*)(s + o_best); h->best_all = h->best_local + kMaxRows;
   *out = h;
   return 0;
 }
@@ -522,6 +576,18 @@ void dfb_destroy(DfbHandle* h) {
   if (h->host_tokens) cudaFreeHost(h->host_tokens);
   if (h->slab) cudaFree(h->slab);
   delete h;
+}
+
+int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp) {
+  if (!h || !tp || !tp->all_reduce || !tp->all_gather) return DFB_E_BAD_ARG;
+  if ((tp->size != 2 && tp->size != 4 && tp->size != 8) || tp->rank < 0 || tp->rank >= tp->size ||
+      tp->vocab_offset < 0)
+    return DFB_E_BAD_ARG;
+  if (h->step_mode != 0 || h->steps != 0) return DFB_E_BAD_ARG;  // before the first step, kernel chain only
+  h->tp = *tp;
+  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  h->graphs.clear();
+  return 0;
 }
 
 int dfb_set_option(DfbHandle* h, int option, int value) {
@@ -561,6 +627,7 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
       return 0;
     case DFB_OPT_STEP_MODE:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      if (value == 1 && (!h->full_geometry || h->sharded())) return DFB_E_GEOMETRY;  // built for the whole model only
       h->step_mode = value;
       return 0;
     case DFB_OPT_PERSIST_CTAS:

@@ -64,6 +64,7 @@ struct GemvArgs {
   unsigned int* ticket;          // argmax: arrival counter (self-resetting)
   int* tokens;                   // argmax: [rows] result (feedback buffer)
   int* tokens_out;               // argmax: optional second copy
+  ArgmaxPart* best_out;          // argmax: optional [rows] (value, index) of the winner (tensor-parallel merge)
   unsigned long long* trace;     // optional timeline slot of this launch (8 words) or null
   int* status;                   // [4] device status word or null
   int late_trigger;              // 1: let the successor start only after this kernel has read its inputs
@@ -405,6 +406,7 @@ stream_gemv_kernel(const GemvArgs a) {
         if (lane == 0) {
           a.tokens[b] = i;
           if (a.tokens_out) a.tokens_out[b] = i;
+          if (a.best_out) a.best_out[b] = ArgmaxPart{v, i};
         }
       }
       if (tid == 0) *a.ticket = 0u;
@@ -729,6 +731,24 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     a.tickets[row * a.kv_heads + kvh] = 0u;
     trace_max(a.trace, 2);
   }
+}
+
+// Tensor parallel: every rank holds the winners of all ranks' vocabulary shards
+// ([ranks][kMaxRows] pairs with shard-local indices); the greedy token of a row
+// is the largest value, the lowest global index among equals.
+__global__ void merge_shard_argmax_kernel(const ArgmaxPart* all, int ranks, int rows, int shard_rows, int* tokens,
+                                          int* tokens_out) {
+  const int b = threadIdx.x;
+  if (b >= rows) return;
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int r = 0; r < ranks; ++r) {
+    const ArgmaxPart p = all[r * kMaxRows + b];
+    const int gi = p.index + r * shard_rows;
+    if (p.value > v || (p.value == v && gi < idx)) { v = p.value; idx = gi; }
+  }
+  tokens[b] = idx;
+  if (tokens_out) tokens_out[b] = idx;
 }
 
 // Copies one step's inputs into the decoder's fixed staging buffers (so a

@@ -214,24 +214,35 @@ row_gemv_kernel(const GemvArgs a) {
     }
     if (probe && it == 0) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
     __syncthreads();
-    float v = 0.f;
-    if (tid < RC * NB) {
+    if (MODE == kModeStore) {
+      // narrow shards have fewer threads than outputs of a group: loop
+      for (int t = tid; t < RC * NB; t += C::kThreads) {
+        const int b = t / RC, r = t % RC;
+        float v = 0.f;
 #pragma unroll
-      for (int w = 0; w < W; ++w) v += red[w][eb][er];
-      v = round_bf16(v);
-    }
-    if (MODE == kModeNormSwiglu) {
-      // rows 0-7 of the group are gate rows, rows 8-15 the matching up rows
-      const float up = __shfl_down_sync(0xffffffffu, v, 8);
-      if (tid < RC * NB && er < 8 && eb < a.rows)
-        a.out[(size_t)eb * a.out_stride + grp * 8 + er] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-    } else if (tid < RC * NB && eb < a.rows) {
-      const int row = grp * RC + er;
-      if (MODE == kModeNormArgmax) {
-        if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + row] = v;
-        if (v > best_v || (v == best_v && row < best_i)) { best_v = v; best_i = row; }
-      } else {
-        a.out[(size_t)eb * a.out_stride + row] = __float2bfloat16_rn(v);
+        for (int w = 0; w < W; ++w) v += red[w][b][r];
+        if (b < a.rows) a.out[(size_t)b * a.out_stride + grp * RC + r] = __float2bfloat16_rn(v);
+      }
+    } else {
+      float v = 0.f;
+      if (tid < RC * NB) {
+#pragma unroll
+        for (int w = 0; w < W; ++w) v += red[w][eb][er];
+        v = round_bf16(v);
+      }
+      if (MODE == kModeNormSwiglu) {
+        // rows 0-7 of the group are gate rows, rows 8-15 the matching up rows
+        const float up = __shfl_down_sync(0xffffffffu, v, 8);
+        if (tid < RC * NB && er < 8 && eb < a.rows)
+          a.out[(size_t)eb * a.out_stride + grp * 8 + er] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+      } else if (tid < RC * NB && eb < a.rows) {
+        const int row = grp * RC + er;
+        if (MODE == kModeNormArgmax) {
+          if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + row] = v;
+          if (v > best_v || (v == best_v && row < best_i)) { best_v = v; best_i = row; }
+        } else {
+          a.out[(size_t)eb * a.out_stride + row] = __float2bfloat16_rn(v);
+        }
       }
     }
     if (nxt < n_groups) __syncthreads();   // `red` is reused by the next group
@@ -271,6 +282,7 @@ row_gemv_kernel(const GemvArgs a) {
         if (lane == 0) {
           a.tokens[b] = i;
           if (a.tokens_out) a.tokens_out[b] = i;
+          if (a.best_out) a.best_out[b] = ArgmaxPart{v, i};
         }
       }
       if (tid == 0) *a.ticket = 0u;

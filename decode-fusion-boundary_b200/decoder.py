@@ -67,7 +67,7 @@ class StreamDecoder:
     def __init__(self, weights, k_cache, v_cache, block_size: int, num_cache_blocks: int,
                  max_model_len: int = 2048, attn_splits: int = 1, fusion_groups: int = 1,
                  verbose: bool = False, debug_bounds: bool = False, use_graph: bool = True,
-                 use_pdl: bool = True, persistent: bool = False):
+                 use_pdl: bool = True, persistent: bool = False, tensor_parallel=None):
         import torch
 
         from . import native
@@ -115,6 +115,12 @@ class StreamDecoder:
         native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_GRAPH, int(use_graph)), "dfb_set_option")
         native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_USE_PDL, int(use_pdl)), "dfb_set_option")
         native.check(self._lib.dfb_set_option(handle, native.DFB_OPT_STEP_MODE, int(persistent)), "dfb_set_option")
+        # ``tensor_parallel``: a tensor_parallel.TensorParallelGroup; ``weights`` / the caches are then this
+        # rank's shard (tensor_parallel.shard_weights) and every rank must issue the same steps
+        self._tp = tensor_parallel
+        if tensor_parallel is not None and tensor_parallel.size > 1:
+            tp_desc = tensor_parallel.descriptor(native, weights.vocab_offset)
+            native.check(self._lib.dfb_set_tensor_parallel(handle, C.byref(tp_desc)), "dfb_set_tensor_parallel")
 
         # persistent per-step buffers: no allocation on the step path
         self._result = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cuda")

@@ -34,7 +34,7 @@ EXPORTS = (
     "dfb_create", "dfb_destroy", "dfb_set_option", "dfb_decode_step", "dfb_decode_step_host",
     "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
-    "dfb_lmhead_argmax_noalloc",
+    "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel",
 )
 
 
@@ -49,6 +49,16 @@ class DfbModelDesc(C.Structure):
         ("max_model_len", C.c_int32), ("block_size", C.c_int32), ("num_blocks", C.c_int32), ("eps", C.c_float),
         ("embed", C.c_void_p), ("final_norm", C.c_void_p), ("rope_cos_sin", C.c_void_p),
         ("layer_weights", C.POINTER(DfbLayerWeights)), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+    ]
+
+
+class DfbTensorParallel(C.Structure):
+    """One rank of a tensor-parallel group; the two collectives are plain
+    function addresses with ncclAllReduce's / ncclAllGather's signatures."""
+    _fields_ = [
+        ("size", C.c_int32), ("rank", C.c_int32), ("vocab_offset", C.c_int32), ("dtype_bf16", C.c_int32),
+        ("dtype_int8", C.c_int32), ("op_sum", C.c_int32), ("all_reduce", C.c_void_p), ("all_gather", C.c_void_p),
+        ("comm", C.c_void_p),
     ]
 
 

@@ -39,13 +39,17 @@ class DecoderWeights:
     layers: list[LayerTensors]
     final_norm: torch.Tensor
     cos_sin: torch.Tensor        # [max_model_len, head_dim] fp32
+    # tensor-parallel shard (tensor_parallel.shard_weights): `geom` then holds the per-rank sizes, `embed`
+    # stays the whole table of `embed_rows` rows and the rank's LM head starts at row `vocab_offset`
+    embed_rows: int | None = None
+    vocab_offset: int = 0
 
     def validate(self) -> None:
         g = self.geom
         expect = dict(ln_in=(g.hidden,), wqkv=(g.qkv_rows, g.hidden), q_norm=(g.head_dim,), k_norm=(g.head_dim,),
                       wo=(g.hidden, g.q_size), ln_post=(g.hidden,), wgu=(2 * g.intermediate, g.hidden),
                       wd=(g.hidden, g.intermediate))
-        tensors = [("embed", self.embed, (g.vocab, g.hidden)), ("final_norm", self.final_norm, (g.hidden,))]
+        tensors = [("embed", self.embed, (self.embed_rows or g.vocab, g.hidden)), ("final_norm", self.final_norm, (g.hidden,))]
         if len(self.layers) != g.layers:
             raise RuntimeError(f"expected {g.layers} layers, got {len(self.layers)}")
         for i, layer in enumerate(self.layers):

@@ -22,6 +22,7 @@
 #ifndef DFB_DECODE_H_
 #define DFB_DECODE_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -38,6 +39,7 @@ extern "C" {
 #define DFB_E_ABI (-3)          /* abi_version mismatch */
 #define DFB_E_DEVICE_STATUS (-4)/* a kernel reported an error in the status word */
 #define DFB_E_TOO_LARGE (-5)    /* request exceeds a fixed capacity */
+#define DFB_E_COMM (-6)         /* a tensor-parallel collective returned an error */
 
 typedef void* dfb_stream_t;     /* a cudaStream_t */
 typedef struct DfbHandle DfbHandle;
@@ -97,6 +99,39 @@ typedef struct DfbStepDesc {
   float* out_logits;          /* [rows, vocab] or NULL; bf16-rounded logits as fp32 (parity checks) */
 } DfbStepDesc;
 
+/* Tensor-parallel shard of the step.  The reference's megakernel backend runs
+ * on one GPU only (it answers tensor_parallel_size != 1 with an explicit
+ * fallback reason, backends/megakernel/compatibility.py); the partitioning
+ * here is the one of the reference's torch path: KV heads and their query
+ * heads, o_proj columns, gate/up rows, down_proj columns and LM-head rows are
+ * split evenly over the ranks (layers/linear.py:54-153, layers/embed_head.py,
+ * engine/model_runner.py:188), with a sum over the ranks after o_proj and
+ * after down_proj.
+ *
+ * A sharded decoder is created with the LOCAL sizes in DfbModelDesc (q_heads,
+ * kv_heads, intermediate, vocab = rows of this rank's LM-head shard; KV cache
+ * with the local kv_heads) and the rank's slices of the weights; `embed`
+ * still points to the whole embedding table (replicated), of which rows
+ * [vocab_offset, vocab_offset + vocab) are this rank's LM head.  The two
+ * collectives are called through function pointers with the signatures of
+ * ncclAllReduce / ncclAllGather, so that the library links against no
+ * communication library; `comm` is the caller's communicator. */
+typedef int (*dfb_all_reduce_fn)(const void* send, void* recv, size_t count, int dtype, int op, void* comm,
+                                 dfb_stream_t stream);
+typedef int (*dfb_all_gather_fn)(const void* send, void* recv, size_t send_count, int dtype, void* comm,
+                                 dfb_stream_t stream);
+typedef struct DfbTensorParallel {
+  int32_t size;               /* ranks: 2, 4 or 8 */
+  int32_t rank;
+  int32_t vocab_offset;       /* first embedding row of this rank's LM-head shard */
+  int32_t dtype_bf16;         /* the communication library's code for bf16 (ncclBfloat16 = 9) */
+  int32_t dtype_int8;         /* ... for bytes (ncclInt8 = 0) */
+  int32_t op_sum;             /* ... for a sum (ncclSum = 0) */
+  dfb_all_reduce_fn all_reduce;
+  dfb_all_gather_fn all_gather;
+  void* comm;
+} DfbTensorParallel;
+
 typedef struct DfbStatus {
   int32_t device_status;      /* 0 = ok; otherwise the first error code a kernel recorded */
   int32_t detail[3];          /* kernel id, index, observed value */
@@ -125,6 +160,9 @@ typedef struct DfbStatus {
  * copies the pointer tables, allocates the activation scratch (a few MB).
  * Replaces TaskGraphDecoder.__init__ (taskgraph.py:150-305). */
 int dfb_create(const DfbModelDesc* desc, DfbHandle** out);
+/* Make `h` one rank of a tensor-parallel group (see DfbTensorParallel); call once,
+ * before the first step.  Every rank must then enqueue the same steps in the same order. */
+int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp);
 void dfb_destroy(DfbHandle* h);
 int dfb_set_option(DfbHandle* h, int option, int value);
 
