@@ -200,6 +200,82 @@ def max_over_ranks(torch, value):
     return replicas.aggregate(_DIST, 0, value, device="cuda")[1]
 
 
+def run_tensor_parallel_arm(args):
+    """``--tp``: ONE model sharded over the ranks (strong scaling), batch 8 at context
+    1024 by default.  Every rank holds 1/N of the projections, of the KV heads
+    and of the LM head; the partial results are summed with NCCL after o_proj and
+    down_proj.  Reports device us/step as the max over ranks next to the per-rank
+    byte floor."""
+    global _DIST
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__  # noqa: F401
+    from dfb_b200 import native
+    from dfb_b200.decoder import StreamDecoder
+    from dfb_b200.geometry import QWEN3_06B
+    from dfb_b200.synthetic import random_init_weights
+    from dfb_b200.tensor_parallel import TensorParallelGroup, shard_weights
+
+    rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    if world not in (2, 4, 8):
+        raise SystemExit("--tp needs 2, 4 or 8 ranks (launch with torch.distributed.run)")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _DIST = dist
+    native.lib()
+    group = TensorParallelGroup.create(dist, local, transport=args.tp_transport)
+    g = QWEN3_06B
+    B, P, W, K = args.batch, args.prompt, args.warmup, args.steps
+    if P + W + K > g.max_model_len:
+        raise SystemExit(f"prompt {P} + {W + K} steps exceeds max_model_len {g.max_model_len}")
+    full = random_init_weights(g, seed=0, norm="ones", device="cuda")
+    weights = shard_weights(full, rank, world)
+    del full.layers[:]          # the unsharded projections are not needed any more
+    lg = weights.geom
+    pages = g.max_pages
+    kv = torch.empty(2, g.layers, B * pages, g.block_size, lg.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv.normal_(0, 1)            # a random KV history stands in for the prefill of the prompt
+    tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
+    dec = StreamDecoder(weights, kv[0], kv[1], g.block_size, B * pages, g.max_model_len, tensor_parallel=group)
+    barrier()
+    sampler = ClockSampler(local)
+    with sampler:
+        time_step_loop(dec, torch, B, P, 3, 5, g.block_size, tables)
+        ms = max_over_ranks(torch, time_step_loop(dec, torch, B, P, W, K, g.block_size, tables))
+    code, st = dec.status()
+    peak, peak_kind = measured_peaks()
+    contexts = [sum(P + W + s for s in range(K)) / K] * B
+    # bytes ONE rank streams per step: its shard of the layers and of the LM head, its KV heads
+    rank_bytes = (lg.layers * lg.layer_weight_bytes() + 2 * lg.hidden + lg.lm_head_bytes()
+                  + lg.kv_bytes_per_token() * int(sum(contexts)))
+    us = 1e3 * ms / K
+    line = {
+        "metric": METRIC, "value": B * K / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"Qwen3-0.6B geometry, bf16 random init (seed 0, N(0,0.02)), batch {B}, prompt {P} "
+                               f"token(s), greedy decode, KV block 256, one model over {world} GPUs",
+                   "batch": B, "prompt_tokens": P, "kv_block_size": 256, "parallelism": f"tp{world}",
+                   "collectives": ("own exchange kernels over peer-mapped memory (push + flag + bounded wait) after "
+                                   "o_proj and down_proj and for the greedy winners" if args.tp_transport == "direct" else
+                                   "ncclAllReduce (bf16 sum) after o_proj and down_proj, ncclAllGather of the "
+                                   "per-rank greedy winners") + "; all captured in the step's CUDA graph",
+                   "l2_policy": "inputs larger than L2 per rank" if rank_bytes > 126e6 else "per-rank bytes fit in L2"},
+        "device_us_per_step": us,
+        "step_floor": {"bytes_per_step_per_rank": rank_bytes, "floor_us": rank_bytes / (peak * 1e3),
+                       "frac_of_floor": rank_bytes / (peak * 1e3) / us, "peak_gbs": peak, "peak": peak_kind},
+        "gpu_launches": (int(st.kernels_per_step) + 1) * K, "collectives_per_step": 2 * g.layers + 1,
+        "clocks": sampler.summary(), "device_status": int(st.device_status),
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dec.close()
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
+    dist.destroy_process_group()
+
+
 def run_own_arm(args):
     global _DIST
     import torch
@@ -289,7 +365,7 @@ def run_own_arm(args):
                    if int(st.kernels_per_step) == 1 else
                    f"chain of {int(st.kernels_per_step)} kernels in one CUDA graph with programmatic dependent launch")
     lm_kernel = ("row_gemv_kernel<1024,NB,NormArgmax> (LM head + greedy argmax, FP32 pipe)" if B <= 2 else
-                 "stream_gemv_kernel<4,8,6,NormArgmax> (LM head + greedy argmax, mma.sync)")
+                 "pair_gemv_kernel<3,NormArgmax> (LM head + greedy argmax, mma.sync with 16 weight rows per MMA)")
 
     peak, peak_kind = measured_peaks()
     lm_bytes = g.lm_head_bytes() + 2 * g.hidden
@@ -508,10 +584,15 @@ def main():
     ap.add_argument("--torch-arm", action="store_true",
                     help="also time a torch / cuBLAS / CUDA-graph restatement of the reference decode path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-transport", default="direct", choices=["direct", "nccl"])
+    ap.add_argument("--tp", action="store_true",
+                    help="tensor parallelism over the launched ranks (one model, strong scaling) instead of replicas")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.tp:
+        run_tensor_parallel_arm(args)
     else:
         run_own_arm(args)
 

@@ -4,6 +4,8 @@
 #include "dfb_kernels.cuh"
 #include "dfb_persistent.cuh"
 #include "dfb_rowgemv.cuh"
+#include "dfb_exchange.cuh"
+#include "dfb_pairgemv.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -68,6 +70,7 @@ struct Launcher {
   int count = 0;
   int err = 0;
   int carve = -1;  // preferred shared-memory share of every kernel this launcher launches
+  int exchanges = 0;        // tensor-parallel exchanges launched so far in this step
   bool plain_next = false;  // the next launch follows a foreign kernel (a collective): no programmatic dependency
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   template <typename Args>
@@ -153,6 +156,10 @@ struct DfbHandle {
   ArgmaxPart* best_all = nullptr;    // [ranks, 8]
   bool full_geometry = true;     // unsharded Qwen3-0.6B shapes (what the persistent kernel is built for)
   bool sharded() const { return tp.size > 1; }
+  unsigned char* window_local = nullptr;          // this rank's exchange window (its own allocation)
+  unsigned char* windows[kMaxRanks] = {};          // every rank's window as mapped into this process
+  bool direct = false;                             // exchanges go through the windows instead of the collectives
+  unsigned int* tp_step = nullptr;                 // device step counter behind the exchange tags
   const bf16* lm_head() const { return (const bf16*)m.embed + (size_t)tp.vocab_offset * m.hidden; }
   int qkv_rows() const { return (m.q_heads + 2 * m.kv_heads) * m.head_dim; }
   int q_size() const { return m.q_heads * m.head_dim; }
@@ -202,6 +209,22 @@ void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
   L.launch(kernel, dim3(grid), dim3(WARPS * 32), a, allow_pdl, smem);
 }
 
+// Tensor-core GEMV with 16 weight rows per MMA (dfb_pairgemv.cuh), K = 1024, 3..8 batch rows.
+int g_pair_gemv = 1;   // 0: use stream_gemv_kernel (8 weight rows per MMA) instead
+template <int PSTAGES, int MODE>
+void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
+  static bool configured = false;
+  constexpr int smem = PairSmem::bytes(PSTAGES);
+  auto kernel = pair_gemv_kernel<PSTAGES, MODE>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { L.err = (int)e; return; }
+    configured = true;
+  }
+  a.trace = L.next_trace();
+  L.launch(kernel, dim3(grid), dim3(256), a, allow_pdl, smem);
+}
+
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
 template <int K, int NB, int MODE>
 void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
@@ -240,6 +263,11 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   if (rows <= g_row_max_rows && n % 16 == 0) {
     a.n_tiles = n / 16;
     launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
+    return L.err;
+  }
+  if (g_pair_gemv && n % 16 == 0) {
+    a.n_tiles = n / 16;
+    launch_pair<2, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
     return L.err;
   }
   launch_gemv<4, 8, 4, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
@@ -294,6 +322,11 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
+  if (g_pair_gemv && inter % 8 == 0) {
+    a.n_tiles = inter / 8;
+    launch_pair<3, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
+    return L.err;
+  }
   launch_gemv<4, 8, 6, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
   return L.err;
 }
@@ -313,13 +346,27 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
+  } else if (g_pair_gemv && m.vocab % 16 == 0) {
+    a.n_tiles = m.vocab / 16;
+    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    launch_pair<3, kModeNormArgmax>(L, a, grid);
   } else {
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     launch_gemv<4, 8, 6, kModeNormArgmax>(L, a, grid);
   }
-  if (h->sharded() && !L.err) {
+  if (h->sharded() && !L.err && h->direct) {
+    ExchangeArgmaxArgs e = {};
+    for (int r = 0; r < h->tp.size; ++r) e.window[r] = h->windows[r];
+    e.size = h->tp.size; e.rank = h->tp.rank; e.rows = rows; e.shard_rows = m.vocab; e.step_counter = h->tp_step;
+    e.best_local = h->best_local; e.tokens = h->tokens; e.tokens_out = tokens_out; e.status = h->status;
+    exchange_argmax_kernel<<<1, 32, 0, L.stream>>>(e);
+    ++L.count;
+    L.plain_next = true;
+  } else if (h->sharded() && !L.err) {
     // every rank collects the winners of all vocabulary shards and picks the same token
+    if (!h->tp.all_gather) return DFB_E_COMM;
     if (h->tp.all_gather(h->best_local, h->best_all, sizeof(ArgmaxPart) * kMaxRows, h->tp.dtype_int8, h->tp.comm,
                          (dfb_stream_t)L.stream))
       return DFB_E_COMM;
@@ -333,6 +380,17 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
 // Tensor parallel: sum the ranks' partial results of a row-parallel projection in place.
 int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
   if (!h->sharded() || L.err) return L.err;
+  if (h->direct) {
+    ExchangeArgs a = {};
+    for (int r = 0; r < h->tp.size; ++r) a.window[r] = h->windows[r];
+    a.size = h->tp.size; a.rank = h->tp.rank; a.rows = rows; a.slot = L.exchanges; a.buf = L.exchanges & 1;
+    a.step_counter = h->tp_step; a.local = buf; a.status = h->status;
+    if (++L.exchanges >= kExchangeSlots - 1) return DFB_E_TOO_LARGE;
+    a.trace = L.next_trace();
+    L.launch(exchange_sum_kernel, dim3(1), dim3(1024), a);
+    return L.err;
+  }
+  if (!h->tp.all_reduce) return DFB_E_COMM;
   if (h->tp.all_reduce(buf, buf, (size_t)rows * h->m.hidden, h->tp.dtype_bf16, h->tp.op_sum, h->tp.comm,
                        (dfb_stream_t)L.stream))
     return DFB_E_COMM;
@@ -340,7 +398,7 @@ int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
   return 0;
 }
 
-int g_attn_wide_ctas = 2 * 148;  // FP32 chain: attention grids up to this many CTAs use 256-thread CTAs
+int g_attn_wide_ctas = 2 * 148;  // attention grids up to this many CTAs use 256-thread CTAs
 
 int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
                      int bt_stride, const int* row_active, bf16* out, int rows, int nsplit) {
@@ -364,6 +422,8 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
     a.late_trigger = g_late_trigger;
     if (ctas <= g_attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
     else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
+  } else if (ctas <= g_attn_wide_ctas) {
+    L.launch(paged_attention_kernel<256, 1>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
   } else {
     L.launch(paged_attention_kernel<128, 1>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
   }
@@ -538,6 +598,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_trace = carve(sizeof(unsigned long long) * 8 * kMaxTraceKernels);
   const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
   const size_t o_best = carve(sizeof(ArgmaxPart) * kMaxRows * 9);  // this rank's winners | all ranks' (up to 8)
+  const size_t o_tpstep = carve(sizeof(unsigned) * 4);
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
@@ -564,6 +625,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   }
   h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
   h->best_local = (ArgmaxPart*)(s + o_best); h->best_all = h->best_local + kMaxRows;
+  h->tp_step = (unsigned int*)(s + o_tpstep);
   *out = h;
   return 0;
 }
@@ -572,6 +634,9 @@ void dfb_destroy(DfbHandle* h) {
   if (!h) return;
   for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
   if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (h->windows[r] && h->windows[r] != h->window_local) cudaIpcCloseMemHandle(h->windows[r]);
+  if (h->window_local) cudaFree(h->window_local);
   if (h->host_stage) cudaFreeHost(h->host_stage);
   if (h->host_tokens) cudaFreeHost(h->host_tokens);
   if (h->slab) cudaFree(h->slab);
@@ -579,12 +644,47 @@ void dfb_destroy(DfbHandle* h) {
 }
 
 int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp) {
-  if (!h || !tp || !tp->all_reduce || !tp->all_gather) return DFB_E_BAD_ARG;
+  if (!h || !tp) return DFB_E_BAD_ARG;
   if ((tp->size != 2 && tp->size != 4 && tp->size != 8) || tp->rank < 0 || tp->rank >= tp->size ||
       tp->vocab_offset < 0)
     return DFB_E_BAD_ARG;
   if (h->step_mode != 0 || h->steps != 0) return DFB_E_BAD_ARG;  // before the first step, kernel chain only
   h->tp = *tp;
+  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  h->graphs.clear();
+  return 0;
+}
+
+int dfb_tp_window_handle(DfbHandle* h, void* handle_out) {
+  if (!h || !handle_out || !h->sharded()) return DFB_E_BAD_ARG;
+  if (!h->window_local) {
+    DFB_CUDA(cudaMalloc((void**)&h->window_local, Window::kBytes));
+    DFB_CUDA(cudaMemset(h->window_local, 0, Window::kBytes));
+  }
+  cudaIpcMemHandle_t ipc;
+  DFB_CUDA(cudaIpcGetMemHandle(&ipc, h->window_local));
+  static_assert(sizeof(ipc) == DFB_TP_HANDLE_BYTES, "IPC handle size");
+  memcpy(handle_out, &ipc, sizeof(ipc));
+  return 0;
+}
+
+int dfb_tp_open_peers(DfbHandle* h, const void* handles) {
+  if (!h || !handles || !h->sharded() || !h->window_local || h->direct || h->steps != 0) return DFB_E_BAD_ARG;
+  const char* p = (const char*)handles;
+  for (int r = 0; r < h->tp.size; ++r) {
+    if (r == h->tp.rank) { h->windows[r] = h->window_local; continue; }
+    cudaIpcMemHandle_t ipc;
+    memcpy(&ipc, p + (size_t)r * DFB_TP_HANDLE_BYTES, sizeof(ipc));
+    void* mapped = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      for (int q = 0; q < r; ++q)
+        if (q != h->tp.rank && h->windows[q]) { cudaIpcCloseMemHandle(h->windows[q]); h->windows[q] = nullptr; }
+      return (int)e;
+    }
+    h->windows[r] = (unsigned char*)mapped;
+  }
+  h->direct = true;
   for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
   h->graphs.clear();
   return 0;
@@ -610,6 +710,12 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
       g_carve_mma = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_PAIR_GEMV:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      g_pair_gemv = value;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

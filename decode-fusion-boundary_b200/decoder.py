@@ -121,6 +121,11 @@ class StreamDecoder:
         if tensor_parallel is not None and tensor_parallel.size > 1:
             tp_desc = tensor_parallel.descriptor(native, weights.vocab_offset)
             native.check(self._lib.dfb_set_tensor_parallel(handle, C.byref(tp_desc)), "dfb_set_tensor_parallel")
+            if tensor_parallel.transport == "direct":
+                mine = C.create_string_buffer(native.DFB_TP_HANDLE_BYTES)
+                native.check(self._lib.dfb_tp_window_handle(handle, mine), "dfb_tp_window_handle")
+                everyone = tensor_parallel.gather_bytes(mine.raw)
+                native.check(self._lib.dfb_tp_open_peers(handle, b"".join(everyone)), "dfb_tp_open_peers")
 
         # persistent per-step buffers: no allocation on the step path
         self._result = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cuda")

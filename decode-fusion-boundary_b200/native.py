@@ -16,14 +16,15 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libdfb_decode.so"
 SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
-HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
+HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
 
 DFB_ABI_VERSION = 1
 DFB_MAX_ROWS = 8
 DFB_ATTN_CHUNK = 64
+DFB_TP_HANDLE_BYTES = 64
 DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
 DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS, DFB_OPT_ROW_GEMV, DFB_OPT_ATTN_WIDE = 5, 6, 7, 8
-DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER = 9, 10, 11
+DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER, DFB_OPT_PAIR_GEMV = 9, 10, 11, 12
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -34,7 +35,7 @@ EXPORTS = (
     "dfb_create", "dfb_destroy", "dfb_set_option", "dfb_decode_step", "dfb_decode_step_host",
     "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
-    "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel",
+    "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
 )
 
 

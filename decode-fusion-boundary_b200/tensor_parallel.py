@@ -118,9 +118,13 @@ class TensorParallelGroup:
     size: int
     comm: C.c_void_p
     lib: object
+    dist: object = None
+    # "direct": the library's own exchange kernels over peer-mapped memory (NVLink, one node);
+    # "nccl": ncclAllReduce / ncclAllGather on the library's stream
+    transport: str = "direct"
 
     @classmethod
-    def create(cls, dist, device_index: int) -> "TensorParallelGroup":
+    def create(cls, dist, device_index: int, transport: str = "direct") -> "TensorParallelGroup":
         """``dist``: an initialised ``torch.distributed`` (any backend) used only
         to hand rank 0's NCCL id to the other ranks."""
         import torch
@@ -141,7 +145,15 @@ class TensorParallelGroup:
         rc = nccl.ncclCommInitRank(C.byref(comm), size, uid, rank)
         if rc:
             raise RuntimeError(f"ncclCommInitRank failed with code {rc}")
-        return cls(rank, size, comm, nccl)
+        if transport not in ("direct", "nccl"):
+            raise ValueError("transport must be 'direct' or 'nccl'")
+        return cls(rank, size, comm, nccl, dist, transport)
+
+    def gather_bytes(self, payload: bytes) -> list[bytes]:
+        """Every rank's ``payload`` in rank order (host side, through torch.distributed)."""
+        out = [None] * self.size
+        self.dist.all_gather_object(out, payload)
+        return out
 
     def descriptor(self, native, vocab_offset: int):
         return native.DfbTensorParallel(

@@ -147,13 +147,15 @@ typedef struct DfbStatus {
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
 #define DFB_OPT_ROW_GEMV 7    /* largest batch (0..8) that runs the projections on the FP32 GEMV kernels in the
                                  kernel chain; larger batches use the tensor-core kernels (process-wide) */
-#define DFB_OPT_ATTN_WIDE 8   /* FP32 chain: attention grids of at most this many CTAs run 256-thread CTAs
+#define DFB_OPT_ATTN_WIDE 8   /* attention grids of at most this many CTAs run 256-thread CTAs
                                  instead of 128-thread ones (process-wide; default 296 = two per SM) */
 #define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
                                         kernels of the FP32 chain ask for as shared memory (process-wide; default 12) */
 #define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chain (default 50) */
 #define DFB_OPT_LATE_TRIGGER 11 /* FP32 chain: 0 (default) = a kernel lets its successor start (and request its
                                   weights) at once, 1 = only after it has read its own inputs (process-wide) */
+#define DFB_OPT_PAIR_GEMV 12    /* tensor-core chain, K = 1024: 1 (default) = 16 weight rows per MMA (pair_gemv_kernel),
+                                  0 = 8 weight rows per MMA (stream_gemv_kernel) (process-wide) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
@@ -163,6 +165,17 @@ int dfb_create(const DfbModelDesc* desc, DfbHandle** out);
 /* Make `h` one rank of a tensor-parallel group (see DfbTensorParallel); call once,
  * before the first step.  Every rank must then enqueue the same steps in the same order. */
 int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp);
+/* Exchanges over peer-mapped memory instead of the two collectives (NVLink, all ranks on one node, one
+ * process per GPU).  Each rank calls dfb_tp_window_handle, which allocates its exchange window (about 260 KB)
+ * and writes a DFB_TP_HANDLE_BYTES-byte inter-process handle (a cudaIpcMemHandle_t); the caller gathers the
+ * handles of all ranks, in rank order, and passes them to dfb_tp_open_peers on every rank, after which the
+ * sums after o_proj / down_proj and the merge of the greedy winners are done by the library's own kernels
+ * (a push into every peer's window, a flag, a bounded wait; all_reduce / all_gather may then be NULL).  A
+ * peer that does not arrive within 2 s makes the waiting kernel record status 4 and finish; the step's
+ * result is then invalid and dfb_read_status reports it. */
+#define DFB_TP_HANDLE_BYTES 64
+int dfb_tp_window_handle(DfbHandle* h, void* handle_out);
+int dfb_tp_open_peers(DfbHandle* h, const void* handles);
 void dfb_destroy(DfbHandle* h);
 int dfb_set_option(DfbHandle* h, int option, int value);
 

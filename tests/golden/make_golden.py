@@ -214,7 +214,7 @@ def _summarise(logits, probe):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory holding src/nanovllm)")
     ap.add_argument("--skip-full", action="store_true")
     args = ap.parse_args()
     ref = _import_reference(args.reference)

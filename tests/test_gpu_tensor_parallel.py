@@ -29,7 +29,8 @@ def _run(world, tmp_path, **kw):
     from tests.tp_worker import tp_parity_worker
 
     args = (world, _free_port(), str(tmp_path), kw.get("layers", 2), kw.get("vocab", 4096),
-            kw.get("prompt_lens", (3, 70, 250)), kw.get("steps", 3), kw.get("use_graph", False))
+            kw.get("prompt_lens", (3, 70, 250)), kw.get("steps", 3), kw.get("use_graph", False),
+            kw.get("transport", "direct"))
     mp.spawn(tp_parity_worker, args=args, nprocs=world, join=True)
     return [json.loads((tmp_path / f"rank{r}.json").read_text()) for r in range(world)]
 
@@ -40,11 +41,12 @@ def _world_sizes():
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("transport", ["direct", "nccl"])
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_tensor_parallel_matches_unsharded_oracle(world, use_graph, tmp_path):
+def test_tensor_parallel_matches_unsharded_oracle(world, use_graph, transport, tmp_path):
     if world not in _world_sizes():
         pytest.skip(f"needs {world} GPUs")
-    reports = _run(world, tmp_path, use_graph=use_graph, vocab=4096 * 2)
+    reports = _run(world, tmp_path, use_graph=use_graph, vocab=4096 * 2, transport=transport)
     for rep in reports:
         assert rep["device_status"] == 0, rep
         assert rep["ranks_agree"], rep

@@ -19,7 +19,7 @@ if str(ROOT) not in sys.path:
 
 
 def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int, vocab: int, prompt_lens, steps: int,
-                     use_graph: bool):
+                     use_graph: bool, transport: str):
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -32,7 +32,7 @@ def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int
 
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     torch.cuda.set_device(rank)
-    group = TensorParallelGroup.create(dist, rank)
+    group = TensorParallelGroup.create(dist, rank, transport=transport)
     seed = 5
     g = H.oracle_geometry(layers=layers, vocab=vocab)
     w = O.make_weights(g, seed=seed, norm="random").to(torch.bfloat16)
@@ -49,6 +49,7 @@ def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int
     kv_gpu = kv[:, :, :, :, h0:h1, :].contiguous().cuda()
     dec = StreamDecoder(local, kv_gpu[0], kv_gpu[1], block_size=g.block_size, num_cache_blocks=nblocks,
                         max_model_len=g.max_pos, use_graph=use_graph, tensor_parallel=group)
+    dist.barrier()   # the ranks start their first step together (the exchange waits are bounded)
     rows = len(prompts)
     lens = [n + 1 for n in prompt_lens]
     logits_gpu = torch.zeros(rows, lg.vocab, dtype=torch.float32, device="cuda")
