@@ -46,6 +46,7 @@ typedef __nv_bfloat16 bf16;
 // for the same split; otherwise a kernel that prefers another one starts late.
 // `percent` is the share of the SM's 228 KB that goes to shared memory (-1:
 // leave the choice to the driver).
+int g_bulk_x = 1;        // FP32 chain: the fused norm fetches its inputs with bulk copies (TMA) instead of loads
 int g_late_trigger = 0;  // FP32 chain: 1 = a kernel lets its successor start only after it has read its inputs
 int g_carve_fp32 = 12;   // chain of FP32 GEMV kernels: little shared memory, L1 helps
 int g_carve_mma = 50;    // chain of tensor-core GEMV kernels: room for the weight stages (up to 101 KB), the rest stays L1
@@ -237,6 +238,7 @@ void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
   }
   configured = true;
   a.late_trigger = g_late_trigger;
+  a.bulk_x = g_bulk_x;
   // The down projection has one CTA per SM's worth of work (128 CTAs): asking for at
   // least 16 KB keeps two of them off one SM (with the 32 KB split of this chain),
   // which measured 25 us per step faster at batch 1 than letting them pair up.
@@ -710,6 +712,12 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
       g_carve_mma = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_BULK_X:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      g_bulk_x = value;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

@@ -68,6 +68,7 @@ struct GemvArgs {
   unsigned long long* trace;     // optional timeline slot of this launch (8 words) or null
   int* status;                   // [4] device status word or null
   int late_trigger;              // 1: let the successor start only after this kernel has read its inputs
+  int bulk_x;                    // 1: FP32 kernels fetch x and the residual of the fused norm with bulk copies
 };
 
 // ---------------------------------------------------------------------------

@@ -156,6 +156,8 @@ typedef struct DfbStatus {
                                   weights) at once, 1 = only after it has read its own inputs (process-wide) */
 #define DFB_OPT_PAIR_GEMV 12    /* tensor-core chain, K = 1024: 1 (default) = 16 weight rows per MMA (pair_gemv_kernel),
                                   0 = 8 weight rows per MMA (stream_gemv_kernel) (process-wide) */
+#define DFB_OPT_BULK_X 13       /* FP32 chain: 1 (default) = the fused norm fetches x and the residual with bulk
+                                  copies (TMA), 0 = with ordinary loads (process-wide) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
