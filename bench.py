@@ -223,7 +223,7 @@ def run_tensor_parallel_arm(args):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _DIST = dist
     native.lib()
-    group = TensorParallelGroup.create(dist, local, transport=args.tp_transport)
+    group = TensorParallelGroup.create(dist, local, transport="nccl" if args.tp_transport == "nccl" else "direct")
     g = QWEN3_06B
     B, P, W, K = args.batch, args.prompt, args.warmup, args.steps
     if P + W + K > g.max_model_len:
@@ -237,6 +237,8 @@ def run_tensor_parallel_arm(args):
     kv.normal_(0, 1)            # a random KV history stands in for the prefill of the prompt
     tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
     dec = StreamDecoder(weights, kv[0], kv[1], g.block_size, B * pages, g.max_model_len, tensor_parallel=group)
+    if args.tp_transport == "direct_unfused":
+        dec.set_option(native.DFB_OPT_TP_FUSED, 0)
     barrier()
     sampler = ClockSampler(local)
     with sampler:
@@ -256,8 +258,11 @@ def run_tensor_parallel_arm(args):
         "config": {"workload": f"Qwen3-0.6B geometry, bf16 random init (seed 0, N(0,0.02)), batch {B}, prompt {P} "
                                f"token(s), greedy decode, KV block 256, one model over {world} GPUs",
                    "batch": B, "prompt_tokens": P, "kv_block_size": 256, "parallelism": f"tp{world}",
-                   "collectives": ("own exchange kernels over peer-mapped memory (push + flag + bounded wait) after "
-                                   "o_proj and down_proj and for the greedy winners" if args.tp_transport == "direct" else
+                   "collectives": ("exchange over peer-mapped memory fused into the kernels: o_proj / down_proj push "
+                                   "tagged words into the peers' windows, the next fused norm pulls them (bounded wait)"
+                                   if args.tp_transport == "direct" else
+                                   "own exchange kernel over peer-mapped memory (push tagged words, bounded wait) after "
+                                   "o_proj and down_proj" if args.tp_transport == "direct_unfused" else
                                    "ncclAllReduce (bf16 sum) after o_proj and down_proj, ncclAllGather of the "
                                    "per-rank greedy winners") + "; all captured in the step's CUDA graph",
                    "l2_policy": "inputs larger than L2 per rank" if rank_bytes > 126e6 else "per-rank bytes fit in L2"},
@@ -584,7 +589,7 @@ def main():
     ap.add_argument("--torch-arm", action="store_true",
                     help="also time a torch / cuBLAS / CUDA-graph restatement of the reference decode path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp-transport", default="direct", choices=["direct", "nccl"])
+    ap.add_argument("--tp-transport", default="direct", choices=["direct", "direct_unfused", "nccl"])
     ap.add_argument("--tp", action="store_true",
                     help="tensor parallelism over the launched ranks (one model, strong scaling) instead of replicas")
     args = ap.parse_args()

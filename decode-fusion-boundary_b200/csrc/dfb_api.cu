@@ -72,6 +72,9 @@ struct Launcher {
   int err = 0;
   int carve = -1;  // preferred shared-memory share of every kernel this launcher launches
   int exchanges = 0;        // tensor-parallel exchanges launched so far in this step
+  int push_slot = -1;       // >= 0: the next projection pushes its result to the peers as exchange `push_slot`
+  int pull_slot = -1;       // >= 0: the next fused norm adds the peers' partial results of exchange `pull_slot`
+  const DfbHandle* tp = nullptr;  // set by a tensor-parallel step
   bool plain_next = false;  // the next launch follows a foreign kernel (a collective): no programmatic dependency
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   template <typename Args>
@@ -160,6 +163,7 @@ struct DfbHandle {
   unsigned char* window_local = nullptr;          // this rank's exchange window (its own allocation)
   unsigned char* windows[kMaxRanks] = {};          // every rank's window as mapped into this process
   bool direct = false;                             // exchanges go through the windows instead of the collectives
+  bool fused = true;                               // ... and inside the projection / norm kernels, not in a kernel of their own
   unsigned int* tp_step = nullptr;                 // device step counter behind the exchange tags
   const bf16* lm_head() const { return (const bf16*)m.embed + (size_t)tp.vocab_offset * m.hidden; }
   int qkv_rows() const { return (m.q_heads + 2 * m.kv_heads) * m.head_dim; }
@@ -175,6 +179,16 @@ struct DfbHandle {
 namespace {
 
 constexpr int kMaxTraceKernels = 1024;
+
+// Tensor parallel, fused exchange: a projection that pushes (producer) or a fused norm that pulls.
+void tp_fill(Launcher& L, const DfbHandle* h, GemvArgs& a, bool producer) {
+  const int slot = producer ? L.push_slot : L.pull_slot;
+  if (!h || slot < 0) return;
+  a.tp_mode = producer ? 1 : 2;
+  a.tp_size = h->tp.size; a.tp_rank = h->tp.rank; a.tp_slot = slot; a.tp_step = h->tp_step;
+  for (int r = 0; r < h->tp.size; ++r) a.tp_window[r] = h->windows[r];
+  if (producer) L.push_slot = -1; else L.pull_slot = -1;
+}
 
 int loads_for_k(int k) { return (k % 256 == 0) ? k / 256 : 0; }
 
@@ -264,11 +278,13 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   a.out = out; a.out_stride = n; a.status = status;
   if (rows <= g_row_max_rows && n % 16 == 0) {
     a.n_tiles = n / 16;
+    tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
     return L.err;
   }
   if (g_pair_gemv && n % 16 == 0) {
     a.n_tiles = n / 16;
+    tp_fill(L, L.tp, a, false);
     launch_pair<2, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
     return L.err;
   }
@@ -287,8 +303,9 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
   // The FP32 kernels cover every input width (the full model's 2048 / 3072 and the
   // tensor-parallel shards 256 ... 1536); the tensor-core kernels 1024, 2048 and 3072.
   const int mma_loads = (k == 1024 || k == 2048 || k == 3072) ? loads_for_k(k) : 0;
-  if (rows <= g_row_max_rows || mma_loads == 0) {
+  if (rows <= g_row_max_rows || mma_loads == 0 || L.push_slot >= 0) {
     a.n_tiles = n / RowRowsFor(k);
+    tp_fill(L, L.tp, a, true);
     switch (k) {
       case 256: launch_row<256, kModeStore>(L, a, rows, a.n_tiles); break;
       case 384: launch_row<384, kModeStore>(L, a, rows, a.n_tiles); break;
@@ -321,11 +338,13 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
   if (rows <= g_row_max_rows && inter % 8 == 0) {
     a.n_tiles = inter / 8;
+    tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
   if (g_pair_gemv && inter % 8 == 0) {
     a.n_tiles = inter / 8;
+    tp_fill(L, L.tp, a, false);
     launch_pair<3, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
     return L.err;
   }
@@ -347,11 +366,13 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
+    tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
   } else if (g_pair_gemv && m.vocab % 16 == 0) {
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
+    tp_fill(L, L.tp, a, false);
     launch_pair<3, kModeNormArgmax>(L, a, grid);
   } else {
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
@@ -446,6 +467,18 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
   const DfbModelDesc& m = h->m;
   Launcher L{stream, h->use_pdl, h->trace_on ? h->trace : nullptr};
   L.carve = rows <= g_row_max_rows ? g_carve_fp32 : g_carve_mma;
+  L.tp = h;
+  // Tensor parallel over the windows: the projections push their partial results and the next fused norm
+  // pulls them, when every consumer of this step runs on a kernel that can (all Qwen3 shards do).
+  const bool pair_ok = g_pair_gemv && h->qkv_rows() % 16 == 0 && m.intermediate % 8 == 0 && m.vocab % 16 == 0;
+  const bool row_ok = h->qkv_rows() % 16 == 0 && m.intermediate % 8 == 0 && m.vocab % 16 == 0;
+  const bool fused = h->sharded() && h->direct && h->fused && (rows <= g_row_max_rows ? row_ok : pair_ok);
+  auto exchange = [&](int rc_in) -> int {   // after a row-parallel projection into h->hbuf
+    if (rc_in || !h->sharded()) return rc_in;
+    if (!fused) return tp_sum(L, h, h->hbuf, rows);
+    L.pull_slot = L.exchanges;
+    return ++L.exchanges >= kExchangeSlots - 1 ? DFB_E_TOO_LARGE : 0;
+  };
   int rc = 0;
   int cur = 0;  // index of the residual buffer holding the current residual
   for (int l = 0; l < m.layers && !rc; ++l) {
@@ -463,15 +496,15 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
     if (rc) break;
     rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, h->st_active(), h->attn, rows, nsplit);
     if (rc) break;
-    rc = launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status);
-    if (!rc) rc = tp_sum(L, h, h->hbuf, rows);
+    if (fused) L.push_slot = L.exchanges;
+    rc = exchange(launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status));
     if (rc) break;
     rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
                        rows, m.hidden, m.intermediate, m.eps, h->status);
     cur ^= 1;
     if (rc) break;
-    rc = launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status);
-    if (!rc) rc = tp_sum(L, h, h->hbuf, rows);
+    if (fused) L.push_slot = L.exchanges;
+    rc = exchange(launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status));
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
   h->kernels_per_step = L.count;
@@ -712,6 +745,12 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
       g_carve_mma = value;
+      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+      h->graphs.clear();
+      return 0;
+    case DFB_OPT_TP_FUSED:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      h->fused = value != 0;
       for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
       h->graphs.clear();
       return 0;

@@ -27,7 +27,6 @@
 
 namespace dfb {
 
-constexpr int kMaxRanks = 8;
 constexpr int kExchangeSlots = 64;                     // exchanges per step fit in 6 bits
 constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // 2 s
 constexpr int kStatusPeerTimeout = 4;
@@ -98,6 +97,53 @@ __device__ __forceinline__ bool wait_word(const uint2* p, unsigned int tag, int*
   }
   data = 0u;
   return false;
+}
+
+__device__ __forceinline__ unsigned int exchange_tag(const unsigned int* step_counter, int slot) {
+  return *step_counter * kExchangeSlots + (unsigned)slot + 1u;
+}
+// words of source rank `src` in inbox `buf` of the window at `window`
+__device__ __forceinline__ uint2* inbox_words(unsigned char* window, int buf, int src) {
+  return reinterpret_cast<uint2*>(window) + ((size_t)buf * kMaxRanks + src) * Window::kSlotWords;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Fused consumer side: the two words (4 values) starting at word `first` of each of
+// NR batch rows from peer `src`, all loads in flight together, re-read until both
+// tags are there (bounded like wait_flag).  Returns the data words in d[b][0..1].
+template <int NR>
+__device__ __forceinline__ void pull_words(unsigned char* window, int buf, int src, int first, int rows,
+                                           unsigned int tag, int* status, uint32_t (&d)[NR][2]) {
+  const uint2* base = inbox_words(window, buf, src) + first;
+  uint4 w[NR];
+#pragma unroll
+  for (int b = 0; b < NR; ++b)
+    w[b] = b < rows ? ld_relaxed_sys_v4(base + (size_t)b * 512) : make_uint4(0, tag, 0, tag);
+  const unsigned long long t0 = global_ns();
+  int polls = 0;
+  for (;;) {
+    bool all = true;
+#pragma unroll
+    for (int b = 0; b < NR; ++b)
+      if (w[b].y != tag || w[b].w != tag) {
+        all = false;
+        w[b] = ld_relaxed_sys_v4(base + (size_t)b * 512);
+      }
+    if (all) break;
+    if ((++polls & 63) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) break;
+      if (global_ns() - t0 > kPeerWaitNs) {
+        report_status(status, kStatusPeerTimeout, kKernelExchange, src, (int)tag);
+        break;
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < NR; ++b) { d[b][0] = w[b].x; d[b][1] = w[b].z; }
 }
 
 // Sum of the ranks' partial [rows, 1024] results, in place.  One CTA of 1024

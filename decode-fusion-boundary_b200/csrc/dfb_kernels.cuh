@@ -24,6 +24,7 @@
 namespace dfb {
 
 constexpr int kMaxRows = 8;
+constexpr int kMaxRanks = 8;          // tensor-parallel ranks
 constexpr int kTileRows = 8;          // weight rows per tile = N of mma.m16n8k16
 constexpr int kAttnThreads = 128;
 constexpr int kAttnChunk = 64;        // context positions per attention CTA
@@ -69,6 +70,12 @@ struct GemvArgs {
   int* status;                   // [4] device status word or null
   int late_trigger;              // 1: let the successor start only after this kernel has read its inputs
   int bulk_x;                    // 1: FP32 kernels fetch x and the residual of the fused norm with bulk copies
+  // tensor-parallel exchange fused into this kernel (dfb_exchange.cuh); 0 = none
+  int tp_mode;                   // 1: push the [rows, 1024] result into every peer's window as tagged words
+                                 // 2: the fused norm adds the peers' partial results found in this rank's window
+  int tp_size, tp_rank, tp_slot; // ranks, this rank, index of the exchange in the step
+  const unsigned int* tp_step;   // device step counter behind the tags
+  unsigned char* tp_window[kMaxRanks];   // every rank's window as mapped here
 };
 
 // ---------------------------------------------------------------------------

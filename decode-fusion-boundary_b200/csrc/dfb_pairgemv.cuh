@@ -20,6 +20,7 @@
 //     epilogue (store / SwiGLU / logits + greedy argmax).
 #pragma once
 
+#include "dfb_exchange.cuh"
 #include "dfb_kernels.cuh"
 
 namespace dfb {
@@ -113,8 +114,42 @@ __global__ void __launch_bounds__(256, 1) pair_gemv_kernel(const GemvArgs a) {
     }
 #pragma unroll
     for (int b = 0; b < kMaxRows; ++b) {
-      x[b][0] = bf_lo(hv[b].x) + bf_lo(rv[b].x); x[b][1] = bf_hi(hv[b].x) + bf_hi(rv[b].x);
-      x[b][2] = bf_lo(hv[b].y) + bf_lo(rv[b].y); x[b][3] = bf_hi(hv[b].y) + bf_hi(rv[b].y);
+      x[b][0] = bf_lo(hv[b].x); x[b][1] = bf_hi(hv[b].x); x[b][2] = bf_lo(hv[b].y); x[b][3] = bf_hi(hv[b].y);
+    }
+    if (a.tp_mode == 2) {
+      // tensor parallel: hv holds this rank's partial projection; add the peers' (pushed into this rank's
+      // window by their projection kernels) in rank order and round once, like the unfused exchange
+      const unsigned int tag = exchange_tag(a.tp_step, a.tp_slot);
+      float acc[kMaxRows][4];
+#pragma unroll
+      for (int b = 0; b < kMaxRows; ++b)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[b][e] = 0.f;
+      for (int r = 0; r < a.tp_size; ++r) {
+        if (r == a.tp_rank) {
+#pragma unroll
+          for (int b = 0; b < kMaxRows; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[b][e] += x[b][e];
+        } else {
+          uint32_t d[kMaxRows][2];
+          pull_words<kMaxRows>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, 2 * tid, a.rows, tag, a.status, d);
+#pragma unroll
+          for (int b = 0; b < kMaxRows; ++b) {
+            acc[b][0] += bf_lo(d[b][0]); acc[b][1] += bf_hi(d[b][0]);
+            acc[b][2] += bf_lo(d[b][1]); acc[b][3] += bf_hi(d[b][1]);
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < kMaxRows; ++b)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[b][e] = round_bf16(acc[b][e]);
+    }
+#pragma unroll
+    for (int b = 0; b < kMaxRows; ++b) {
+      x[b][0] += bf_lo(rv[b].x); x[b][1] += bf_hi(rv[b].x);
+      x[b][2] += bf_lo(rv[b].y); x[b][3] += bf_hi(rv[b].y);
       if (a.res_out && blockIdx.x == 0 && b < a.rows)
         reinterpret_cast<uint2*>(a.res_out + (size_t)b * K)[tid] =
             make_uint2(pack_bf16(x[b][0], x[b][1]), pack_bf16(x[b][2], x[b][3]));

@@ -16,6 +16,7 @@
 //     (store / SwiGLU / logits + greedy argmax) is done by one thread per row.
 #pragma once
 
+#include "dfb_exchange.cuh"
 #include "dfb_kernels.cuh"
 
 namespace dfb {
@@ -112,8 +113,26 @@ row_gemv_kernel(const GemvArgs a) {
           hv = __ldcg(reinterpret_cast<const uint2*>(a.x + xrow * K) + tid);
           if (a.res_in) rv = __ldcg(reinterpret_cast<const uint2*>(a.res_in + (size_t)b * K) + tid);
         }
-        x[b][0] = bf_lo(hv.x) + bf_lo(rv.x); x[b][1] = bf_hi(hv.x) + bf_hi(rv.x);
-        x[b][2] = bf_lo(hv.y) + bf_lo(rv.y); x[b][3] = bf_hi(hv.y) + bf_hi(rv.y);
+        x[b][0] = bf_lo(hv.x); x[b][1] = bf_hi(hv.x); x[b][2] = bf_lo(hv.y); x[b][3] = bf_hi(hv.y);
+        if (a.tp_mode == 2) {
+          // tensor parallel: hv is this rank's partial projection; add the peers' (pushed into this rank's
+          // window by their projection kernels) in rank order and round once, like the unfused exchange
+          const unsigned int tag = exchange_tag(a.tp_step, a.tp_slot);
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < a.tp_size; ++r) {
+            if (r == a.tp_rank) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) acc[e] += x[b][e];
+            } else {
+              uint32_t d[1][2];
+              pull_words<1>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, b * 512 + 2 * tid, 1, tag, a.status, d);
+              acc[0] += bf_lo(d[0][0]); acc[1] += bf_hi(d[0][0]); acc[2] += bf_lo(d[0][1]); acc[3] += bf_hi(d[0][1]);
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[b][e] = round_bf16(acc[e]);
+        }
+        x[b][0] += bf_lo(rv.x); x[b][1] += bf_hi(rv.x); x[b][2] += bf_lo(rv.y); x[b][3] += bf_hi(rv.y);
         if (a.res_out && blockIdx.x == 0)
           reinterpret_cast<uint2*>(a.res_out + (size_t)b * K)[tid] =
               make_uint2(pack_bf16(x[b][0], x[b][1]), pack_bf16(x[b][2], x[b][3]));
@@ -239,13 +258,30 @@ row_gemv_kernel(const GemvArgs a) {
     if (probe && it == 0) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
     __syncthreads();
     if (MODE == kModeStore) {
-      // narrow shards have fewer threads than outputs of a group: loop
-      for (int t = tid; t < RC * NB; t += C::kThreads) {
-        const int b = t / RC, r = t % RC;
+      // narrow shards have fewer threads than outputs of a group: loop (same trip count for every thread)
+      const bool push = a.tp_mode == 1;
+      const unsigned int tag = push ? exchange_tag(a.tp_step, a.tp_slot) : 0u;
+      for (int t0 = 0; t0 < RC * NB; t0 += C::kThreads) {
+        const int t = t0 + tid;
+        const bool act = t < RC * NB;
+        const int b = act ? t / RC : 0, r = act ? t % RC : 0;
         float v = 0.f;
+        if (act) {
 #pragma unroll
-        for (int w = 0; w < W; ++w) v += red[w][b][r];
-        if (b < a.rows) a.out[(size_t)b * a.out_stride + grp * RC + r] = __float2bfloat16_rn(v);
+          for (int w = 0; w < W; ++w) v += red[w][b][r];
+        }
+        v = round_bf16(v);
+        const float vn = __shfl_down_sync(0xffffffffu, v, 1);   // the next row's value (same batch row: RC is even)
+        if (act && b < a.rows) {
+          a.out[(size_t)b * a.out_stride + grp * RC + r] = __float2bfloat16_rn(v);
+          if (push && !(r & 1)) {
+            // tensor parallel: the same two values as one tagged word into every peer's window
+            const uint2 word = make_uint2(pack_bf16(v, vn), tag);
+            const size_t wi = (size_t)b * 512 + (size_t)(grp * RC + r) / 2;
+            for (int p = 0; p < a.tp_size; ++p)
+              if (p != a.tp_rank) inbox_words(a.tp_window[p], a.tp_slot & 1, a.tp_rank)[wi] = word;
+          }
+        }
       }
     } else {
       float v = 0.f;

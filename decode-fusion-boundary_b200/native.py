@@ -25,7 +25,7 @@ DFB_TP_HANDLE_BYTES = 64
 DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
 DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS, DFB_OPT_ROW_GEMV, DFB_OPT_ATTN_WIDE = 5, 6, 7, 8
 DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER, DFB_OPT_PAIR_GEMV = 9, 10, 11, 12
-DFB_OPT_BULK_X = 13
+DFB_OPT_BULK_X, DFB_OPT_TP_FUSED = 13, 14
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -158,6 +158,8 @@ typedef struct DfbStatus {
                                   0 = 8 weight rows per MMA (stream_gemv_kernel) (process-wide) */
 #define DFB_OPT_BULK_X 13       /* FP32 chain: 1 (default) = the fused norm fetches x and the residual with bulk
                                   copies (TMA), 0 = with ordinary loads (process-wide) */
+#define DFB_OPT_TP_FUSED 14     /* tensor parallel over peer windows: 1 (default) = the projections push and the next
+                                  fused norm pulls the partial results, 0 = a separate exchange kernel (per decoder) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

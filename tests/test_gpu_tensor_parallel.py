@@ -41,7 +41,7 @@ def _world_sizes():
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("transport", ["direct", "nccl"])
+@pytest.mark.parametrize("transport", ["direct", "direct_unfused", "nccl"])
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_tensor_parallel_matches_unsharded_oracle(world, use_graph, transport, tmp_path):
     if world not in _world_sizes():

@@ -32,7 +32,7 @@ def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int
 
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     torch.cuda.set_device(rank)
-    group = TensorParallelGroup.create(dist, rank, transport=transport)
+    group = TensorParallelGroup.create(dist, rank, transport="nccl" if transport == "nccl" else "direct")
     seed = 5
     g = H.oracle_geometry(layers=layers, vocab=vocab)
     w = O.make_weights(g, seed=seed, norm="random").to(torch.bfloat16)
@@ -49,6 +49,9 @@ def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int
     kv_gpu = kv[:, :, :, :, h0:h1, :].contiguous().cuda()
     dec = StreamDecoder(local, kv_gpu[0], kv_gpu[1], block_size=g.block_size, num_cache_blocks=nblocks,
                         max_model_len=g.max_pos, use_graph=use_graph, tensor_parallel=group)
+    if transport == "direct_unfused":   # the exchange as a kernel of its own instead of inside the projections
+        from dfb_b200 import native
+        dec.set_option(native.DFB_OPT_TP_FUSED, 0)
     dist.barrier()   # the ranks start their first step together (the exchange waits are bounded)
     rows = len(prompts)
     lens = [n + 1 for n in prompt_lens]
