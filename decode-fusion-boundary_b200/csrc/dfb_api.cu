@@ -227,7 +227,7 @@ void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
 // Tensor-core GEMV with 16 weight rows per MMA (dfb_pairgemv.cuh), K = 1024, 3..8 batch rows.
 int g_pair_gemv = 1;   // 0: use stream_gemv_kernel (8 weight rows per MMA) instead
 template <int PSTAGES, int MODE>
-void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
+void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true, int carve = -2) {
   static bool configured = false;
   constexpr int smem = PairSmem::bytes(PSTAGES);
   auto kernel = pair_gemv_kernel<PSTAGES, MODE>;
@@ -237,7 +237,10 @@ void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
     configured = true;
   }
   a.trace = L.next_trace();
+  const int chain_carve = L.carve;
+  if (carve != -2) L.carve = carve;   // this kernel wants another L1/shared split than the rest of its chain
   L.launch(kernel, dim3(grid), dim3(256), a, allow_pdl, smem);
+  L.carve = chain_carve;
 }
 
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
@@ -369,11 +372,13 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
   } else if (g_pair_gemv && m.vocab % 16 == 0) {
+    // The LM head is long enough to be bound by its per-tile CTA barrier with one CTA per SM: two CTAs of two
+    // stages each (93 KB) overlap one another's barriers; that needs more shared memory than the chain's split.
     a.n_tiles = m.vocab / 16;
-    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
+    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 2 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     tp_fill(L, L.tp, a, false);
-    launch_pair<3, kModeNormArgmax>(L, a, grid);
+    launch_pair<2, kModeNormArgmax>(L, a, grid, true, 100);
   } else {
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;

@@ -33,16 +33,8 @@ struct PairSmem {
   static constexpr int bytes(int stages) { return stages * kStageBytes + kXBytes + 8 * stages + 16; }
 };
 
-__device__ __forceinline__ void mma_bf16_16816_full(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                                    uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 template <int PSTAGES, int MODE>
-__global__ void __launch_bounds__(256, 1) pair_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   constexpr bool kNorm = MODE != kModeStore;
   constexpr int K = PairSmem::kK, kWarps = 8;
   using SM = PairSmem;
