@@ -218,3 +218,30 @@ def test_capacity_errors(cuda_device):
         dec.decode_host([1], [5000], [[0]])          # position beyond max_model_len
     assert dec.decode_rows(torch.zeros(0, dtype=torch.int64, device="cuda"), None, None) == []
     dec.close()
+
+
+def test_option_and_tensor_parallel_argument_errors(cuda_device):
+    """Bad option values and tensor-parallel misuse are refused with an error code, not acted on."""
+    import ctypes as C
+
+    from dfb_b200 import native
+
+    g, w, kv, tables, first = _setup([10], seed=23)
+    dec = H.make_decoder(w, kv.cuda())
+    lib, h = native.lib(), dec._handle
+    for opt, bad in ((native.DFB_OPT_ROW_GEMV, 9), (native.DFB_OPT_STEP_MODE, 2), (native.DFB_OPT_SMEM_CARVEOUT, 101),
+                     (native.DFB_OPT_SMEM_CARVEOUT_MMA, -2), (native.DFB_OPT_LATE_TRIGGER, 2),
+                     (native.DFB_OPT_PAIR_GEMV, 5), (native.DFB_OPT_BULK_X, -1), (native.DFB_OPT_TP_FUSED, 3),
+                     (native.DFB_OPT_ATTN_WIDE, -1), (99, 0)):
+        assert lib.dfb_set_option(h, opt, bad) == -1, (opt, bad)          # DFB_E_BAD_ARG
+    # a single-GPU decoder has no exchange window, and a tensor-parallel group needs 2, 4 or 8 ranks
+    buf = C.create_string_buffer(native.DFB_TP_HANDLE_BYTES)
+    assert lib.dfb_tp_window_handle(h, buf) == -1
+    assert lib.dfb_tp_open_peers(h, buf) == -1
+    for size, rank in ((3, 0), (1, 0), (2, 2), (2, -1)):
+        tp = native.DfbTensorParallel(size=size, rank=rank, vocab_offset=0, dtype_bf16=9, dtype_int8=0, op_sum=0)
+        assert lib.dfb_set_tensor_parallel(h, C.byref(tp)) == -1, (size, rank)
+    assert lib.dfb_set_tensor_parallel(h, None) == -1
+    # the decoder still works after the refused calls
+    assert len(dec.decode_host([first[0]], [10], [tables[0][:1]])) == 1
+    dec.close()
