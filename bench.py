@@ -107,7 +107,7 @@ class BenchSeq:
         return self._n
 
 
-def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None):
+def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None, warmup=1):
     """The CPU oracle (fp32, the reference's torch-path arithmetic) on the same
     workload shape: returns (tokens/s, steps done, seconds, threads)."""
     import torch
@@ -118,7 +118,7 @@ def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None):
     g = O.QWEN3_06B
     w = O.make_weights(g, seed=0, norm="ones")
     cos_sin = O.rope_cos_sin_table(g)
-    tables, nblocks = O.allocate_blocks([prompt_len + steps + 1] * batch, g.block_size)
+    tables, nblocks = O.allocate_blocks([prompt_len + steps + warmup + 1] * batch, g.block_size)
     kv = O.new_kv_cache(g, nblocks, torch.float32)
     import numpy as np
     rng = np.random.Generator(np.random.Philox(key=1234))
@@ -126,8 +126,11 @@ def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None):
     lens = [prompt_len] * batch
     if prompt_len > 1:  # fill the history with random K/V instead of timing a prefill
         kv.normal_(0, 1)
-    done, t0 = 0, time.perf_counter()
-    O.decode_step(w, kv, cos_sin, cur, [n - 1 for n in lens], tables)  # warm-up (page-in, thread pool)
+    done = 0
+    for _ in range(max(warmup, 1)):   # untimed warm-up steps (page-in, thread pool), same feedback as the timed ones
+        _, nxt = O.decode_step(w, kv, cos_sin, cur, [n - 1 for n in lens], tables)
+        cur = [int(t) for t in nxt]
+        lens = [n + 1 for n in lens]
     t0 = time.perf_counter()
     while done < steps and time.perf_counter() - t0 < budget_s:
         _, nxt = O.decode_step(w, kv, cos_sin, cur, [n - 1 for n in lens], tables)
@@ -143,10 +146,10 @@ def run_reference_arm(args):
     if rank != 0:
         return
     budget = 60.0
-    tps, done, dt, threads = cpu_reference_run(args.batch, args.prompt, args.steps, budget)
+    tps, done, dt, threads = cpu_reference_run(args.batch, args.prompt, args.steps, budget, warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
-        "warmup": 1, "ms_per_step": 1e3 * dt / max(done, 1), "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(done, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, n_gpus=args.gpus),
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
