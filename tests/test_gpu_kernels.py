@@ -76,8 +76,10 @@ def test_rmsnorm_qkv_embedding_gather(small):
     assert ok, d
 
 
-@pytest.mark.parametrize("n,k", [(1024, 2048), (1024, 3072), (4096, 1024)])
-@pytest.mark.parametrize("rows", [1, 4, 8])
+@pytest.mark.parametrize("n,k", [(1024, 2048), (1024, 3072), (4096, 1024),
+                                 # o_proj / down_proj of the tensor-parallel shards (1/2, 1/4, 1/8 of 2048 and 3072)
+                                 (1024, 1024), (1024, 512), (1024, 256), (1024, 1536), (1024, 768), (1024, 384)])
+@pytest.mark.parametrize("rows", [1, 2, 4, 8])
 def test_linear(cuda_device, n, k, rows):
     from dfb_b200 import native
     x, wt = _rand((rows, k), 3), _rand((n, k), 4, 0.02)
