@@ -157,7 +157,7 @@ row_gemv_kernel(const GemvArgs a) {
       y.z = round_bf16(round_bf16(x[b][2] * rstd) * w2); y.w = round_bf16(round_bf16(x[b][3] * rstd) * w3);
       reinterpret_cast<float4*>(xs[b])[tid] = y;
     }
-  } else {
+  } else if (NB > 2) {
 #pragma unroll
     for (int b = 0; b < NB; ++b)
       for (int c = tid; c < K / 8; c += C::kThreads) {
@@ -173,7 +173,8 @@ row_gemv_kernel(const GemvArgs a) {
         reinterpret_cast<float4*>(xs[b])[2 * c + 1] = make_float4(f[4], f[5], f[6], f[7]);
       }
   }
-  __syncthreads();
+  constexpr bool kDirectX = !kNorm && NB <= 2;   // plain x, one or two rows: each lane loads its 8 values itself
+  if (!kDirectX) __syncthreads();
   if (a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
   if (probe) { c1 = clock64(); a.trace[5] = (unsigned long long)(c1 - c0); }
@@ -182,6 +183,14 @@ row_gemv_kernel(const GemvArgs a) {
   float xr[NB <= 2 ? NB : 1][8];
 #pragma unroll
   for (int b = 0; b < (NB <= 2 ? NB : 0); ++b) {
+    if (kDirectX) {
+      if (b < a.rows) unpack8(ldg_cg(a.x + (size_t)b * K + col), xr[b]);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xr[b][e] = 0.f;
+      }
+      continue;
+    }
     const float4 x0 = *reinterpret_cast<const float4*>(&xs[b][col]);
     const float4 x1 = *reinterpret_cast<const float4*>(&xs[b][col + 4]);
     xr[b][0] = x0.x; xr[b][1] = x0.y; xr[b][2] = x0.z; xr[b][3] = x0.w;
