@@ -9,8 +9,8 @@ capture any of them from this driver, e.g. (one GPU, small case):
         -o prof python decode-fusion-boundary_b200/profile_step.py --layers 1 --lmhead-only 4
 
 ``--mode chained`` (default) runs the step as the chain of per-op kernels
-(``row_gemv_kernel`` for one or two rows, ``stream_gemv_kernel`` above that,
-``paged_attention_kernel``), ``--mode persistent`` as the single persistent
+(``row_gemv_kernel`` for one or two rows, ``pair_gemv_kernel`` / ``stream_gemv_kernel``
+above that, ``paged_attention_kernel``), ``--mode persistent`` as the single persistent
 kernel; ``--no-graph`` launches directly instead of replaying a CUDA graph.  Weights are seeded random
 values; the KV history is random; nothing here checks results (the tests do).
 """
