@@ -3,7 +3,6 @@
 of the whole batch).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--batch B] [--prompt P] [--sweep]
 
 Default workload (N=1): batch 1, a one-token prompt (context 1), bf16
 random-init weights of the Qwen3-0.6B geometry, W + K greedy decode steps, so
@@ -11,17 +10,31 @@ the step is pure weight streaming (1,192,099,840 B per step).
 
 Prints ONE JSON line.  ``value`` is whole-job decode tokens/s with every input
 resident on the device (CUDA events around K back-to-back steps, tokens fed
-back on the device); ``e2e`` is the same metric through the user-facing
-``MegakernelBackend.decode`` / ``decode_batch`` call with host inputs, i.e. one
-host-to-device copy, the step, one device-to-host copy and one synchronisation
-per step; ``roofline`` is the LM-head + argmax kernel (the largest single kernel)
-timed alone, ``step_floor`` relates the whole step to its byte floor; ``cpu_baseline`` is the CPU oracle (a port of the reference torch path)
-timed on the host cores for a bounded number of steps.
+back on the device), the median of ``--repeats`` timed loops with their spread;
+``e2e`` is the same metric through the user-facing ``MegakernelBackend.decode``
+/ ``decode_batch`` call with host inputs (one host-to-device copy, the step,
+one device-to-host copy and one synchronisation per step); ``step_floor``
+relates the whole step to its byte floor; ``kernels`` lists the six kernels of
+the step, each timed alone through its standalone C-ABI launcher over all 28
+layers' weights (cold in L2, as inside a step) together with its share of the
+live step's time taken from the library's own timeline; ``roofline`` is the
+entry of that list with the largest share of the step's time; ``sweep`` holds
+batch 1/2/4/8 at prompt 512 and the long-context point (batch 8, per-row
+contexts uniform in [256, 2048), seeded block-table permutation) next to the
+reference's torch-CUDA-graph arm; ``cpu_baseline`` is the CPU oracle (a port of
+the reference torch path) timed on the host cores for a bounded number of
+steps.
 
-``--impl reference`` times that CPU path alone with all host threads.
-With ``--gpus N`` (launched by torchrun) every rank runs an independent replica
-of the workload (the step has no cross-sequence exchange): weak scaling, value
-= tokens of all ranks / max-over-ranks time.
+``--impl reference`` times that CPU path alone with all host threads.  With
+``--gpus N`` (launched by torch.distributed.run) every rank runs an independent
+replica of the workload (the step has no cross-sequence exchange: weak scaling,
+value = tokens of all ranks / max-over-ranks time) and the line also carries a
+``tensor_parallel`` block: ONE model sharded over the N ranks (batch 8, context
+1024), device time as the max over ranks.
+
+Profiling drivers (no JSON contract): ``--profile-step`` runs a few plain steps
+or standalone LM-head launches for Nsight Compute; ``--cta-sweep`` prints the
+per-op time of the persistent kernel against its CTA count.
 """
 
 from __future__ import annotations
@@ -29,6 +42,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -42,9 +56,11 @@ sys.path.insert(0, str(ROOT))
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head launch, from the
-# Nsight Compute capture summarised under profiles/ (batch 1, full vocabulary).
-LMHEAD_DRAM_TRAFFIC_BYTES = 316_430_080
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of each kernel at batch 1, from the Nsight
+# Compute captures summarised under profiles/ (None: not captured).
+DRAM_TRAFFIC_BYTES = {
+    "lm_head_argmax": 316_430_080,
+}
 
 
 def measured_peaks():
@@ -107,9 +123,21 @@ class BenchSeq:
         return self._n
 
 
+def spread(values):
+    """min / max / coefficient of variation of repeated measurements (the
+    reference reports mean, CoV, p50 and p95 of its runs: metrics.py:45-119)."""
+    m = statistics.fmean(values)
+    sd = statistics.pstdev(values) if len(values) > 1 else 0.0
+    return {"min": min(values), "max": max(values), "mean": m, "cov": sd / m if m else 0.0, "n": len(values)}
+
+
+# ----------------------------------------------------------------------------------------------------------
+# CPU reference arm (the oracle port of the reference torch path)
+# ----------------------------------------------------------------------------------------------------------
 def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None, warmup=1):
     """The CPU oracle (fp32, the reference's torch-path arithmetic) on the same
     workload shape: returns (tokens/s, steps done, seconds, threads)."""
+    import numpy as np
     import torch
     from oracle import qwen3_decode as O
 
@@ -120,7 +148,6 @@ def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None, warmup=1
     cos_sin = O.rope_cos_sin_table(g)
     tables, nblocks = O.allocate_blocks([prompt_len + steps + warmup + 1] * batch, g.block_size)
     kv = O.new_kv_cache(g, nblocks, torch.float32)
-    import numpy as np
     rng = np.random.Generator(np.random.Philox(key=1234))
     cur = rng.integers(0, g.vocab, batch).tolist()
     lens = [prompt_len] * batch
@@ -142,19 +169,24 @@ def cpu_reference_run(batch, prompt_len, steps, budget_s, threads=None, warmup=1
 
 
 def run_reference_arm(args):
+    """``--impl reference``: rank 0 alone times the CPU path with every host core
+    (torch.distributed.run exports OMP_NUM_THREADS=1, so the thread count is set
+    explicitly); the other ranks exit without work."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    budget = 60.0
-    tps, done, dt, threads = cpu_reference_run(args.batch, args.prompt, args.steps, budget, warmup=args.warmup)
+    cores = os.cpu_count() or 1
+    tps, done, dt, threads = cpu_reference_run(args.batch, args.prompt, args.steps, 60.0, threads=cores,
+                                               warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(done, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, n_gpus=args.gpus),
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{done} decode steps of the same workload on the host CPU (fp32 oracle port "
-                                   f"of the reference torch path; the Python reference itself cannot travel)"},
+                         "sample": f"{done} decode steps of the same workload on the host CPU, all {threads} host "
+                                   "threads (fp32 oracle port of the reference torch path; one CPU job whatever "
+                                   "the number of GPUs of the other arm)"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -168,28 +200,9 @@ def workload_config(args, n_gpus):
             "l2_policy": "inputs larger than L2 (1.19 GB of weights streamed per step)"}
 
 
-def time_step_loop(dec, torch, batch, prompt, warmup, steps, block_size, tables):
-    """Device-resident loop: tokens fed back on the device, positions and block
-    tables prepared before the timed region.  Returns ms for `steps` steps."""
-    total = warmup + steps
-    pos_all = torch.arange(prompt - 1, prompt - 1 + total, dtype=torch.int64, device="cuda").repeat(batch, 1).t().contiguous()
-    first_ids = torch.randint(0, 151936, (batch,), dtype=torch.int64, device="cuda")
-    pages = -(-(prompt + total) // block_size)
-    bt = torch.tensor([t[:pages] for t in tables], dtype=torch.int32, device="cuda")
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for s in range(total):
-        if s == warmup:
-            torch.cuda.synchronize()
-            barrier()
-            start.record()
-        ctx = prompt + s
-        dec.enqueue_rows(first_ids if s == 0 else None, pos_all[s], bt[:, : -(-ctx // block_size)], max_context=ctx)
-    stop.record()
-    torch.cuda.synchronize()
-    barrier()
-    return start.elapsed_time(stop)
-
-
+# ----------------------------------------------------------------------------------------------------------
+# timed loops
+# ----------------------------------------------------------------------------------------------------------
 _DIST = None
 
 
@@ -203,229 +216,188 @@ def max_over_ranks(torch, value):
     return replicas.aggregate(_DIST, 0, value, device="cuda")[1]
 
 
-def run_tensor_parallel_arm(args):
-    """``--tp``: ONE model sharded over the ranks (strong scaling), batch 8 at context
-    1024 by default.  Every rank holds 1/N of the projections, of the KV heads
-    and of the LM head; the partial results are summed with NCCL after o_proj and
-    down_proj.  Reports device us/step as the max over ranks next to the per-rank
-    byte floor."""
-    global _DIST
-    import torch
-    import torch.distributed as dist
-    import __graft_entry__  # noqa: F401
-    from dfb_b200 import native
-    from dfb_b200.decoder import StreamDecoder
-    from dfb_b200.geometry import QWEN3_06B
-    from dfb_b200.synthetic import random_init_weights
-    from dfb_b200.tensor_parallel import TensorParallelGroup, shard_weights
-
-    rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
-    if world not in (2, 4, 8):
-        raise SystemExit("--tp needs 2, 4 or 8 ranks (launch with torch.distributed.run)")
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    _DIST = dist
-    native.lib()
-    group = TensorParallelGroup.create(dist, local, transport="nccl" if args.tp_transport == "nccl" else "direct")
-    g = QWEN3_06B
-    B, P, W, K = args.batch, args.prompt, args.warmup, args.steps
-    if P + W + K > g.max_model_len:
-        raise SystemExit(f"prompt {P} + {W + K} steps exceeds max_model_len {g.max_model_len}")
-    full = random_init_weights(g, seed=0, norm="ones", device="cuda")
-    weights = shard_weights(full, rank, world)
-    del full.layers[:]          # the unsharded projections are not needed any more
-    lg = weights.geom
-    pages = g.max_pages
-    kv = torch.empty(2, g.layers, B * pages, g.block_size, lg.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
-    kv.normal_(0, 1)            # a random KV history stands in for the prefill of the prompt
-    tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
-    dec = StreamDecoder(weights, kv[0], kv[1], g.block_size, B * pages, g.max_model_len, tensor_parallel=group)
-    if args.tp_transport == "direct_unfused":
-        dec.set_option(native.DFB_OPT_TP_FUSED, 0)
-    barrier()
-    sampler = ClockSampler(local)
-    with sampler:
-        time_step_loop(dec, torch, B, P, 3, 5, g.block_size, tables)
-        ms = max_over_ranks(torch, time_step_loop(dec, torch, B, P, W, K, g.block_size, tables))
-    code, st = dec.status()
-    peak, peak_kind = measured_peaks()
-    contexts = [sum(P + W + s for s in range(K)) / K] * B
-    # bytes ONE rank streams per step: its shard of the layers and of the LM head, its KV heads
-    rank_bytes = (lg.layers * lg.layer_weight_bytes() + 2 * lg.hidden + lg.lm_head_bytes()
-                  + lg.kv_bytes_per_token() * int(sum(contexts)))
-    us = 1e3 * ms / K
-    line = {
-        "metric": METRIC, "value": B * K / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": f"Qwen3-0.6B geometry, bf16 random init (seed 0, N(0,0.02)), batch {B}, prompt {P} "
-                               f"token(s), greedy decode, KV block 256, one model over {world} GPUs",
-                   "batch": B, "prompt_tokens": P, "kv_block_size": 256, "parallelism": f"tp{world}",
-                   "collectives": ("exchange over peer-mapped memory fused into the kernels: o_proj / down_proj push "
-                                   "tagged words into the peers' windows, the next fused norm pulls them (bounded wait)"
-                                   if args.tp_transport == "direct" else
-                                   "own exchange kernel over peer-mapped memory (push tagged words, bounded wait) after "
-                                   "o_proj and down_proj" if args.tp_transport == "direct_unfused" else
-                                   "ncclAllReduce (bf16 sum) after o_proj and down_proj, ncclAllGather of the "
-                                   "per-rank greedy winners") + "; all captured in the step's CUDA graph",
-                   "l2_policy": "inputs larger than L2 per rank" if rank_bytes > 126e6 else "per-rank bytes fit in L2"},
-        "device_us_per_step": us,
-        "step_floor": {"bytes_per_step_per_rank": rank_bytes, "floor_us": rank_bytes / (peak * 1e3),
-                       "frac_of_floor": rank_bytes / (peak * 1e3) / us, "peak_gbs": peak, "peak": peak_kind},
-        "gpu_launches": (int(st.kernels_per_step) + 1) * K, "collectives_per_step": 2 * g.layers + 1,
-        "clocks": sampler.summary(), "device_status": int(st.device_status),
-    }
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    dec.close()
+def time_step_loop(dec, torch, prompts, warmup, steps, block_size, tables, sync=True):
+    """Device-resident loop: tokens fed back on the device, positions and block
+    tables prepared before the timed region.  ``prompts``: context length of every
+    row before the first step.  Returns ms for ``steps`` steps."""
+    batch, total = len(prompts), warmup + steps
+    base = torch.tensor([p - 1 for p in prompts], dtype=torch.int64, device="cuda")
+    pos_all = (base[None, :] + torch.arange(total, dtype=torch.int64, device="cuda")[:, None]).contiguous()
+    first_ids = torch.randint(0, 151936, (batch,), dtype=torch.int64, device="cuda")
+    top = max(prompts)
+    pages = -(-(top + total) // block_size)
+    bt = torch.tensor([t[:pages] for t in tables], dtype=torch.int32, device="cuda")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for s in range(total):
+        if s == warmup:
+            torch.cuda.synchronize()
+            if sync:
+                barrier()
+            start.record()
+        ctx = top + s
+        dec.enqueue_rows(first_ids if s == 0 else None, pos_all[s], bt[:, : -(-ctx // block_size)], max_context=ctx)
+    stop.record()
     torch.cuda.synchronize()
-    dist.barrier()
-    group.close()
-    dist.destroy_process_group()
+    if sync:
+        barrier()
+    return start.elapsed_time(stop)
 
 
-def run_own_arm(args):
-    global _DIST
-    import torch
-    import __graft_entry__  # noqa: F401
-    from dfb_b200 import MegakernelBackend, native
-    from dfb_b200.geometry import QWEN3_06B
-    from dfb_b200.synthetic import nano_model_view, random_init_weights
+def step_timeline(dec, torch, native, prompts, block_size, tables):
+    """One traced step (the library's own globaltimer timeline): how much of the
+    step's span each kernel kind accounts for, attributing to every kernel the time
+    from its predecessor's end to its own end."""
+    batch = len(prompts)
+    top = max(prompts)
+    pages = -(-(top + 4) // block_size)
+    bt = torch.tensor([t[:pages] for t in tables], dtype=torch.int32, device="cuda")
+    ids = torch.randint(0, 151936, (batch,), dtype=torch.int64, device="cuda")
+    pos = torch.tensor([p - 1 for p in prompts], dtype=torch.int64, device="cuda")
+    dec.set_option(native.DFB_OPT_TRACE, 1)
+    names = ("rmsnorm_qkv", "attention", "o_proj", "rmsnorm_gateup_swiglu", "down_proj")
+    shares = {n: 0.0 for n in names + ("lm_head_argmax",)}
+    span = 0.0
+    try:
+        for _ in range(3):      # the last traced step counts (the first ones capture the graph and warm up)
+            dec.read_trace()
+            dec.enqueue_rows(ids, pos, bt, max_context=top)
+            torch.cuda.synchronize()
+        t = dec.read_trace()
+        n = len(t)
+        if n >= 6 and (n - 1) % 5 == 0:
+            ends = [int(row[2]) for row in t]
+            prev = int(t[0][0])
+            for i in range(n):
+                name = "lm_head_argmax" if i == n - 1 else names[i % 5]
+                shares[name] += max(ends[i] - prev, 0) / 1e3
+                prev = max(prev, ends[i])
+            span = (max(ends) - int(t[0][0])) / 1e3
+    finally:
+        dec.set_option(native.DFB_OPT_TRACE, 0)
+    return shares, span
 
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        _DIST = dist
-    native.lib()  # no fallback: fail here if the CUDA library is missing
 
-    g = QWEN3_06B
-    B, P, W, K = args.batch, args.prompt, args.warmup, args.steps
-    total = W + K
-    if P + total > g.max_model_len:
-        raise SystemExit(f"prompt {P} + {total} steps exceeds max_model_len {g.max_model_len}")
-    weights = random_init_weights(g, seed=0, norm="ones", device="cuda")
-    model, hf = nano_model_view(weights)
+def time_kernels_alone(dec, torch, native, weights, g, batch, context, peak):
+    """Each kernel of the step alone through its standalone C-ABI launcher: one
+    CUDA graph holds the launches of all 28 layers (so every launch finds its
+    weights cold in L2, as inside a step), replayed and timed with CUDA events.
+    These launches are serialised (no programmatic dependent launch), which is the
+    view Nsight Compute has of them too."""
+    lib = native.lib()
+    B, L = batch, g.layers
+    bf = torch.bfloat16
+    h = torch.randn(B, g.hidden, device="cuda").to(bf)
+    res = torch.randn(B, g.hidden, device="cuda").to(bf)
+    res_out = torch.empty_like(res)
+    qkv = torch.randn(B, g.qkv_rows, device="cuda").to(bf)
+    attn = torch.randn(B, g.q_size, device="cuda").to(bf)
+    act = torch.randn(B, g.intermediate, device="cuda").to(bf)
+    hout = torch.empty(B, g.hidden, device="cuda", dtype=bf)
     pages = g.max_pages
-    kv_rows = 8 if args.sweep else B      # the sweep goes up to batch 8
-    kv = torch.zeros(2, g.layers, kv_rows * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
-    if P > 1:
-        kv.normal_(0, 1)  # a random KV history stands in for the prefill of the prompt
-    tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
-    config = SimpleNamespace(hf_config=hf, max_model_len=g.max_model_len, max_num_seqs=B, tensor_parallel_size=1,
-                             kvcache_block_size=g.block_size, decode_backend="megakernel")
-    backend = MegakernelBackend(config, model)
-    backend.set_kv_cache(kv)
-    backend.ensure_ready()
-    dec = backend.decoder
+    bt = torch.tensor([list(range(r * pages, (r + 1) * pages)) for r in range(B)], dtype=torch.int32, device="cuda")
+    pos = torch.full((B,), context - 1, dtype=torch.int32, device="cuda")
+    handle = dec._handle
 
-    sampler = ClockSampler(local)
-    with sampler:
-        # (1) device-resident throughput
-        time_step_loop(dec, torch, B, P, 3, 5, g.block_size, tables)   # graph capture + warm caches
-        ms = time_step_loop(dec, torch, B, P, W, K, g.block_size, tables)
-        ms = max_over_ranks(torch, ms)
+    def launches(name, stream):
+        for l, lw in enumerate(weights.layers):
+            if name == "rmsnorm_qkv":
+                rc = lib.dfb_launch_rmsnorm_qkv(h.data_ptr(), None, res.data_ptr(), res_out.data_ptr(), lw.ln_in.data_ptr(),
+                                                lw.wqkv.data_ptr(), qkv.data_ptr(), B, g.hidden, g.qkv_rows, g.eps, stream)
+            elif name == "attention":
+                rc = lib.dfb_launch_attention(handle, l, qkv.data_ptr(), pos.data_ptr(), bt.data_ptr(), pages, None,
+                                              attn.data_ptr(), B, context, stream)
+            elif name == "o_proj":
+                rc = lib.dfb_launch_linear(attn.data_ptr(), lw.wo.data_ptr(), hout.data_ptr(), B, g.hidden, g.q_size, stream)
+            elif name == "rmsnorm_gateup_swiglu":
+                rc = lib.dfb_launch_rmsnorm_gateup_swiglu(h.data_ptr(), res.data_ptr(), res_out.data_ptr(),
+                                                          lw.ln_post.data_ptr(), lw.wgu.data_ptr(), act.data_ptr(), B,
+                                                          g.hidden, g.intermediate, g.eps, stream)
+            else:
+                rc = lib.dfb_launch_linear(act.data_ptr(), lw.wd.data_ptr(), hout.data_ptr(), B, g.hidden,
+                                           g.intermediate, stream)
+            native.check(rc, name)
 
-        # (2) end to end through the backend's public call, host inputs, one sync per step
-        def e2e_loop(n_warm, n_timed):
-            cur = [int(t) for t in torch.randint(0, g.vocab, (B,)).tolist()]
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0 = 0.0
-            for s in range(n_warm + n_timed):
-                if s == n_warm:
-                    torch.cuda.synchronize(); barrier(); start.record(); t0 = time.perf_counter()
-                n_tok = P + s + 1            # the sampled token was appended before the step
-                nblk = -(-n_tok // g.block_size)
-                if B == 1:
-                    cur = backend.decode(BenchSeq(cur[0], n_tok, tables[0][:nblk]), tables[0][:nblk])
-                else:
-                    ids = torch.tensor(cur, dtype=torch.int64).pin_memory().cuda(non_blocking=True)
-                    pos = torch.tensor([n_tok - 1] * B, dtype=torch.int64).pin_memory().cuda(non_blocking=True)
-                    bt = torch.tensor([t[:nblk] for t in tables], dtype=torch.int32).pin_memory().cuda(non_blocking=True)
-                    cur = backend.decode_batch(ids, pos, bt)
-            stop.record(); torch.cuda.synchronize(); wall = time.perf_counter() - t0; barrier()
-            return start.elapsed_time(stop), wall
-        e2e_ms, e2e_wall = e2e_loop(W, K)
-        e2e_ms = max_over_ranks(torch, max(e2e_ms, 1e3 * e2e_wall))
-
-        # (3) the dominant kernel alone: LM head + argmax, 311 MB of weights per launch
-        lm_iters = 20
-        hid = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
-        res = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
-        stream = torch.cuda.current_stream().cuda_stream
-        lm = lambda: native.check(native.lib().dfb_launch_lmhead_argmax(
-            dec._handle, hid.data_ptr(), res.data_ptr(), None, None, B, stream), "lmhead")
-        for _ in range(3):
-            lm()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(); s0.record()
-        for _ in range(lm_iters):
-            lm()
-        s1.record(); torch.cuda.synchronize()
-        lm_ms = s0.elapsed_time(s1) / lm_iters
-    clocks = sampler.summary()
-    code, st = dec.status()
-    kernels_per_step = int(st.kernels_per_step) + 1   # + the input staging kernel
-    step_kernel = ("decode_step_persistent_kernel (whole step: 28 layers + LM head + argmax)"
-                   if int(st.kernels_per_step) == 1 else
-                   f"chain of {int(st.kernels_per_step)} kernels in one CUDA graph with programmatic dependent launch")
-    lm_kernel = ("row_gemv_kernel<1024,NB,NormArgmax> (LM head + greedy argmax, FP32 pipe)" if B <= 2 else
-                 "pair_gemv_kernel<3,NormArgmax> (LM head + greedy argmax, mma.sync with 16 weight rows per MMA)")
-
-    peak, peak_kind = measured_peaks()
-    lm_bytes = g.lm_head_bytes() + 2 * g.hidden
-    contexts = [sum(P + W + s for s in range(K)) / K] * B           # mean attended tokens per row
-    step_bytes = g.step_bytes(contexts)
-    us_per_step = 1e3 * ms / K
-    tok_s = world * B * K / (ms / 1e3)
-    line = {
-        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(args, world),
-        "device_us_per_step": us_per_step,
-        "step_floor": {"bytes_per_step": step_bytes, "floor_us": step_bytes / (peak * 1e3),
-                       "frac_of_floor": step_bytes / (peak * 1e3) / us_per_step, "peak_gbs": peak, "peak": peak_kind},
-        "e2e": {"value": world * B * K / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms / K,
-                "h2d_bytes_per_step": 4 * (24 + 8 * g.max_pages) if B == 1 else 8 * B * 2 + 4 * B * g.max_pages,
-                "d2h_bytes_per_step": 48, "api": "MegakernelBackend.decode" if B == 1 else "MegakernelBackend.decode_batch"},
-        "gpu_launches": kernels_per_step * K,
-        # the dominant kernel is the LM head + argmax kernel (26% of the step's bytes in one launch), timed alone
-        "roofline": {"kernel": lm_kernel, "bound": "hbm", "achieved": lm_bytes / (lm_ms * 1e6), "peak": peak,
-                     "unit": "GB/s", "frac": lm_bytes / (lm_ms * 1e6) / peak, "traffic": LMHEAD_DRAM_TRAFFIC_BYTES,
-                     "bytes_per_launch": lm_bytes, "us_per_launch": 1e3 * lm_ms, "peak_source": peak_kind},
-        "step_kernels": step_kernel,
-        "clocks": clocks,
-        "device_status": int(st.device_status),
+    kv_tok = 2 * g.kv_size * 2      # K and V bytes of one context token of one layer
+    per_launch = {
+        "rmsnorm_qkv": 2 * g.qkv_rows * g.hidden + 2 * g.hidden,
+        "attention": kv_tok * context * B + 4 * g.head_dim,
+        "o_proj": 2 * g.hidden * g.q_size,
+        "rmsnorm_gateup_swiglu": 2 * 2 * g.intermediate * g.hidden + 2 * g.hidden,
+        "down_proj": 2 * g.hidden * g.intermediate,
+        "lm_head_argmax": g.lm_head_bytes() + 2 * g.hidden,
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tps, done, dt, threads = cpu_reference_run(B, P, 400, budget_s=20.0)
-        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{done} decode steps of the same workload ({dt:.1f} s) by the fp32 CPU "
-                                          "oracle, a port of the reference torch path"}
-    if args.torch_arm and world == 1:
-        try:
-            line["torch_cudagraph"] = torch_cudagraph_arm(weights, g, B, P, W, K)
-        except Exception as exc:   # the comparison arm must never break the bench line
-            line["torch_cudagraph"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
-    if args.sweep and world == 1:
-        line["sweep"] = sweep(dec, torch, g, peak, weights if args.torch_arm else None)
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    dec.close()
-    if world > 1:
-        _DIST.destroy_process_group()
+    out = []
+    reps = 10
+    for name in ("rmsnorm_qkv", "attention", "o_proj", "rmsnorm_gateup_swiglu", "down_proj"):
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            launches(name, side.cuda_stream)       # warm-up outside the capture (function attributes, modules)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                launches(name, torch.cuda.current_stream().cuda_stream)
+            for _ in range(2):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            side.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / (reps * L)
+        out.append({"name": name, "launches_per_step": L, "bytes": per_launch[name], "us": us,
+                    "achieved_gbs": per_launch[name] / (us * 1e3), "frac": per_launch[name] / (us * 1e3) / peak})
+    # LM head + argmax: long enough to time with plain launches
+    hid = torch.randn(B, g.hidden, device="cuda").to(bf)
+    stream = torch.cuda.current_stream().cuda_stream
+    lm = lambda: native.check(lib.dfb_launch_lmhead_argmax(handle, hid.data_ptr(), res.data_ptr(), None, None, B, stream),
+                              "lmhead")
+    for _ in range(3):
+        lm()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(); s0.record()
+    for _ in range(20):
+        lm()
+    s1.record(); torch.cuda.synchronize()
+    us = 1e3 * s0.elapsed_time(s1) / 20
+    out.append({"name": "lm_head_argmax", "launches_per_step": 1, "bytes": per_launch["lm_head_argmax"], "us": us,
+                "achieved_gbs": per_launch["lm_head_argmax"] / (us * 1e3),
+                "frac": per_launch["lm_head_argmax"] / (us * 1e3) / peak})
+    return out
 
 
-def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=True):
-    """The reference's torch decode path restated on torch / cuBLAS ops, the way its
-    CUDA-graph arm runs it (engine/model_runner.py:292-313,379-416: the graph covers
-    the 28 layers, the LM head GEMM and the greedy sampler run outside it), on the
-    same weights and workload.  A comparison arm only: it uses library kernels
-    (cuBLAS, FlashAttention if it runs on this GPU, else SDPA) and is not part of
-    the backend.  Returns a dict with the device us/step."""
+# ----------------------------------------------------------------------------------------------------------
+# comparison arm: the reference's torch decode path with CUDA graphs
+# ----------------------------------------------------------------------------------------------------------
+def reference_cudagraph_points(points, steps):
+    """The unmodified reference engine (baseline/_ref), torch-cudagraph arm, in a
+    process of its own.  Returns {(batch, prompt): point} or {"unavailable": why}."""
+    script = ROOT / "baseline" / "reference_engine.py"
+    if not (ROOT / "baseline" / "_ref" / "nanovllm").exists():
+        return {"unavailable": "baseline/_ref not installed (sh baseline/install_reference.sh)"}
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS"):
+        env.pop(k, None)
+    spec = ",".join(f"{b}:{p}" for b, p in points)
+    try:
+        proc = subprocess.run([sys.executable, str(script), "--points", spec, "--steps", str(steps)], env=env,
+                              capture_output=True, text=True, timeout=900)
+        last = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+        if not last:
+            return {"unavailable": f"no output (rc {proc.returncode}): {proc.stderr[-300:]}"}
+        data = json.loads(last[-1])
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    if "unavailable" in data:
+        return {"unavailable": data["unavailable"]}
+    return {(p["batch"], p["prompt"]): p for p in data["points"]}
+
+
+def torch_cudagraph_standin(weights, g, batch, prompt, warmup, steps, use_compile=True):
+    """Fallback comparison arm when baseline/_ref is absent: the reference's torch
+    decode path restated on torch / cuBLAS / FlashAttention library kernels, the 28
+    layers in one CUDA graph and the LM head GEMM + argmax outside it
+    (engine/model_runner.py:292-313,379-416).  Labelled a stand-in wherever quoted."""
     import torch
     import torch.nn.functional as F
 
@@ -461,18 +433,12 @@ def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=Tr
         a, b = x.chunk(2, -1)
         return F.silu(a) * b
 
-    compiled = False
     if use_compile:
         try:
             rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (rms, add_rms, rope, silu_mul))
-            compiled = True
         except Exception:
-            compiled = False
-    attention = "flash_attn_with_kvcache"
-    try:
-        from flash_attn import flash_attn_with_kvcache
-    except Exception:
-        flash_attn_with_kvcache, attention = None, "sdpa"
+            pass
+    from flash_attn import flash_attn_with_kvcache
 
     st = dict(ids=torch.zeros(B, dtype=torch.int64, device=dev), pos=torch.zeros(B, dtype=torch.int64, device=dev),
               slots=torch.zeros(B, dtype=torch.int64, device=dev), lens=torch.zeros(B, dtype=torch.int32, device=dev),
@@ -483,14 +449,8 @@ def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=Tr
         D = g.kv_heads * g.head_dim
         kc.view(-1, D).index_copy_(0, st["slots"], k.reshape(B, D))
         vc.view(-1, D).index_copy_(0, st["slots"], v.reshape(B, D))
-        if attention == "flash_attn_with_kvcache":
-            return flash_attn_with_kvcache(q.unsqueeze(1), kc, vc, cache_seqlens=st["lens"], block_table=st["bt"],
-                                           softmax_scale=scale, causal=True).reshape(B, -1)
-        kk = kc[st["bt"].long()].reshape(B, pages * bs, g.kv_heads, g.head_dim).transpose(1, 2)
-        vv = vc[st["bt"].long()].reshape(B, pages * bs, g.kv_heads, g.head_dim).transpose(1, 2)
-        mask = (torch.arange(pages * bs, device=dev)[None, :] < st["lens"][:, None])[:, None, None, :]
-        o = F.scaled_dot_product_attention(q.unsqueeze(2), kk, vv, attn_mask=mask, scale=scale, enable_gqa=True)
-        return o.reshape(B, -1)
+        return flash_attn_with_kvcache(q.unsqueeze(1), kc, vc, cache_seqlens=st["lens"], block_table=st["bt"],
+                                       softmax_scale=scale, causal=True).reshape(B, -1)
 
     def model():
         h = F.embedding(st["ids"], weights.embed)
@@ -512,7 +472,7 @@ def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=Tr
         x, _ = add_rms(h, res, weights.final_norm)
         return x
 
-    def set_step(ctx):           # staging copies of the step's inputs, as prepare_decode does
+    def set_step(ctx):
         st["pos"].fill_(ctx - 1)
         st["lens"].fill_(ctx)
         blk, off = (ctx - 1) // bs, (ctx - 1) % bs
@@ -520,16 +480,8 @@ def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=Tr
 
     with torch.inference_mode():
         set_step(prompt)
-        try:
-            for _ in range(3):
-                model()
-        except Exception as exc:
-            if attention != "sdpa":
-                attention, flash_attn_with_kvcache = "sdpa", None
-                for _ in range(3):
-                    model()
-            else:
-                return {"unavailable": f"torch arm failed: {type(exc).__name__}: {exc}"[:200]}
+        for _ in range(3):
+            model()
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
@@ -545,39 +497,414 @@ def torch_cudagraph_arm(weights, g, batch, prompt, warmup, steps, use_compile=Tr
             st["ids"].copy_(logits.float().argmax(-1))
         e1.record()
         torch.cuda.synchronize()
-    us = 1e3 * e0.elapsed_time(e1) / steps
-    return {"device_us_per_step": us, "tok_s": B * 1e6 / us, "attention": attention, "compiled_elementwise": compiled,
-            "what": "restatement of the reference torch decode path (CUDA graph over the layers; LM head GEMM, argmax and "
-                    "input staging outside it) on torch / cuBLAS / FlashAttention library kernels, same weights and "
-                    "workload; the reference package itself is not present on the GPU box"}
+    return 1e3 * e0.elapsed_time(e1) / steps
 
 
-def sweep(dec, torch, g, peak, torch_arm_weights=None):
-    """Extra device-time points: batch 1/2/4/8 at context 512..639 and batch 8 at
-    mixed long contexts (not part of the headline line)."""
+def long_context_case(g, rows=8, seed=2024, steps=48):
+    """BASELINE config 4: per-row contexts uniform in [256, 2048 - steps) and a
+    seeded random permutation of the physical KV blocks."""
+    import numpy as np
+
+    rng = np.random.Generator(np.random.Philox(key=seed))
+    ctx = [int(c) for c in rng.integers(256, 2048 - steps - 16, rows)]
+    perm = rng.permutation(rows * g.max_pages).tolist()
+    tables = [perm[r * g.max_pages:(r + 1) * g.max_pages] for r in range(rows)]
+    return ctx, tables
+
+
+def sweep(dec, torch, g, peak, repeats):
+    """Device-time points beside the headline: BASELINE config 3 (batch 1/2/4/8,
+    prompt 512) and config 4 (batch 8, mixed long contexts, scattered blocks)."""
     out = []
     pages = g.max_pages
-    for B, P in ((1, 1), (1, 512), (2, 512), (4, 512), (8, 512), (8, 1920)):
-        if B * pages > dec._k_cache.shape[1]:
-            continue
-        tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
-        time_step_loop(dec, torch, B, P, 2, 4, g.block_size, tables)
-        ms = time_step_loop(dec, torch, B, P, 8, 120, g.block_size, tables)
-        ctx = [P + 8 + 59.5] * B
-        by = g.step_bytes(ctx)
-        us = 1e3 * ms / 120
-        entry = {"batch": B, "prompt": P, "device_us_per_step": us, "tok_s": B * 120 / (ms / 1e3),
-                 "floor_us": by / (peak * 1e3), "frac_of_floor": by / (peak * 1e3) / us}
-        if torch_arm_weights is not None:
-            try:
-                t = torch_cudagraph_arm(torch_arm_weights, g, B, P, 8, 120)
-                entry["torch_cudagraph_us_per_step"] = t.get("device_us_per_step")
-                entry["torch_attention"] = t.get("attention", t.get("unavailable"))
-            except Exception as exc:
-                entry["torch_cudagraph_us_per_step"] = None
-                entry["torch_attention"] = f"{type(exc).__name__}: {exc}"[:120]
-        out.append(entry)
+    W, K = 4, 48
+    cases = [(f"batch {B}, prompt 512", [512] * B, [list(range(r * pages, (r + 1) * pages)) for r in range(B)])
+             for B in (1, 2, 4, 8)]
+    ctx4, tables4 = long_context_case(g, steps=W + K)
+    cases.append(("batch 8, contexts uniform in [256, 2048), permuted block tables", ctx4, tables4))
+    for label, prompts, tables in cases:
+        B = len(prompts)
+        time_step_loop(dec, torch, prompts, 2, 3, g.block_size, tables, sync=False)
+        runs = [1e3 * time_step_loop(dec, torch, prompts, W, K, g.block_size, tables, sync=False) / K
+                for _ in range(max(repeats, 3))]
+        us = statistics.median(runs)
+        mean_ctx = [p + W + (K - 1) / 2 for p in prompts]
+        by = g.step_bytes(mean_ctx)
+        out.append({"case": label, "batch": B, "prompt": prompts if len(set(prompts)) > 1 else prompts[0],
+                    "device_us_per_step": us, "spread_us": spread(runs), "tok_s": B * 1e6 / us,
+                    "bytes_per_step": by, "floor_us": by / (peak * 1e3), "frac_of_floor": by / (peak * 1e3) / us})
     return out
+
+
+# ----------------------------------------------------------------------------------------------------------
+# tensor parallelism over the launched ranks
+# ----------------------------------------------------------------------------------------------------------
+def tensor_parallel_block(args, torch, dist, full_weights, local, transport="direct"):
+    """BASELINE config 5: ONE model over all ranks (KV heads 8/N per rank, MLP split
+    column/row, LM head by vocabulary), batch 8 at context 1024, device us/step as
+    the max over ranks, next to one GPU running the same workload and to the
+    per-rank byte floor.  Every rank must call this."""
+    from dfb_b200 import native
+    from dfb_b200.decoder import StreamDecoder
+    from dfb_b200.geometry import QWEN3_06B as g
+    from dfb_b200.tensor_parallel import TensorParallelGroup, shard_weights
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    B, P, W, K = 8, 1024, 4, max(16, min(args.steps, 64))
+    peak, peak_kind = measured_peaks()
+    pages = g.max_pages
+    tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
+    gen = torch.Generator(device="cuda").manual_seed(99)    # the same history on every rank
+    kv_full = torch.empty(2, g.layers, B * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv_full[0].normal_(0, 1.0, generator=gen)
+    kv_full[1].normal_(0, 0.64, generator=gen)
+    first_ids = torch.randint(0, g.vocab, (B,), dtype=torch.int64, device="cuda", generator=gen)
+
+    def run(dec, record):
+        """W + K steps from the same first ids; returns (ms for K steps, tokens per step)."""
+        total = W + K
+        pos_all = torch.arange(P - 1, P - 1 + total, dtype=torch.int64, device="cuda").repeat(B, 1).t().contiguous()
+        bt = torch.tensor([t[:-(-(P + total) // g.block_size)] for t in tables], dtype=torch.int32, device="cuda")
+        toks = torch.zeros(total, B, dtype=torch.int32, device="cuda")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for s in range(total):
+            if s == W:
+                torch.cuda.synchronize(); barrier(); e0.record()
+            ctx = P + s
+            dec.enqueue_rows(first_ids if s == 0 else None, pos_all[s], bt[:, : -(-ctx // g.block_size)], max_context=ctx)
+            if record:
+                toks[s].copy_(dec.tokens_device()[:B])
+        e1.record(); torch.cuda.synchronize(); barrier()
+        return e0.elapsed_time(e1), toks.cpu()
+
+    # one GPU, the same workload (every rank runs it, so that clocks and memory traffic are alike)
+    single = StreamDecoder(full_weights, kv_full[0], kv_full[1], g.block_size, B * pages, g.max_model_len)
+    run(single, False)
+    ms_single, toks_single = run(single, True)
+    ms_single_timed, _ = run(single, False)
+    single.close()
+    kv_local = kv_full[:, :, :, :, rank * (g.kv_heads // world):(rank + 1) * (g.kv_heads // world)].contiguous()
+    del kv_full
+    group = TensorParallelGroup.create(dist, local, transport="nccl" if transport == "nccl" else "direct")
+    weights = shard_weights(full_weights, rank, world)
+    lg = weights.geom
+    dec = StreamDecoder(weights, kv_local[0], kv_local[1], g.block_size, B * pages, g.max_model_len, tensor_parallel=group)
+    kv0 = kv_local.clone()
+    run(dec, False)
+    kv_local.copy_(kv0)
+    ms_rec, toks_tp = run(dec, True)
+    kv_local.copy_(kv0)
+    ms_tp, _ = run(dec, False)
+    ms_tp = max_over_ranks(torch, ms_tp)
+    ms_one = max_over_ranks(torch, ms_single_timed)
+    code, st = dec.status()
+    same = int((toks_tp == toks_single).all(dim=1).sum())
+    mean_ctx = P + W + (K - 1) / 2
+    rank_bytes = (lg.layers * lg.layer_weight_bytes() + 2 * lg.hidden + lg.lm_head_bytes()
+                  + lg.kv_bytes_per_token() * int(B * mean_ctx))
+    us = 1e3 * ms_tp / K
+    block = {
+        "workload": f"batch {B}, context {P}, {K} greedy steps, one model over {world} GPUs (KV heads "
+                    f"{g.kv_heads // world} per rank, MLP split column/row, LM head by vocabulary)",
+        "scaling": "strong", "ranks": world, "steps": K, "device_us_per_step": us, "tok_s": B * 1e6 / us,
+        "one_gpu_same_workload_us_per_step": 1e3 * ms_one / K, "speedup_over_one_gpu": ms_one / ms_tp,
+        "per_rank_bytes_per_step": rank_bytes, "per_rank_floor_us": rank_bytes / (peak * 1e3),
+        "frac_of_floor": rank_bytes / (peak * 1e3) / us, "peak_gbs": peak, "peak": peak_kind,
+        "exchanges_per_step": 2 * g.layers + 1,
+        "exchange": "o_proj / down_proj push {2 x bf16, tag} words into the peers' windows (peer-mapped memory, "
+                    "plain stores over NVLink), the next fused norm pulls them with a bounded wait; greedy winners "
+                    "merged the same way" if transport == "direct" else "ncclAllReduce / ncclAllGather in the graph",
+        "steps_with_tokens_equal_to_one_gpu": same, "steps_compared": int(toks_tp.shape[0]),
+        "device_status": int(st.device_status), "gpu_launches": (int(st.kernels_per_step) + 1) * K,
+    }
+    dec.close()
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
+    return block
+
+
+# ----------------------------------------------------------------------------------------------------------
+# this repository's arm
+# ----------------------------------------------------------------------------------------------------------
+def run_own_arm(args):
+    global _DIST
+    import torch
+    import __graft_entry__  # noqa: F401
+    from dfb_b200 import MegakernelBackend, native
+    from dfb_b200.geometry import QWEN3_06B
+    from dfb_b200.synthetic import nano_model_view, random_init_weights
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        _DIST = dist
+    native.lib()  # no fallback: fail here if the CUDA library is missing
+
+    g = QWEN3_06B
+    B, P, W, K = args.batch, args.prompt, args.warmup, args.steps
+    total = W + K
+    if P + total > g.max_model_len:
+        raise SystemExit(f"prompt {P} + {total} steps exceeds max_model_len {g.max_model_len}")
+    weights = random_init_weights(g, seed=0, norm="ones", device="cuda")
+    model, hf = nano_model_view(weights)
+    pages = g.max_pages
+    extras = world == 1 and not args.quick
+    kv_rows = 8 if extras else B      # the sweep goes up to batch 8
+    kv = torch.zeros(2, g.layers, kv_rows * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv[0].normal_(0, 1.0)             # a random KV history stands in for the prefill of the prompts:
+    kv[1].normal_(0, 0.64)            # K has unit RMS after its norm, V the scale of a N(0, 0.02) projection
+    tables = [list(range(r * pages, (r + 1) * pages)) for r in range(B)]
+    config = SimpleNamespace(hf_config=hf, max_model_len=g.max_model_len, max_num_seqs=kv_rows, tensor_parallel_size=1,
+                             kvcache_block_size=g.block_size, decode_backend="megakernel")
+    backend = MegakernelBackend(config, model)
+    backend.set_kv_cache(kv)
+    backend.ensure_ready()
+    dec = backend.decoder
+    peak, peak_kind = measured_peaks()
+
+    sampler = ClockSampler(local)
+    with sampler:
+        # (1) device-resident throughput: `repeats` timed loops of exactly K steps each
+        time_step_loop(dec, torch, [P] * B, 3, 5, g.block_size, tables)   # graph capture + warm caches
+        runs_ms = [max_over_ranks(torch, time_step_loop(dec, torch, [P] * B, W, K, g.block_size, tables))
+                   for _ in range(args.repeats)]
+        ms = statistics.median(runs_ms)
+
+        # (2) end to end through the backend's public call, host inputs, one sync per step
+        def e2e_loop(n_warm, n_timed):
+            cur = [int(t) for t in torch.randint(0, g.vocab, (B,)).tolist()]
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = 0.0
+            for s in range(n_warm + n_timed):
+                if s == n_warm:
+                    torch.cuda.synchronize(); barrier(); start.record(); t0 = time.perf_counter()
+                n_tok = P + s + 1            # the sampled token was appended before the step
+                nblk = -(-n_tok // g.block_size)
+                if B == 1:
+                    cur = backend.decode(BenchSeq(cur[0], n_tok, tables[0][:nblk]), tables[0][:nblk])
+                else:
+                    ids = torch.tensor(cur, dtype=torch.int64).pin_memory().cuda(non_blocking=True)
+                    pos = torch.tensor([n_tok - 1] * B, dtype=torch.int64).pin_memory().cuda(non_blocking=True)
+                    bt = torch.tensor([t[:nblk] for t in tables], dtype=torch.int32).pin_memory().cuda(non_blocking=True)
+                    cur = backend.decode_batch(ids, pos, bt)
+            stop.record(); torch.cuda.synchronize(); wall = time.perf_counter() - t0; barrier()
+            return max(start.elapsed_time(stop), 1e3 * wall)
+        e2e_runs = [max_over_ranks(torch, e2e_loop(W, K)) for _ in range(max(3, args.repeats // 2))]
+        e2e_ms = statistics.median(e2e_runs)
+
+        # (3) where the step's time goes: the library's own timeline of one live step, and every kernel alone
+        shares, span_us = ({}, 0.0)
+        kernels = []
+        if rank == 0:
+            shares, span_us = step_timeline(dec, torch, native, [P] * B, g.block_size, tables)
+            kernels = time_kernels_alone(dec, torch, native, weights, g, B, max(P, 1), peak)
+    clocks = sampler.summary()
+    code, st = dec.status()
+    kernels_per_step = int(st.kernels_per_step) + 1   # + the input staging kernel
+    step_kernel = ("decode_step_persistent_kernel (whole step: 28 layers + LM head + argmax)"
+                   if int(st.kernels_per_step) == 1 else
+                   f"chain of {int(st.kernels_per_step)} kernels in one CUDA graph with programmatic dependent launch")
+    total_share = sum(shares.values()) or 1.0
+    for k in kernels:
+        k["share_of_step"] = shares.get(k["name"], 0.0) / total_share
+        k["live_us_per_step"] = shares.get(k["name"], 0.0)
+        k["traffic"] = DRAM_TRAFFIC_BYTES.get(k["name"]) if B == 1 else None
+    top = max(kernels, key=lambda k: k["share_of_step"]) if kernels else None
+
+    contexts = [sum(P + W + s for s in range(K)) / K] * B           # mean attended tokens per row
+    step_bytes = g.step_bytes(contexts)
+    us_per_step = 1e3 * ms / K
+    tok_s = world * B * K / (ms / 1e3)
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args, world),
+        "repeats": args.repeats,
+        "spread": {k: (world * B * K / (v / 1e3) if k in ("min", "max", "mean") else v)
+                   for k, v in spread(runs_ms).items()},
+        "device_us_per_step": us_per_step,
+        "device_us_per_step_spread": spread([1e3 * r / K for r in runs_ms]),
+        "step_floor": {"bytes_per_step": step_bytes, "floor_us": step_bytes / (peak * 1e3),
+                       "frac_of_floor": step_bytes / (peak * 1e3) / us_per_step, "peak_gbs": peak, "peak": peak_kind},
+        "e2e": {"value": world * B * K / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms / K,
+                "h2d_bytes_per_step": 4 * (24 + 8 * g.max_pages) if B == 1 else 8 * B * 2 + 4 * B * g.max_pages,
+                "d2h_bytes_per_step": 48, "api": "MegakernelBackend.decode" if B == 1 else "MegakernelBackend.decode_batch",
+                "runs": len(e2e_runs)},
+        "gpu_launches": kernels_per_step * K,
+        "step_kernels": step_kernel,
+        "clocks": clocks,
+        "device_status": int(st.device_status),
+    }
+    if top is not None:
+        # the kernel with the largest share of the step's TIME (not bytes), timed alone over all layers' weights
+        line["roofline"] = {"kernel": top["name"], "bound": "hbm", "achieved": top["achieved_gbs"], "peak": peak,
+                            "unit": "GB/s", "frac": top["frac"], "traffic": top["traffic"],
+                            "bytes_per_launch": top["bytes"], "us_per_launch": top["us"],
+                            "share_of_step": top["share_of_step"], "peak_source": peak_kind}
+        line["kernels"] = kernels
+        line["timeline_span_us"] = span_us
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, done, dt, threads = cpu_reference_run(B, P, 400, budget_s=15.0, threads=os.cpu_count())
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{done} decode steps of the same workload ({dt:.1f} s) by the fp32 CPU "
+                                          "oracle, a port of the reference torch path"}
+    if extras:
+        line["sweep"] = sweep(dec, torch, g, peak, args.repeats)
+    dec.close()
+    del backend, dec
+    if extras and not args.no_torch_arm:
+        # the comparison arm runs last, in a process of its own, after this arm's decoder is closed
+        pts = [(1, 1), (1, 512), (2, 512), (4, 512), (8, 512), (8, 1150)]
+        torch.cuda.empty_cache()
+        ref = reference_cudagraph_points(pts, 64)
+        if "unavailable" in ref:
+            arm = {"arm": "stand-in: the reference torch decode path restated on torch / cuBLAS / FlashAttention "
+                          "kernels with CUDA graphs (the reference package is not installed here)",
+                   "why": ref["unavailable"], "points": []}
+            for b, p in pts:
+                try:
+                    arm["points"].append({"batch": b, "prompt": p,
+                                          "device_us_per_step": torch_cudagraph_standin(weights, g, b, p, 4, 48)})
+                except Exception as exc:
+                    arm["points"].append({"batch": b, "prompt": p, "unavailable": f"{type(exc).__name__}: {exc}"[:160]})
+        else:
+            arm = {"arm": "the unmodified reference engine (baseline/_ref): LLM(dir, decode_backend='torch', "
+                          "enforce_eager=False), CUDA graphs, same seeded weights; per decode step: the reference's own "
+                          "CUDA-event span, the host wall time and the summed GPU kernel time (torch.profiler)",
+                   "points": list(ref.values())}
+        line["torch_cudagraph"] = arm
+    if world > 1:
+        try:
+            line["tensor_parallel"] = tensor_parallel_block(args, torch, dist, weights, local)
+        except Exception as exc:
+            line["tensor_parallel"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        _DIST.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------------------
+# profiling drivers
+# ----------------------------------------------------------------------------------------------------------
+def run_profile_step(args):
+    """A few plain decode steps (or standalone LM-head launches) of a small or
+    full model for Nsight Compute; nothing here checks results (the tests do)."""
+    import torch
+    import __graft_entry__  # noqa: F401
+    from dfb_b200 import native
+    from dfb_b200.decoder import StreamDecoder
+    from dfb_b200.geometry import ModelGeometry
+    from dfb_b200.synthetic import random_init_weights
+
+    g = ModelGeometry(layers=args.layers, vocab=args.vocab)
+    w = random_init_weights(g, seed=0, device="cuda")
+    pages, B = g.max_pages, args.batch
+    kv = torch.empty(2, g.layers, B * pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    kv.normal_(0, 1)
+    dec = StreamDecoder(w, kv[0], kv[1], g.block_size, B * pages, g.max_model_len, use_graph=not args.no_graph,
+                        persistent=args.mode == "persistent")
+    if args.ctas:
+        dec.set_option(native.DFB_OPT_PERSIST_CTAS, args.ctas)
+    if args.row_gemv >= 0:
+        dec.set_option(native.DFB_OPT_ROW_GEMV, args.row_gemv)
+    tables = torch.tensor([list(range(r * pages, (r + 1) * pages)) for r in range(B)], dtype=torch.int32, device="cuda")
+    ids = torch.randint(0, g.vocab, (B,), dtype=torch.int64, device="cuda")
+    if args.lmhead_only:
+        hid = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
+        res = torch.randn(B, g.hidden, device="cuda").to(torch.bfloat16)
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(args.lmhead_only):
+            native.check(native.lib().dfb_launch_lmhead_argmax(dec._handle, hid.data_ptr(), res.data_ptr(), None, None,
+                                                               B, stream), "dfb_launch_lmhead_argmax")
+        torch.cuda.synchronize()
+        print(f"lm head launches={args.lmhead_only} rows={B} vocab={g.vocab}")
+        dec.close()
+        return
+    for s in range(args.steps):
+        ctx = args.prompt + s
+        pos = torch.full((B,), ctx - 1, dtype=torch.int64, device="cuda")
+        dec.enqueue_rows(ids if s == 0 else None, pos, tables[:, : -(-ctx // g.block_size)], max_context=ctx)
+    torch.cuda.synchronize()
+    code, st = dec.status()
+    print(f"steps={args.steps} mode={args.mode} device_status={st.device_status} kernels_per_step={st.kernels_per_step}")
+    dec.close()
+    if code:
+        raise SystemExit(1)
+
+
+def run_cta_sweep(args):
+    """Per-op time against the CTA count (the reference's TG_NUM_SMS diagnostic,
+    backends/megakernel/taskgraph.py:68-83): the persistent kernel at 1 ... 148
+    CTAs from its own timeline, and the LM-head kernel of the chain against its
+    grid size."""
+    import torch
+    import __graft_entry__  # noqa: F401
+    from dfb_b200 import native
+    from dfb_b200.decoder import StreamDecoder
+    from dfb_b200.geometry import QWEN3_06B as g
+    from dfb_b200.synthetic import random_init_weights
+
+    w = random_init_weights(g, seed=0, device="cuda")
+    pages = g.max_pages
+    kv = torch.zeros(2, g.layers, pages, g.block_size, g.kv_heads, g.head_dim, dtype=torch.bfloat16, device="cuda")
+    tables = [list(range(pages))]
+    out = {"persistent_kernel": [], "chain_lm_head": [], "chain_step": None}
+    ops = ("qkv", "attention", "o_proj", "gate_up", "down")
+    for ctas in (1, 16, 64, 108, 148):
+        dec = StreamDecoder(w, kv[0], kv[1], g.block_size, pages, g.max_model_len, persistent=True)
+        dec.set_option(native.DFB_OPT_PERSIST_CTAS, ctas)
+        steps = 2 if ctas == 1 else 16
+        time_step_loop(dec, torch, [1], 1, 2, g.block_size, tables, sync=False)
+        ms = time_step_loop(dec, torch, [1], 1, steps, g.block_size, tables, sync=False) / steps
+        dec.set_option(native.DFB_OPT_TRACE, 1)
+        ids = torch.randint(0, g.vocab, (1,), dtype=torch.int64, device="cuda")
+        pos = torch.zeros(1, dtype=torch.int64, device="cuda")
+        bt = torch.tensor([tables[0][:1]], dtype=torch.int32, device="cuda")
+        for _ in range(2):
+            dec.read_trace()
+            dec.enqueue_rows(ids, pos, bt, max_context=1)
+            torch.cuda.synchronize()
+        t = dec.read_trace()
+        per_op = {}
+        if len(t) == 5 * g.layers + 1:
+            for i, name in enumerate(ops):
+                rows = t[i:5 * g.layers:5]
+                per_op[name] = float(sum(int(r[2]) - int(r[0]) for r in rows)) / len(rows) / 1e3
+            per_op["lm_head"] = (int(t[-1][2]) - int(t[-1][0])) / 1e3
+        code, st = dec.status()
+        out["persistent_kernel"].append({"ctas": ctas, "ms_per_step": ms, "us_per_op": per_op,
+                                         "mean_us_per_op": 1e3 * ms / (5 * g.layers + 1),
+                                         "device_status": int(st.device_status)})
+        dec.close()
+    dec = StreamDecoder(w, kv[0], kv[1], g.block_size, pages, g.max_model_len)
+    time_step_loop(dec, torch, [1], 2, 3, g.block_size, tables, sync=False)
+    out["chain_step"] = {"ms_per_step": time_step_loop(dec, torch, [1], 4, 64, g.block_size, tables, sync=False) / 64}
+    hid = torch.randn(1, g.hidden, device="cuda").to(torch.bfloat16)
+    res = torch.randn(1, g.hidden, device="cuda").to(torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    for ctas in (16, 64, 108, 148, 296, 444, 592):
+        dec.set_option(native.DFB_OPT_LMHEAD_CTAS, ctas)
+        lm = lambda: native.check(native.lib().dfb_launch_lmhead_argmax(dec._handle, hid.data_ptr(), res.data_ptr(), None,
+                                                                        None, 1, stream), "lmhead")
+        for _ in range(3):
+            lm()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); e0.record()
+        for _ in range(10):
+            lm()
+        e1.record(); torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / 10
+        tiles = g.vocab // 16
+        out["chain_lm_head"].append({"ctas": ctas, "us": us, "us_per_tile_per_cta": us / (-(-tiles // ctas))})
+    dec.close()
+    print(json.dumps(out), flush=True)
 
 
 def main():
@@ -588,19 +915,32 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=1)
-    ap.add_argument("--sweep", action="store_true")
-    ap.add_argument("--torch-arm", action="store_true",
-                    help="also time a torch / cuBLAS / CUDA-graph restatement of the reference decode path")
+    ap.add_argument("--repeats", type=int, default=5, help="timed loops of --steps steps each; the median is reported")
+    ap.add_argument("--quick", action="store_true", help="headline only: no sweep and no comparison arm")
+    ap.add_argument("--no-torch-arm", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp-transport", default="direct", choices=["direct", "direct_unfused", "nccl"])
-    ap.add_argument("--tp", action="store_true",
-                    help="tensor parallelism over the launched ranks (one model, strong scaling) instead of replicas")
+    # profiling drivers
+    ap.add_argument("--profile-step", action="store_true", help="run plain steps for a profiler instead of the benchmark")
+    ap.add_argument("--cta-sweep", action="store_true", help="per-op time against the CTA count")
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--mode", choices=["persistent", "chained"], default="chained")
+    ap.add_argument("--lmhead-only", type=int, default=0, metavar="N")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--row-gemv", type=int, default=-1, help="profile driver: DFB_OPT_ROW_GEMV of the decoder")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    args.repeats = max(args.repeats, 1)
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # a rank that dies while its memory is bound to an NVLink multicast object faults its peers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if args.profile_step:
+        run_profile_step(args)
+    elif args.cta_sweep:
+        run_cta_sweep(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
-    elif args.tp:
-        run_tensor_parallel_arm(args)
     else:
         run_own_arm(args)
 

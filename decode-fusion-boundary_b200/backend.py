@@ -169,6 +169,17 @@ class MegakernelBackend:
         weights = weights_from_nano_model(
             self.model, self.config.hf_config, max_model_len=max_model_len,
             block_size=self.config.kvcache_block_size)
+        # Tensor parallel (this build's extension of the reference's tensor_parallel_size == 1 rule,
+        # taskgraph.py:119-122): the rank's nano-vLLM modules already hold its shards of the projections and
+        # of the vocabulary (layers/linear.py:54-153, layers/embed_head.py); the decoder needs the local
+        # shapes plus the whole embedding table for the token gather, collected once here.
+        group = _get_attr(self.config, "megakernel_tensor_parallel", None)
+        if group is not None and getattr(group, "size", 1) > 1:
+            from .tensor_parallel import localize_nano_weights
+
+            weights = localize_nano_weights(weights, group)
+        else:
+            group = None
         self.decoder = StreamDecoder(
             weights,
             k_cache=self.kv_cache[0],
@@ -180,6 +191,7 @@ class MegakernelBackend:
             fusion_groups=int(_get_attr(self.config, "fusion_groups", 1)),
             verbose=bool(_get_attr(self.config, "megakernel_verbose", False)),
             debug_bounds=bool(_get_attr(self.config, "megakernel_debug_bounds", False)),
+            tensor_parallel=group,
         )
 
     def decode_batch(self, input_ids, positions, block_tables) -> list[int]:

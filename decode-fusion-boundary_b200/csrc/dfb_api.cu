@@ -46,22 +46,50 @@ typedef __nv_bfloat16 bf16;
 // for the same split; otherwise a kernel that prefers another one starts late.
 // `percent` is the share of the SM's 228 KB that goes to shared memory (-1:
 // leave the choice to the driver).
-int g_bulk_x = 1;        // FP32 chain: the fused norm fetches its inputs with bulk copies (TMA) instead of loads
-int g_late_trigger = 0;  // FP32 chain: 1 = a kernel lets its successor start only after it has read its inputs
-int g_carve_fp32 = 12;   // chain of FP32 GEMV kernels: little shared memory, L1 helps
-int g_carve_mma = 50;    // chain of tensor-core GEMV kernels: room for the weight stages (up to 101 KB), the rest stays L1
+// Tuning knobs of the kernel chain.  Every decoder owns a copy (dfb_set_option
+// changes that decoder only); the standalone dfb_launch_* entry points use the
+// defaults.
+struct ChainOptions {
+  int row_max_rows = 2;        // largest batch that takes the FP32 GEMV kernels (0 = never)
+  int attn_wide_ctas = 2 * 148;// attention grids up to this many CTAs use 256-thread CTAs
+  int carve_fp32 = 12;         // chain of FP32 GEMV kernels: little shared memory, L1 helps
+  int carve_mma = 50;          // chain of tensor-core GEMV kernels: room for the weight stages, the rest stays L1
+  int late_trigger = 0;        // FP32 chain: 1 = a kernel lets its successor start only after it has read its inputs
+  int pair_gemv = 1;           // tensor-core chain, K = 1024: 16 weight rows per MMA; 0: stream_gemv_kernel
+  int bulk_x = 1;              // FP32 chain: the fused norm fetches its inputs with bulk copies (TMA) instead of loads
+  int look_ahead = 1;          // every kernel requests the weights of the kernel two places down the chain into L2
+  int lmhead_ahead_mb = 32;    // ... and the last layer's kernels this many MB of the LM head
+  unsigned long long peer_wait_ns = kPeerWaitNs;   // tensor parallel: limit of a wait for a peer
+};
+const ChainOptions kDefaultOptions;
+
+// Function attributes are per device: remember what was set for (device, function).
+std::mutex g_attr_mu;
 void prefer_carveout(const void* fn, int percent) {
   if (percent < 0) return;
-  static std::mutex mu;
   static std::map<std::pair<int, const void*>, int> last;
   int dev = 0;
   cudaGetDevice(&dev);
-  std::lock_guard<std::mutex> lock(mu);
+  std::lock_guard<std::mutex> lock(g_attr_mu);
   auto key = std::make_pair(dev, fn);
   auto it = last.find(key);
   if (it != last.end() && it->second == percent) return;
   last[key] = percent;
   cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+}
+// Dynamic shared memory beyond 48 KB needs a one-time opt-in per device and function.
+cudaError_t ensure_dynamic_smem(const void* fn, int bytes) {
+  static std::map<std::pair<int, const void*>, int> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(g_attr_mu);
+  auto key = std::make_pair(dev, fn);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[key] = bytes;
+  return e;
 }
 
 struct Launcher {
@@ -75,8 +103,17 @@ struct Launcher {
   int push_slot = -1;       // >= 0: the next projection pushes its result to the peers as exchange `push_slot`
   int pull_slot = -1;       // >= 0: the next fused norm adds the peers' partial results of exchange `pull_slot`
   const DfbHandle* tp = nullptr;  // set by a tensor-parallel step
+  const ChainOptions* opt = &kDefaultOptions;
+  const void* ahead_ptr = nullptr;        // look-ahead request the next launched kernel carries (cleared by it)
+  unsigned long long ahead_bytes = 0;
+  int embed_rows = 0;                     // rows of the embedding table when a kernel gathers by token id
   bool plain_next = false;  // the next launch follows a foreign kernel (a collective): no programmatic dependency
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
+  // what every GEMV launch of a step carries: the pending look-ahead request and the embedding row count
+  void fill_common(GemvArgs& a) {
+    a.ahead_ptr = ahead_ptr; a.ahead_bytes = ahead_bytes; a.embed_rows = embed_rows;
+    ahead_ptr = nullptr; ahead_bytes = 0;
+  }
   template <typename Args>
   void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true,
               size_t smem = 0) {
@@ -125,6 +162,7 @@ struct DfbHandle {
   bool use_pdl = true;
   int lmhead_ctas = 0;
   bool trace_on = false;
+  ChainOptions opt;              // tuning knobs of this decoder's kernel chain
   int step_mode = 0;             // 0: chain of per-op kernels (default); 1: one persistent kernel per step
   int persist_ctas = 0;          // grid of the persistent kernel (0 = one CTA per SM)
   int trace_entries = 0;         // timeline entries written by the last traced step
@@ -165,6 +203,8 @@ struct DfbHandle {
   bool direct = false;                             // exchanges go through the windows instead of the collectives
   bool fused = true;                               // ... and inside the projection / norm kernels, not in a kernel of their own
   unsigned int* tp_step = nullptr;                 // device step counter behind the exchange tags
+  unsigned char* loopback[kMaxRanks] = {};         // stand-ins for the peers' windows (dfb_tp_open_loopback)
+  int embed_rows() const { return m.vocab * (tp.size > 1 ? tp.size : 1); }   // the embedding table is never sharded
   const bf16* lm_head() const { return (const bf16*)m.embed + (size_t)tp.vocab_offset * m.hidden; }
   int qkv_rows() const { return (m.q_heads + 2 * m.kv_heads) * m.head_dim; }
   int q_size() const { return m.q_heads * m.head_dim; }
@@ -186,6 +226,7 @@ void tp_fill(Launcher& L, const DfbHandle* h, GemvArgs& a, bool producer) {
   if (!h || slot < 0) return;
   a.tp_mode = producer ? 1 : 2;
   a.tp_size = h->tp.size; a.tp_rank = h->tp.rank; a.tp_slot = slot; a.tp_step = h->tp_step;
+  a.tp_wait_ns = h->opt.peer_wait_ns;
   for (int r = 0; r < h->tp.size; ++r) a.tp_window[r] = h->windows[r];
   if (producer) L.push_slot = -1; else L.pull_slot = -1;
 }
@@ -196,14 +237,15 @@ int loads_for_k(int k) { return (k % 256 == 0) ? k / 256 : 0; }
 // that the CTAs of two consecutive kernels are resident together: the
 // successor prefetches its weights while the predecessor computes.
 int sm_count_cached() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
+  static int count[64] = {};   // per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    count[dev] = n;
   }
-  return n;
+  return count[dev];
 }
 int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
 
@@ -212,31 +254,24 @@ int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < 
 // weight stages) exceeds 48 KB, which needs a one-time opt-in per function.
 template <int LOADS, int WARPS, int STAGES, int MODE>
 void launch_gemv(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true) {
-  static bool configured = false;
   constexpr int smem = GemvSmem<LOADS, WARPS>::bytes(STAGES);
   auto kernel = stream_gemv_kernel<LOADS, WARPS, STAGES, MODE>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) { L.err = (int)e; return; }
-    configured = true;
-  }
+  cudaError_t e = ensure_dynamic_smem((const void*)kernel, smem);
+  if (e != cudaSuccess) { L.err = (int)e; return; }
   a.trace = L.next_trace();
+  L.fill_common(a);
   L.launch(kernel, dim3(grid), dim3(WARPS * 32), a, allow_pdl, smem);
 }
 
 // Tensor-core GEMV with 16 weight rows per MMA (dfb_pairgemv.cuh), K = 1024, 3..8 batch rows.
-int g_pair_gemv = 1;   // 0: use stream_gemv_kernel (8 weight rows per MMA) instead
 template <int PSTAGES, int MODE>
 void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true, int carve = -2) {
-  static bool configured = false;
   constexpr int smem = PairSmem::bytes(PSTAGES);
   auto kernel = pair_gemv_kernel<PSTAGES, MODE>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) { L.err = (int)e; return; }
-    configured = true;
-  }
+  cudaError_t e = ensure_dynamic_smem((const void*)kernel, smem);
+  if (e != cudaSuccess) { L.err = (int)e; return; }
   a.trace = L.next_trace();
+  L.fill_common(a);
   const int chain_carve = L.carve;
   if (carve != -2) L.carve = carve;   // this kernel wants another L1/shared split than the rest of its chain
   L.launch(kernel, dim3(grid), dim3(256), a, allow_pdl, smem);
@@ -246,16 +281,15 @@ void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true, int 
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
 template <int K, int NB, int MODE>
 void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
-  static bool configured = false;
   constexpr int smem = row_smem_bytes<K, NB>();
   auto kernel = row_gemv_kernel<K, NB, MODE>;
-  if (!configured && smem > 32 * 1024) {   // static + dynamic shared memory beyond 48 KB needs the opt-in
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (smem > 32 * 1024) {   // static + dynamic shared memory beyond 48 KB needs the opt-in
+    cudaError_t e = ensure_dynamic_smem((const void*)kernel, smem);
     if (e != cudaSuccess) { L.err = (int)e; return; }
   }
-  configured = true;
-  a.late_trigger = g_late_trigger;
-  a.bulk_x = g_bulk_x;
+  a.late_trigger = L.opt->late_trigger;
+  a.bulk_x = L.opt->bulk_x;
+  L.fill_common(a);
   // The down projection has one CTA per SM's worth of work (128 CTAs): asking for at
   // least 16 KB keeps two of them off one SM (with the 32 KB split of this chain),
   // which measured 25 us per step faster at batch 1 than letting them pair up.
@@ -270,7 +304,6 @@ void launch_row(Launcher& L, GemvArgs& a, int rows, int grid, bool allow_pdl = t
   else if (rows <= 4) launch_row_nb<K, 4, MODE>(L, a, grid, allow_pdl);
   else launch_row_nb<K, 8, MODE>(L, a, grid, allow_pdl);
 }
-int g_row_max_rows = 2;   // DFB_OPT_ROW_GEMV: largest batch that takes the FP32 kernels (0 = never)
 
 int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_in, bf16* res_out, const bf16* ln_w,
                     const bf16* w, bf16* out, int rows, int hidden, int n, float eps, int* status, bool allow_pdl) {
@@ -279,13 +312,13 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   a.w = w; a.n_tiles = n / kTileRows; a.rows = rows; a.k = hidden;
   a.x = x; a.ids = ids; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = out; a.out_stride = n; a.status = status;
-  if (rows <= g_row_max_rows && n % 16 == 0) {
+  if (rows <= L.opt->row_max_rows && n % 16 == 0) {
     a.n_tiles = n / 16;
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
     return L.err;
   }
-  if (g_pair_gemv && n % 16 == 0) {
+  if (L.opt->pair_gemv && n % 16 == 0) {
     a.n_tiles = n / 16;
     tp_fill(L, L.tp, a, false);
     launch_pair<2, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
@@ -306,7 +339,7 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
   // The FP32 kernels cover every input width (the full model's 2048 / 3072 and the
   // tensor-parallel shards 256 ... 1536); the tensor-core kernels 1024, 2048 and 3072.
   const int mma_loads = (k == 1024 || k == 2048 || k == 3072) ? loads_for_k(k) : 0;
-  if (rows <= g_row_max_rows || mma_loads == 0 || L.push_slot >= 0) {
+  if (rows <= L.opt->row_max_rows || mma_loads == 0 || L.push_slot >= 0) {
     a.n_tiles = n / RowRowsFor(k);
     tp_fill(L, L.tp, a, true);
     switch (k) {
@@ -339,13 +372,13 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   a.w = wgu; a.n_tiles = inter / 4; a.rows = rows; a.k = hidden;
   a.x = h; a.res_in = res_in; a.res_out = res_out; a.norm_w = ln_w; a.eps = eps;
   a.out = act; a.out_stride = inter; a.gate_rows = inter; a.status = status;
-  if (rows <= g_row_max_rows && inter % 8 == 0) {
+  if (rows <= L.opt->row_max_rows && inter % 8 == 0) {
     a.n_tiles = inter / 8;
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
-  if (g_pair_gemv && inter % 8 == 0) {
+  if (L.opt->pair_gemv && inter % 8 == 0) {
     a.n_tiles = inter / 8;
     tp_fill(L, L.tp, a, false);
     launch_pair<3, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
@@ -365,13 +398,13 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens;
   a.tokens_out = h->sharded() ? nullptr : tokens_out;
   a.best_out = h->sharded() ? h->best_local : nullptr;
-  if (rows <= g_row_max_rows && m.vocab % 16 == 0) {
+  if (rows <= L.opt->row_max_rows && m.vocab % 16 == 0) {
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
-  } else if (g_pair_gemv && m.vocab % 16 == 0) {
+  } else if (L.opt->pair_gemv && m.vocab % 16 == 0) {
     // The LM head is long enough to be bound by its per-tile CTA barrier with one CTA per SM: two CTAs of two
     // stages each (93 KB) overlap one another's barriers; that needs more shared memory than the chain's split.
     a.n_tiles = m.vocab / 16;
@@ -389,6 +422,7 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     for (int r = 0; r < h->tp.size; ++r) e.window[r] = h->windows[r];
     e.size = h->tp.size; e.rank = h->tp.rank; e.rows = rows; e.shard_rows = m.vocab; e.step_counter = h->tp_step;
     e.best_local = h->best_local; e.tokens = h->tokens; e.tokens_out = tokens_out; e.status = h->status;
+    e.wait_ns = h->opt.peer_wait_ns;
     exchange_argmax_kernel<<<1, 32, 0, L.stream>>>(e);
     ++L.count;
     L.plain_next = true;
@@ -412,7 +446,7 @@ int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
     ExchangeArgs a = {};
     for (int r = 0; r < h->tp.size; ++r) a.window[r] = h->windows[r];
     a.size = h->tp.size; a.rank = h->tp.rank; a.rows = rows; a.slot = L.exchanges; a.buf = L.exchanges & 1;
-    a.step_counter = h->tp_step; a.local = buf; a.status = h->status;
+    a.step_counter = h->tp_step; a.local = buf; a.status = h->status; a.wait_ns = h->opt.peer_wait_ns;
     if (++L.exchanges >= kExchangeSlots - 1) return DFB_E_TOO_LARGE;
     a.trace = L.next_trace();
     L.launch(exchange_sum_kernel, dim3(1), dim3(1024), a);
@@ -426,14 +460,14 @@ int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
   return 0;
 }
 
-int g_attn_wide_ctas = 2 * 148;  // attention grids up to this many CTAs use 256-thread CTAs
-
 int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
-                     int bt_stride, const int* row_active, bf16* out, int rows, int nsplit) {
+                     int bt_stride, int bt_cols, const int* row_active, bf16* out, int rows, int nsplit) {
   const DfbModelDesc& m = h->m;
   AttnArgs a = {};
   a.qkv = qkv; a.qkv_stride = h->qkv_rows(); a.q_size = h->q_size(); a.kv_size = h->kv_size();
-  a.positions = positions; a.block_tables = bt; a.bt_stride = bt_stride; a.row_active = row_active;
+  a.positions = positions; a.block_tables = bt; a.bt_stride = bt_stride; a.bt_cols = bt_cols; a.row_active = row_active;
+  a.ahead_ptr = L.ahead_ptr; a.ahead_bytes = L.ahead_bytes;
+  L.ahead_ptr = nullptr; L.ahead_bytes = 0;
   a.q_norm = (const bf16*)h->layers[layer].q_norm; a.k_norm = (const bf16*)h->layers[layer].k_norm;
   a.cos_sin = m.rope_cos_sin; a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim);
   a.k_cache = (bf16*)m.k_cache + (size_t)layer * h->kv_layer_elems;
@@ -446,11 +480,11 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   // CTAs most SMs are idle during attention: 256 threads then halve each thread's
   // share of the chunk and with it the latency of the CTA.
   const int ctas = nsplit * m.kv_heads * rows;
-  if (rows <= g_row_max_rows) {
-    a.late_trigger = g_late_trigger;
-    if (ctas <= g_attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
+  if (rows <= L.opt->row_max_rows) {
+    a.late_trigger = L.opt->late_trigger;
+    if (ctas <= L.opt->attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
     else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
-  } else if (ctas <= g_attn_wide_ctas) {
+  } else if (ctas <= L.opt->attn_wide_ctas) {
     L.launch(paged_attention_kernel<256, 1>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
   } else {
     L.launch(paged_attention_kernel<128, 1>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
@@ -468,26 +502,43 @@ int split_bucket(const DfbHandle* h, int max_context) {
 }
 
 // The whole step as one chain of 5 kernels per layer + the LM head.
-int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
+//
+// Look-ahead: kernel i of the chain also asks for the weights of kernel i + 2 to
+// be brought into L2 (a bulk prefetch: no registers, no shared memory, nothing
+// waits for it).  Kernel i + 1 requests its own weights into registers / shared
+// memory as soon as it is resident, i.e. while kernel i runs; its CTAs that only
+// fit on the SMs after kernel i has ended, and everything its first tiles do not
+// cover, would otherwise start their HBM round trip after the dependency.
+int enqueue_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t stream, float* logits_out) {
   const DfbModelDesc& m = h->m;
   Launcher L{stream, h->use_pdl, h->trace_on ? h->trace : nullptr};
-  L.carve = rows <= g_row_max_rows ? g_carve_fp32 : g_carve_mma;
+  L.opt = &h->opt;
+  L.carve = rows <= h->opt.row_max_rows ? h->opt.carve_fp32 : h->opt.carve_mma;
   L.tp = h;
+  L.embed_rows = h->embed_rows();
   // Tensor parallel over the windows: the projections push their partial results and the next fused norm
   // pulls them, when every consumer of this step runs on a kernel that can (all Qwen3 shards do).
-  const bool pair_ok = g_pair_gemv && h->qkv_rows() % 16 == 0 && m.intermediate % 8 == 0 && m.vocab % 16 == 0;
+  const bool pair_ok = h->opt.pair_gemv && h->qkv_rows() % 16 == 0 && m.intermediate % 8 == 0 && m.vocab % 16 == 0;
   const bool row_ok = h->qkv_rows() % 16 == 0 && m.intermediate % 8 == 0 && m.vocab % 16 == 0;
-  const bool fused = h->sharded() && h->direct && h->fused && (rows <= g_row_max_rows ? row_ok : pair_ok);
+  const bool fused = h->sharded() && h->direct && h->fused && (rows <= h->opt.row_max_rows ? row_ok : pair_ok);
   auto exchange = [&](int rc_in) -> int {   // after a row-parallel projection into h->hbuf
     if (rc_in || !h->sharded()) return rc_in;
     if (!fused) return tp_sum(L, h, h->hbuf, rows);
     L.pull_slot = L.exchanges;
     return ++L.exchanges >= kExchangeSlots - 1 ? DFB_E_TOO_LARGE : 0;
   };
+  const bool ahead = h->opt.look_ahead != 0;
+  const size_t b_qkv = sizeof(bf16) * (size_t)h->qkv_rows() * m.hidden, b_o = sizeof(bf16) * (size_t)m.hidden * h->q_size();
+  const size_t b_gu = sizeof(bf16) * 2 * (size_t)m.intermediate * m.hidden, b_d = sizeof(bf16) * (size_t)m.hidden * m.intermediate;
+  size_t b_lm = (size_t)h->opt.lmhead_ahead_mb << 20;
+  if (b_lm > sizeof(bf16) * (size_t)m.vocab * m.hidden) b_lm = sizeof(bf16) * (size_t)m.vocab * m.hidden;
+  auto want = [&](const void* p, size_t bytes) { if (ahead) { L.ahead_ptr = p; L.ahead_bytes = bytes; } };
   int rc = 0;
   int cur = 0;  // index of the residual buffer holding the current residual
   for (int l = 0; l < m.layers && !rc; ++l) {
     const DfbLayerWeights& w = h->layers[l];
+    const bool last = l + 1 == m.layers;
+    want(w.wo, b_o);
     if (l == 0) {
       // embedding rows are gathered by token id; the residual starts as the embedding itself.
       // No PDL on the first kernel: it must observe the staged inputs of this step.
@@ -499,16 +550,22 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float*
       cur ^= 1;
     }
     if (rc) break;
-    rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, h->st_active(), h->attn, rows, nsplit);
+    want(w.wgu, b_gu);
+    rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, bt_cols, h->st_active(), h->attn, rows,
+                          nsplit);
     if (rc) break;
     if (fused) L.push_slot = L.exchanges;
+    want(w.wd, b_d);
     rc = exchange(launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status));
     if (rc) break;
+    if (last) want(h->lm_head(), b_lm / 2);
+    else want(h->layers[l + 1].wqkv, b_qkv);
     rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
                        rows, m.hidden, m.intermediate, m.eps, h->status);
     cur ^= 1;
     if (rc) break;
     if (fused) L.push_slot = L.exchanges;
+    if (last) want((const char*)h->lm_head() + b_lm / 2, b_lm - b_lm / 2);
     rc = exchange(launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status));
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
@@ -541,17 +598,19 @@ int enqueue_persistent(DfbHandle* h, int rows, cudaStream_t stream, float* logit
   return L.err;
 }
 
-int run_step(DfbHandle* h, int rows, int nsplit, cudaStream_t stream, float* logits_out) {
+int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t stream, float* logits_out) {
   const bool persistent = h->step_mode == 1;
   if (!h->use_graph || logits_out)
-    return persistent ? enqueue_persistent(h, rows, stream, logits_out) : enqueue_step(h, rows, nsplit, stream, logits_out);
-  const int key = persistent ? 8192 + rows : rows * 64 + nsplit + (h->use_pdl ? 4096 : 0);
+    return persistent ? enqueue_persistent(h, rows, stream, logits_out)
+                      : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
+  // one graph per (rows, split bucket, filled block-table columns)
+  const int key = persistent ? (1 << 20) + rows : ((bt_cols * 16 + rows) * 64 + nsplit) * 2 + (h->use_pdl ? 1 : 0);
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
     cudaGraph_t graph = nullptr;
     DFB_CUDA(cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal));
     int rc = persistent ? enqueue_persistent(h, rows, h->capture_stream, nullptr)
-                        : enqueue_step(h, rows, nsplit, h->capture_stream, nullptr);
+                        : enqueue_step(h, rows, nsplit, bt_cols, h->capture_stream, nullptr);
     cudaError_t e = cudaStreamEndCapture(h->capture_stream, &graph);
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) return (int)e;
@@ -674,8 +733,10 @@ void dfb_destroy(DfbHandle* h) {
   if (!h) return;
   for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
   if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
-  for (int r = 0; r < kMaxRanks; ++r)
-    if (h->windows[r] && h->windows[r] != h->window_local) cudaIpcCloseMemHandle(h->windows[r]);
+  for (int r = 0; r < kMaxRanks; ++r) {
+    if (h->loopback[r]) cudaFree(h->loopback[r]);
+    else if (h->windows[r] && h->windows[r] != h->window_local) cudaIpcCloseMemHandle(h->windows[r]);
+  }
   if (h->window_local) cudaFree(h->window_local);
   if (h->host_stage) cudaFreeHost(h->host_stage);
   if (h->host_tokens) cudaFreeHost(h->host_tokens);
@@ -730,59 +791,78 @@ int dfb_tp_open_peers(DfbHandle* h, const void* handles) {
   return 0;
 }
 
+int dfb_tp_open_loopback(DfbHandle* h) {
+  if (!h || !h->sharded() || h->direct || h->steps != 0) return DFB_E_BAD_ARG;
+  if (!h->window_local) {
+    DFB_CUDA(cudaMalloc((void**)&h->window_local, Window::kBytes));
+    DFB_CUDA(cudaMemset(h->window_local, 0, Window::kBytes));
+  }
+  for (int r = 0; r < h->tp.size; ++r) {
+    if (r == h->tp.rank) { h->windows[r] = h->window_local; continue; }
+    DFB_CUDA(cudaMalloc((void**)&h->loopback[r], Window::kBytes));
+    DFB_CUDA(cudaMemset(h->loopback[r], 0, Window::kBytes));
+    h->windows[r] = h->loopback[r];
+  }
+  h->direct = true;
+  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  h->graphs.clear();
+  return 0;
+}
+
 int dfb_set_option(DfbHandle* h, int option, int value) {
   if (!h) return DFB_E_BAD_ARG;
+  // every option below may change which kernels a captured step holds
+  auto drop_graphs = [&]() {
+    for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+    h->graphs.clear();
+  };
   switch (option) {
     case DFB_OPT_USE_GRAPH: h->use_graph = value != 0; return 0;
     case DFB_OPT_USE_PDL: h->use_pdl = value != 0; return 0;
     case DFB_OPT_ROW_GEMV:
       if (value < 0 || value > kMaxRows) return DFB_E_BAD_ARG;
-      g_row_max_rows = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.row_max_rows = value;
+      break;
     case DFB_OPT_SMEM_CARVEOUT:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
-      g_carve_fp32 = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.carve_fp32 = value;
+      break;
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
-      g_carve_mma = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.carve_mma = value;
+      break;
     case DFB_OPT_TP_FUSED:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
       h->fused = value != 0;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      break;
     case DFB_OPT_BULK_X:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
-      g_bulk_x = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.bulk_x = value;
+      break;
     case DFB_OPT_PAIR_GEMV:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
-      g_pair_gemv = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.pair_gemv = value;
+      break;
     case DFB_OPT_LATE_TRIGGER:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
-      g_late_trigger = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.late_trigger = value;
+      break;
     case DFB_OPT_ATTN_WIDE:
       if (value < 0) return DFB_E_BAD_ARG;
-      g_attn_wide_ctas = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      h->opt.attn_wide_ctas = value;
+      break;
+    case DFB_OPT_LOOK_AHEAD:
+      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      h->opt.look_ahead = value;
+      break;
+    case DFB_OPT_LMHEAD_AHEAD_MB:
+      if (value < 0 || value > 100) return DFB_E_BAD_ARG;
+      h->opt.lmhead_ahead_mb = value;
+      break;
+    case DFB_OPT_PEER_WAIT_US:
+      if (value < 1) return DFB_E_BAD_ARG;
+      h->opt.peer_wait_ns = 1000ull * (unsigned long long)value;
+      break;
     case DFB_OPT_STEP_MODE:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
       if (value == 1 && (!h->full_geometry || h->sharded())) return DFB_E_GEOMETRY;  // built for the whole model only
@@ -791,22 +871,18 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_PERSIST_CTAS:
       if (value < 0 || value > 4096) return DFB_E_BAD_ARG;
       h->persist_ctas = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      break;
     case DFB_OPT_TRACE:
       h->trace_on = value != 0;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      break;
     case DFB_OPT_LMHEAD_CTAS:
       if (value < 0 || value > 4096) return DFB_E_BAD_ARG;
       h->lmhead_ctas = value;
-      for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
-      h->graphs.clear();
-      return 0;
+      break;
     default: return DFB_E_BAD_ARG;
   }
+  drop_graphs();
+  return 0;
 }
 
 int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
@@ -819,16 +895,21 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
   a.ids = s->input_ids; a.positions = s->positions; a.block_tables = s->block_tables;
   a.bt_cols = s->block_table_cols; a.bt_stride_in = s->block_table_stride; a.bt_stride_out = h->max_pages;
   a.row_active = s->row_active; a.rows = s->rows;
-  a.ids_out = s->input_ids ? h->st_ids() : nullptr; a.positions_out = h->st_pos(); a.bt_out = h->st_bt();
+  a.prev_tokens = h->tokens;   // input_ids == NULL: the previous step's tokens become this step's input ids
+  a.embed_rows = h->embed_rows(); a.status = h->status;
+  a.ids_out = h->st_ids(); a.positions_out = h->st_pos(); a.bt_out = h->st_bt();
   a.row_active_out = h->st_active();
-  if (!s->input_ids) {
-    // feedback: the previous step's tokens become this step's input ids
-    DFB_CUDA(cudaMemcpyAsync(h->st_ids(), h->tokens, sizeof(int) * s->rows, cudaMemcpyDeviceToDevice, stream));
-  }
   stage_inputs_kernel<<<1, 128, 0, stream>>>(a);
   DFB_CUDA(cudaGetLastError());
-  const int bound = s->max_context > 0 ? s->max_context : s->block_table_cols * h->m.block_size;
-  int rc = run_step(h, s->rows, split_bucket(h, bound), stream, s->out_logits);
+  // The attention grid is sized from the caller's bound; a bound that does not cover the filled
+  // block-table columns would only be caught on the device (status 6), so never go below one column.
+  int bound = s->block_table_cols * h->m.block_size;
+  if (s->max_context > 0 && s->max_context < bound) {
+    bound = s->max_context;
+    const int lowest = (s->block_table_cols - 1) * h->m.block_size + 1;   // the last column holds at least one token
+    if (bound < lowest) bound = lowest;
+  }
+  int rc = run_step(h, s->rows, split_bucket(h, bound), s->block_table_cols, stream, s->out_logits);
   if (rc) return rc;
   if (s->out_tokens)
     DFB_CUDA(cudaMemcpyAsync(s->out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
@@ -847,7 +928,9 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
   int max_ctx = 1;
   for (int r = 0; r < rows; ++r) {
     if (positions[r] < 0 || positions[r] >= h->m.max_model_len) return DFB_E_BAD_ARG;
-    if (input_ids[r] < 0 || input_ids[r] >= h->m.vocab) return DFB_E_BAD_ARG;
+    if (positions[r] >= (int64_t)cols * h->m.block_size) return DFB_E_BAD_ARG;   // beyond the block table given
+    // ids index the whole (replicated) embedding table, also on a tensor-parallel shard
+    if (input_ids[r] < 0 || input_ids[r] >= h->embed_rows()) return DFB_E_BAD_ARG;
     hs[r] = (int)input_ids[r];
     hs[8 + r] = (int)positions[r];
     hs[16 + r] = row_active ? row_active[r] : 1;
@@ -855,7 +938,7 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
     for (int c = 0; c < cols; ++c) hs[24 + r * h->max_pages + c] = block_tables[r * cols + c];
   }
   DFB_CUDA(cudaMemcpyAsync(h->stage, hs, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
-  int rc = run_step(h, rows, split_bucket(h, max_ctx), stream, nullptr);
+  int rc = run_step(h, rows, split_bucket(h, max_ctx), cols, stream, nullptr);
   if (rc) return rc;
   DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   DFB_CUDA(cudaStreamSynchronize(stream));
@@ -920,7 +1003,7 @@ int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int
   if (!h || !qkv || !positions || !block_tables || !attn_out) return DFB_E_BAD_ARG;
   if (rows < 1 || rows > kMaxRows || layer < 0 || layer >= h->m.layers) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
-  return launch_attention(L, h, layer, (const bf16*)qkv, positions, block_tables, block_table_stride, row_active,
+  return launch_attention(L, h, layer, (const bf16*)qkv, positions, block_tables, block_table_stride, 0, row_active,
                           (bf16*)attn_out, rows, split_bucket(h, max_context > 0 ? max_context : h->m.max_model_len));
 }
 

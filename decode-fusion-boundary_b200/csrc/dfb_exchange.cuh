@@ -28,7 +28,7 @@
 namespace dfb {
 
 constexpr int kExchangeSlots = 64;                     // exchanges per step fit in 6 bits
-constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // default limit of a wait for a peer: 2 s
 constexpr int kStatusPeerTimeout = 4;
 constexpr int kKernelExchange = 3;
 
@@ -51,6 +51,7 @@ struct ExchangeArgs {
   __nv_bfloat16* local;               // [rows, 1024]: partial in, sum out
   int* status;
   unsigned long long* trace;
+  unsigned long long wait_ns;         // limit of each wait for a peer
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -64,13 +65,14 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
 
 // Waits until *flag has reached `tag` (wrap-safe).  Returns false after kPeerWaitNs
 // or when another wait of this step has already failed.
-__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int tag, int* status, int who) {
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int tag, int* status, int who,
+                                          unsigned long long limit_ns) {
   const unsigned long long t0 = global_ns();
   int polls = 0;
   while ((int)(ld_acquire_sys(flag) - tag) < 0) {
     if ((++polls & 63) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (global_ns() - t0 > kPeerWaitNs) {
+      if (global_ns() - t0 > limit_ns) {
         report_status(status, kStatusPeerTimeout, kKernelExchange, who, (int)tag);
         return false;
       }
@@ -80,7 +82,8 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
 }
 
 // Polls one {data, tag} word until the tag arrives; bounded like wait_flag.
-__device__ __forceinline__ bool wait_word(const uint2* p, unsigned int tag, int* status, int who, uint32_t& data) {
+__device__ __forceinline__ bool wait_word(const uint2* p, unsigned int tag, int* status, int who, uint32_t& data,
+                                          unsigned long long limit_ns) {
   const unsigned long long t0 = global_ns();
   int polls = 0;
   for (;;) {
@@ -89,7 +92,7 @@ __device__ __forceinline__ bool wait_word(const uint2* p, unsigned int tag, int*
     if (v.y == tag) { data = v.x; return true; }
     if ((++polls & 63) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) break;
-      if (global_ns() - t0 > kPeerWaitNs) {
+      if (global_ns() - t0 > limit_ns) {
         report_status(status, kStatusPeerTimeout, kKernelExchange, who, (int)tag);
         break;
       }
@@ -117,7 +120,8 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
 // tags are there (bounded like wait_flag).  Returns the data words in d[b][0..1].
 template <int NR>
 __device__ __forceinline__ void pull_words(unsigned char* window, int buf, int src, int first, int rows,
-                                           unsigned int tag, int* status, uint32_t (&d)[NR][2]) {
+                                           unsigned int tag, int* status, unsigned long long limit_ns,
+                                           uint32_t (&d)[NR][2]) {
   const uint2* base = inbox_words(window, buf, src) + first;
   uint4 w[NR];
 #pragma unroll
@@ -136,7 +140,7 @@ __device__ __forceinline__ void pull_words(unsigned char* window, int buf, int s
     if (all) break;
     if ((++polls & 63) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) break;
-      if (global_ns() - t0 > kPeerWaitNs) {
+      if (global_ns() - t0 > limit_ns) {
         report_status(status, kStatusPeerTimeout, kKernelExchange, src, (int)tag);
         break;
       }
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__(1024) exchange_sum_kernel(const ExchangeArgs a
       for (int k = 0; k < 4; ++k) w[k] = mw[k];
     } else {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) wait_word(inbox + (size_t)r * Window::kSlotWords + k, tag, a.status, r, w[k]);
+      for (int k = 0; k < 4; ++k) wait_word(inbox + (size_t)r * Window::kSlotWords + k, tag, a.status, r, w[k], a.wait_ns);
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) { acc[2 * k] += bf_lo(w[k]); acc[2 * k + 1] += bf_hi(w[k]); }
@@ -202,6 +206,7 @@ struct ExchangeArgmaxArgs {
   int* tokens;
   int* tokens_out;
   int* status;
+  unsigned long long wait_ns;     // limit of each wait for a peer
 };
 __global__ void exchange_argmax_kernel(const ExchangeArgmaxArgs a) {
   const int tid = threadIdx.x;   // 32 threads
@@ -217,7 +222,8 @@ __global__ void exchange_argmax_kernel(const ExchangeArgmaxArgs a) {
   __syncwarp();
   if (tid < a.size && tid != a.rank) {
     st_release_sys(reinterpret_cast<unsigned int*>(a.window[tid] + Window::kPairFlagsOff) + a.rank, tag);
-    wait_flag(reinterpret_cast<const unsigned int*>(a.window[a.rank] + Window::kPairFlagsOff) + tid, tag, a.status, tid);
+    wait_flag(reinterpret_cast<const unsigned int*>(a.window[a.rank] + Window::kPairFlagsOff) + tid, tag, a.status, tid,
+              a.wait_ns);
   }
   __syncwarp();
   if (tid < a.rows) {

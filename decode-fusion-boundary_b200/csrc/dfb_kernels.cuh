@@ -76,6 +76,12 @@ struct GemvArgs {
   int tp_size, tp_rank, tp_slot; // ranks, this rank, index of the exchange in the step
   const unsigned int* tp_step;   // device step counter behind the tags
   unsigned char* tp_window[kMaxRanks];   // every rank's window as mapped here
+  unsigned long long tp_wait_ns; // how long a pull waits for a peer before it records kStatusPeerTimeout
+  // look-ahead: weights of a kernel further down the chain, requested into L2 (no registers, no
+  // shared memory, nothing waits for them) so that the kernel that needs them finds them on chip
+  const void* ahead_ptr;
+  unsigned long long ahead_bytes;  // multiple of 16; 0 = none
+  int embed_rows;                // rows of the embedding table behind `ids` (ids are clamped into it)
 };
 
 // ---------------------------------------------------------------------------
@@ -126,6 +132,25 @@ __device__ __forceinline__ void mma_bf16_16816_full(float (&c)[4], uint32_t a0, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Asks the memory system to bring [p, p + bytes) into L2 (bulk prefetch: no
+// destination, nothing to wait for).  p 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// The whole grid covers [base, base + bytes) in 4 KB pieces; called by warp 0 of every CTA.
+__device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned long long bytes, int cta, int ctas) {
+  if (base == nullptr || bytes == 0) return;
+  constexpr unsigned long long kPiece = 4096;
+  const unsigned long long pieces = (bytes + kPiece - 1) / kPiece;
+  const unsigned char* b = static_cast<const unsigned char*>(base);
+  for (unsigned long long c = (unsigned long long)cta * 32 + (threadIdx.x & 31); c < pieces;
+       c += (unsigned long long)ctas * 32) {
+    const unsigned long long off = c * kPiece;
+    const unsigned long long left = bytes - off;
+    l2_prefetch(b + off, (uint32_t)(left < kPiece ? left : kPiece));
+  }
+}
+
 // Optional timeline: per kernel {earliest CTA start, latest return from the
 // dependency wait, latest CTA end, earliest wait return} in globaltimer ns.
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -144,13 +169,27 @@ __device__ __forceinline__ void trace_max(unsigned long long* slot, int i) {
 // on with a safe substitute value and the host reads the word after the step.
 constexpr int kStatusBadPosition = 1;
 constexpr int kStatusBadBlock = 2;
+constexpr int kStatusBadToken = 5;       // a token id outside the embedding table (clamped, never dereferenced)
+constexpr int kStatusBadGrid = 6;        // the attention grid has fewer splits than a row's context needs
 constexpr int kKernelAttention = 2;
+constexpr int kKernelStage = 4;
 __device__ __forceinline__ void report_status(int* status, int code, int kernel, int index, int value) {
   if (status && atomicCAS(status, 0, code) == 0) {
     status[1] = kernel;
     status[2] = index;
     status[3] = value;
   }
+}
+
+// A token id as an embedding row: ids outside [0, embed_rows) are recorded and
+// replaced by row 0 (embed_rows <= 0: the caller vouches for the ids).
+constexpr int kKernelGemvIds = 5;
+__device__ __forceinline__ int clamp_token(int id, int embed_rows, int* status, int row) {
+  if (embed_rows > 0 && (id < 0 || id >= embed_rows)) {
+    report_status(status, kStatusBadToken, kKernelGemvIds, row, id);
+    return 0;
+  }
+  return id;
 }
 
 // ---------------------------------------------------------------------------
@@ -269,6 +308,7 @@ stream_gemv_kernel(const GemvArgs a) {
 #pragma unroll
     for (int j = 0; j < LOADS; ++j) nw[j] = ldg_stream(a.norm_w + kbase + 32 * j);
   }
+  if (warp == 1) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   __syncthreads();  // the barriers are initialised before anyone polls them
 
   pdl_wait();
@@ -285,7 +325,7 @@ stream_gemv_kernel(const GemvArgs a) {
     float xs[LOADS][8];
     float ss = 0.f;
     if (live) {
-      const size_t xrow = a.ids ? (size_t)a.ids[g] : (size_t)g;
+      const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[g], a.embed_rows, a.status, g) : (size_t)g;
       uint4 hv[LOADS], rv[LOADS];
 #pragma unroll
       for (int j = 0; j < LOADS; ++j) {
@@ -444,6 +484,7 @@ struct AttnArgs {
   const int* positions;         // [rows]
   const int* block_tables;      // [rows, bt_stride]
   int bt_stride;
+  int bt_cols;                  // valid columns of a row of block_tables (0 = not known)
   const int* row_active;        // [rows] or null
   const __nv_bfloat16* q_norm;  // [128]
   const __nv_bfloat16* k_norm;  // [128]
@@ -463,6 +504,8 @@ struct AttnArgs {
   unsigned int* tickets;        // [rows, kv_heads]
   unsigned long long* trace;    // optional timeline slot of this launch or null
   int late_trigger;             // 1: let the successor start only after this kernel has read its inputs
+  const void* ahead_ptr;        // look-ahead prefetch into L2 (see GemvArgs)
+  unsigned long long ahead_bytes;
 };
 
 // CHAIN only separates instantiations: a function's preferred shared-memory split is
@@ -478,14 +521,29 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
   const int tid = threadIdx.x;
   if (tid == 0) { trace_min(a.trace, 0); trace_max(a.trace, 4); }
   int pos = a.positions[row];
+  bool write_ok = true;   // false once any input of this row had to be replaced: its KV slot is then left alone
   if (pos < 0 || pos >= a.max_pos) {
     // A position outside the RoPE table / block table: record it and carry on
     // with a clamped value so that no address is formed from it.
     report_status(a.status, kStatusBadPosition, kKernelAttention, row, pos);
     pos = pos < 0 ? 0 : a.max_pos - 1;
+    write_ok = false;
   }
-  const int ctx = pos + 1;
-  const int nsplits = (ctx + kAttnChunk - 1) / kAttnChunk;
+  if (tid < 32)
+    l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x),
+                      (int)(gridDim.x * gridDim.y * gridDim.z));
+  int ctx = pos + 1;
+  int nsplits = (ctx + kAttnChunk - 1) / kAttnChunk;
+  if (nsplits > (int)gridDim.x) {
+    // The host sized the grid from a context bound smaller than this row's position: the chunk holding
+    // the new token has no CTA.  Record it and attend to what the grid covers, so that the tickets
+    // still balance and nothing is written outside the covered range.
+    if (split == 0) report_status(a.status, kStatusBadGrid, kKernelAttention, row, pos);
+    nsplits = (int)gridDim.x;
+    ctx = nsplits * kAttnChunk;
+    pos = ctx - 1;
+    write_ok = false;
+  }
   if (split >= nsplits) return;  // split 0 always stays and orders the grid after its predecessor
 
   __shared__ float qs[2][kHeadDim];
@@ -500,10 +558,18 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
   const int end = min(ctx, start + kAttnChunk);
   const bool owner = split == nsplits - 1;  // the chunk holding the new token
   const int pg = tid >> 4, l16 = tid & 15;  // position group, 16-byte slice of the head
-  int block = a.block_tables[row * a.bt_stride + start / a.block_size];
+  int bt_col = start / a.block_size;
+  if (a.bt_cols > 0 && bt_col >= a.bt_cols) {
+    // the position lies beyond the columns the caller filled in: never read a stale table entry
+    report_status(a.status, kStatusBadBlock, kKernelAttention, row, -1 - bt_col);
+    bt_col = a.bt_cols - 1;
+    write_ok = false;
+  }
+  int block = a.block_tables[row * a.bt_stride + bt_col];
   if (block < 0 || block >= a.num_blocks) {
     report_status(a.status, kStatusBadBlock, kKernelAttention, row, block);
     block = 0;
+    write_ok = false;
   }
   const size_t tok_stride = (size_t)a.kv_heads * kHeadDim;
   const size_t base = ((size_t)block * a.block_size + (start % a.block_size)) * tok_stride + (size_t)kvh * kHeadDim + 8 * l16;
@@ -582,7 +648,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
 #pragma unroll
       for (int u = 0; u < ITER; ++u)
         if (u == i) { kreg[u] = kn; vreg[u] = vn; }
-      if (a.row_active == nullptr || a.row_active[row] != 0) {
+      if (write_ok && (a.row_active == nullptr || a.row_active[row] != 0)) {
         const size_t off = base + (size_t)pi * tok_stride;
         *reinterpret_cast<uint4*>(a.k_cache + off) = kn;
         *reinterpret_cast<uint4*>(a.v_cache + off) = vn;
@@ -770,23 +836,35 @@ __global__ void merge_shard_argmax_kernel(const ArgmaxPart* all, int ranks, int 
 
 // Copies one step's inputs into the decoder's fixed staging buffers (so a
 // captured graph can read them from constant addresses), converting the
-// engine's int64 ids / positions to int32.
+// engine's int64 ids / positions to int32.  Token ids index the embedding
+// table in the first kernel of the step, so an id outside [0, embed_rows) is
+// recorded in the status word and replaced by 0 here: no address is ever
+// formed from it.  Without `ids` the previous step's tokens (`prev_tokens`)
+// are fed back, with the same check (an all-NaN row of logits has no winner).
 struct StageArgs {
-  const int64_t* ids;        // null: keep the previous step's tokens
+  const int64_t* ids;        // null: feed back prev_tokens
+  const int* prev_tokens;    // [rows] tokens of the previous step (device)
   const int64_t* positions;
   const int* block_tables;
   int bt_cols, bt_stride_in, bt_stride_out;
   const int* row_active;     // null: all active
   int rows;
+  int embed_rows;
   int* ids_out;
   int* positions_out;
   int* bt_out;
   int* row_active_out;
+  int* status;
 };
 __global__ void stage_inputs_kernel(const StageArgs a) {
   const int tid = threadIdx.x;
   if (tid < a.rows) {
-    if (a.ids) a.ids_out[tid] = (int)a.ids[tid];
+    long long id = a.ids ? (long long)a.ids[tid] : (long long)a.prev_tokens[tid];
+    if (id < 0 || id >= a.embed_rows) {
+      report_status(a.status, kStatusBadToken, kKernelStage, tid, (int)id);
+      id = 0;
+    }
+    a.ids_out[tid] = (int)id;
     a.positions_out[tid] = (int)a.positions[tid];
     a.row_active_out[tid] = a.row_active ? a.row_active[tid] : 1;
   }

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   }
   uint2 nwv = make_uint2(0, 0);
   if (kNorm) nwv = *reinterpret_cast<const uint2*>(a.norm_w + 4 * tid);
+  if (warp == 1) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   __syncthreads();  // the barriers are initialised before anyone polls them
 
   pdl_wait();
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
       hv[b] = make_uint2(0, 0);
       rv[b] = make_uint2(0, 0);
       if (b < a.rows) {
-        const size_t xrow = a.ids ? (size_t)a.ids[b] : (size_t)b;
+        const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[b], a.embed_rows, a.status, b) : (size_t)b;
         hv[b] = __ldcg(reinterpret_cast<const uint2*>(a.x + xrow * K) + tid);
         if (a.res_in) rv[b] = __ldcg(reinterpret_cast<const uint2*>(a.res_in + (size_t)b * K) + tid);
       }
@@ -125,7 +126,8 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
             for (int e = 0; e < 4; ++e) acc[b][e] += x[b][e];
         } else {
           uint32_t d[kMaxRows][2];
-          pull_words<kMaxRows>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, 2 * tid, a.rows, tag, a.status, d);
+          pull_words<kMaxRows>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, 2 * tid, a.rows, tag, a.status,
+                               a.tp_wait_ns, d);
 #pragma unroll
           for (int b = 0; b < kMaxRows; ++b) {
             acc[b][0] += bf_lo(d[b][0]); acc[b][1] += bf_hi(d[b][0]);

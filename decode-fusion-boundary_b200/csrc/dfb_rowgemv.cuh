@@ -72,6 +72,7 @@ row_gemv_kernel(const GemvArgs a) {
   }
   uint2 nwv = make_uint2(0, 0);
   if (kNorm) nwv = *reinterpret_cast<const uint2*>(a.norm_w + 4 * tid);
+  if (warp == 0) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   // Norm modes fetch x and the residual with two bulk copies per batch row (TMA) into
   // the bytes that later hold the fp32 copy of x: ordinary loads would queue in the
   // load/store unit behind the weight requests of the kernels that were let in early
@@ -92,9 +93,6 @@ row_gemv_kernel(const GemvArgs a) {
     }
   }
   if (threadIdx.x == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
-  const bool probe = a.trace && blockIdx.x == 0 && threadIdx.x == 0;   // cycle counts of CTA 0 in words 5-7
-  long long c0 = 0, c1 = 0, c2 = 0;
-  if (probe) c0 = clock64();
 
   // ---- x into shared memory as fp32 (with the fused residual add + RMSNorm) ----
   if (kNorm) {
@@ -109,7 +107,7 @@ row_gemv_kernel(const GemvArgs a) {
           hv = reinterpret_cast<const uint2*>(xs[b])[tid];
           rv = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(xs[b]) + 2 * K)[tid];
         } else {
-          const size_t xrow = a.ids ? (size_t)a.ids[b] : (size_t)b;
+          const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[b], a.embed_rows, a.status, b) : (size_t)b;
           hv = __ldcg(reinterpret_cast<const uint2*>(a.x + xrow * K) + tid);
           if (a.res_in) rv = __ldcg(reinterpret_cast<const uint2*>(a.res_in + (size_t)b * K) + tid);
         }
@@ -125,7 +123,8 @@ row_gemv_kernel(const GemvArgs a) {
               for (int e = 0; e < 4; ++e) acc[e] += x[b][e];
             } else {
               uint32_t d[1][2];
-              pull_words<1>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, b * 512 + 2 * tid, 1, tag, a.status, d);
+              pull_words<1>(a.tp_window[a.tp_rank], a.tp_slot & 1, r, b * 512 + 2 * tid, 1, tag, a.status,
+                            a.tp_wait_ns, d);
               acc[0] += bf_lo(d[0][0]); acc[1] += bf_hi(d[0][0]); acc[2] += bf_lo(d[0][1]); acc[3] += bf_hi(d[0][1]);
             }
           }
@@ -177,7 +176,6 @@ row_gemv_kernel(const GemvArgs a) {
   if (!kDirectX) __syncthreads();
   if (a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
-  if (probe) { c1 = clock64(); a.trace[5] = (unsigned long long)(c1 - c0); }
 
   // this lane's 8 values of x per batch row (kept in registers for one or two rows)
   float xr[NB <= 2 ? NB : 1][8];
@@ -264,7 +262,7 @@ row_gemv_kernel(const GemvArgs a) {
         if (lc < 8) red[warp][b0 + bb][hr * 8 + lc] = q1;
       }
     }
-    if (probe && it == 0) { c2 = clock64(); a.trace[6] = (unsigned long long)(c2 - c1); }
+    if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 5);
     __syncthreads();
     if (MODE == kModeStore) {
       // narrow shards have fewer threads than outputs of a group: loop (same trip count for every thread)
@@ -358,7 +356,6 @@ row_gemv_kernel(const GemvArgs a) {
     }
   }
   if (threadIdx.x == 0) trace_max(a.trace, 2);
-  if (probe) a.trace[7] = (unsigned long long)(clock64() - c2);
 }
 
 }  // namespace dfb

@@ -25,8 +25,10 @@ from .contracts import max_pages_per_seq, row_active_mask
 # TG_MAX_BATCH (taskgraph.py:33).
 TG_MAX_BATCH = 8
 # Tensor-parallel sizes the backend admits.  The reference admits only 1
-# (taskgraph.py:119-122).
-SUPPORTED_TP_SIZES = (1,)
+# (taskgraph.py:119-122); this build also runs 2, 4 and 8 ranks, provided the
+# engine attached a tensor-parallel group (``config.megakernel_tensor_parallel``,
+# a ``tensor_parallel.TensorParallelGroup`` of that size) for the exchanges.
+SUPPORTED_TP_SIZES = (1, 2, 4, 8)
 
 
 @dataclass(frozen=True)
@@ -50,8 +52,19 @@ def taskgraph_compatibility(config: Any, seqs: list[Any], is_prefill: bool) -> T
     max_num_seqs = getattr(config, "max_num_seqs", None)
     if isinstance(max_num_seqs, int) and max_num_seqs < len(seqs):
         return TaskGraphCompatibility(False, f"batch {len(seqs)} exceeds max_num_seqs={max_num_seqs}")
-    if getattr(config, "tensor_parallel_size", 1) not in SUPPORTED_TP_SIZES:
-        return TaskGraphCompatibility(False, "Task-graph megakernel requires tensor_parallel_size=1")
+    tp_size = getattr(config, "tensor_parallel_size", 1)
+    if tp_size not in SUPPORTED_TP_SIZES:
+        return TaskGraphCompatibility(False, "Task-graph megakernel requires tensor_parallel_size in (1, 2, 4, 8)")
+    if tp_size != 1:
+        group = getattr(config, "megakernel_tensor_parallel", None)
+        if group is None:
+            return TaskGraphCompatibility(
+                False, f"Task-graph megakernel at tensor_parallel_size={tp_size} needs a tensor-parallel group "
+                       "(config.megakernel_tensor_parallel)")
+        if getattr(group, "size", None) != tp_size:
+            return TaskGraphCompatibility(
+                False, f"tensor-parallel group has {getattr(group, 'size', None)} ranks but "
+                       f"tensor_parallel_size={tp_size}")
     for seq in seqs:
         if bool(getattr(seq, "is_greedy", False)):
             continue
@@ -121,7 +134,10 @@ class StreamDecoder:
         if tensor_parallel is not None and tensor_parallel.size > 1:
             tp_desc = tensor_parallel.descriptor(native, weights.vocab_offset)
             native.check(self._lib.dfb_set_tensor_parallel(handle, C.byref(tp_desc)), "dfb_set_tensor_parallel")
-            if tensor_parallel.transport == "direct":
+            if tensor_parallel.transport == "loopback":
+                # diagnostic: local stand-ins for the peers' windows, nobody fills them (timeout path on one GPU)
+                native.check(self._lib.dfb_tp_open_loopback(handle), "dfb_tp_open_loopback")
+            elif tensor_parallel.transport == "direct":
                 mine = C.create_string_buffer(native.DFB_TP_HANDLE_BYTES)
                 native.check(self._lib.dfb_tp_window_handle(handle, mine), "dfb_tp_window_handle")
                 everyone = tensor_parallel.gather_bytes(mine.raw)
@@ -160,15 +176,14 @@ class StreamDecoder:
     def read_trace(self):
         """Timeline of the last traced step: rows of ``(start, wait_done_last,
         end, wait_done_first, prologue_done, first_tile_mma_done, first_tile_done, 0)``
-        in ns per kernel, in launch order; also re-arms
-        the buffer (call once before the step to arm it)."""
+        in ns per kernel, in launch order; also re-arms the buffer (call once
+        before the step to arm it)."""
         import numpy as np
 
         buf = np.zeros((1024, 8), dtype=np.uint64)
         n = self._lib.dfb_read_trace(self._handle, buf.ctypes.data, 1024)
         if n < 0:
             self._native.check(n, "dfb_read_trace")
-        self.trace_detail = buf[512:576].reshape(32, 16).copy()   # clock64 marks of CTA 0 (persistent kernel)
         return buf[:n]
 
     def _stream(self) -> int:

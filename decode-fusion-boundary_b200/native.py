@@ -26,6 +26,9 @@ DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3
 DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS, DFB_OPT_ROW_GEMV, DFB_OPT_ATTN_WIDE = 5, 6, 7, 8
 DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER, DFB_OPT_PAIR_GEMV = 9, 10, 11, 12
 DFB_OPT_BULK_X, DFB_OPT_TP_FUSED = 13, 14
+DFB_OPT_LOOK_AHEAD, DFB_OPT_LMHEAD_AHEAD_MB, DFB_OPT_PEER_WAIT_US = 15, 16, 17
+DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
+DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -37,6 +40,7 @@ EXPORTS = (
     "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
+    "dfb_tp_open_loopback",
 )
 
 
@@ -134,6 +138,10 @@ def lib() -> C.CDLL:
     L.dfb_launch_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     L.dfb_launch_rmsnorm_gateup_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
     L.dfb_launch_lmhead_argmax.argtypes = [vp, vp, vp, vp, vp, i32, vp]
+    L.dfb_set_tensor_parallel.argtypes = [vp, C.POINTER(DfbTensorParallel)]
+    L.dfb_tp_window_handle.argtypes = [vp, vp]
+    L.dfb_tp_open_peers.argtypes = [vp, vp]
+    L.dfb_tp_open_loopback.argtypes = [vp]
     L.dfb_lmhead_argmax_noalloc.argtypes = [vp, vp, vp, vp, i32, i32, i32, f32, vp, vp, vp]
     for name in EXPORTS:
         if name not in ("dfb_destroy", "dfb_error_string"):

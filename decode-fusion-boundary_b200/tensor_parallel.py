@@ -2,7 +2,7 @@
 library calls through.
 
 The reference's megakernel backend is single-GPU (tensor_parallel_size != 1 is
-an explicit fallback reason, backends/megakernel/compatibility.py); the
+an explicit fallback reason, backends/megakernel/taskgraph.py:119-122); the
 partitioning here is the one of its torch path: ``QKVParallelLinear`` /
 ``MergedColumnParallelLinear`` split output rows by head and by gate/up half,
 ``RowParallelLinear`` splits input columns and sums over the ranks
@@ -74,6 +74,30 @@ def shard_weights(weights, rank: int, size: int):
     layers = [shard_layer_tensors(l, weights.geom, rank, size) for l in weights.layers]
     return DecoderWeights(local, weights.embed, layers, weights.final_norm, weights.cos_sin,
                           embed_rows=weights.geom.vocab, vocab_offset=rank * local.vocab)
+
+
+def localize_nano_weights(weights, group):
+    """``weights`` as read from ONE RANK of a tensor-parallel nano-vLLM model
+    (``weights_from_nano_model``): the projections are already that rank's
+    shards, and ``embed`` is the rank's slice ``[vocab / size, hidden]`` of the
+    vocabulary-parallel embedding (layers/embed_head.py).  The decode step
+    gathers embedding rows by token id on every rank, so the slices are
+    collected once into the whole table; the rank's LM head is its slice of it."""
+    import torch
+
+    from .weights import DecoderWeights
+
+    size, rank = group.size, group.rank
+    g = weights.geom
+    local_vocab = weights.embed.shape[0]
+    parts = [torch.empty_like(weights.embed) for _ in range(size)]
+    group.dist.all_gather(parts, weights.embed.contiguous())
+    full = torch.cat(parts).contiguous()
+    local = replace(g, q_heads=weights.layers[0].wo.shape[1] // g.head_dim,
+                    kv_heads=(weights.layers[0].wqkv.shape[0] - weights.layers[0].wo.shape[1]) // (2 * g.head_dim),
+                    intermediate=weights.layers[0].wd.shape[1], vocab=local_vocab)
+    return DecoderWeights(local, full, weights.layers, weights.final_norm, weights.cos_sin,
+                          embed_rows=full.shape[0], vocab_offset=rank * local_vocab)
 
 
 def merge_shard_argmax(values, indices, shard_rows: int):

@@ -101,7 +101,7 @@ typedef struct DfbStepDesc {
 
 /* Tensor-parallel shard of the step.  The reference's megakernel backend runs
  * on one GPU only (it answers tensor_parallel_size != 1 with an explicit
- * fallback reason, backends/megakernel/compatibility.py); the partitioning
+ * fallback reason, backends/megakernel/taskgraph.py:119-122); the partitioning
  * here is the one of the reference's torch path: KV heads and their query
  * heads, o_proj columns, gate/up rows, down_proj columns and LM-head rows are
  * split evenly over the ranks (layers/linear.py:54-153, layers/embed_head.py,
@@ -132,8 +132,19 @@ typedef struct DfbTensorParallel {
   void* comm;
 } DfbTensorParallel;
 
+/* Device status codes (DfbStatus.device_status); detail = {kernel id, index, observed value}.  A kernel that
+ * meets one of these records the first of a step, substitutes a safe value (no address is formed from the bad
+ * input, the row's KV slot is left unwritten) and finishes; the step's result for that row is then invalid. */
+#define DFB_STATUS_BAD_POSITION 1  /* positions[index] outside [0, max_model_len) */
+#define DFB_STATUS_BAD_BLOCK 2     /* block id of row `index` outside [0, num_blocks), or (value < 0) a position
+                                      beyond the block-table columns given: value = -1 - column */
+#define DFB_STATUS_COPY_TIMEOUT 3  /* a bulk copy into shared memory did not complete within its bounded wait */
+#define DFB_STATUS_PEER_TIMEOUT 4  /* tensor parallel: peer `index` did not deliver tag `value` in time */
+#define DFB_STATUS_BAD_TOKEN 5     /* token id of row `index` outside the embedding table (row 0 used instead) */
+#define DFB_STATUS_BAD_GRID 6      /* max_context smaller than positions[index] + 1: the attention grid is too small */
+
 typedef struct DfbStatus {
-  int32_t device_status;      /* 0 = ok; otherwise the first error code a kernel recorded */
+  int32_t device_status;      /* 0 = ok; otherwise the first DFB_STATUS_* code a kernel recorded */
   int32_t detail[3];          /* kernel id, index, observed value */
   int64_t steps;              /* decode steps enqueued so far */
   int64_t kernels_per_step;   /* kernels of this library launched by one step */
@@ -145,21 +156,27 @@ typedef struct DfbStatus {
 #define DFB_OPT_LMHEAD_CTAS 3 /* grid of the LM-head kernel (default 2 x SM count) */
 #define DFB_OPT_STEP_MODE 5   /* 0 (default): the step is a chain of per-op kernels; 1: one persistent kernel */
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
+/* Options 7-17 belong to the decoder they are set on (no process-wide state). */
 #define DFB_OPT_ROW_GEMV 7    /* largest batch (0..8) that runs the projections on the FP32 GEMV kernels in the
-                                 kernel chain; larger batches use the tensor-core kernels (process-wide) */
+                                 kernel chain; larger batches use the tensor-core kernels */
 #define DFB_OPT_ATTN_WIDE 8   /* attention grids of at most this many CTAs run 256-thread CTAs
-                                 instead of 128-thread ones (process-wide; default 296 = two per SM) */
+                                 instead of 128-thread ones (default 296 = two per SM) */
 #define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
-                                        kernels of the FP32 chain ask for as shared memory (process-wide; default 12) */
+                                        kernels of the FP32 chain ask for as shared memory (default 12) */
 #define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chain (default 50) */
 #define DFB_OPT_LATE_TRIGGER 11 /* FP32 chain: 0 (default) = a kernel lets its successor start (and request its
-                                  weights) at once, 1 = only after it has read its own inputs (process-wide) */
-#define DFB_OPT_PAIR_GEMV 12    /* tensor-core chain, K = 1024: 1 (default) = 16 weight rows per MMA (pair_gemv_kernel),
-                                  0 = 8 weight rows per MMA (stream_gemv_kernel) (process-wide) */
+                                  weights) at once, 1 = only after it has read its own inputs */
+#define DFB_OPT_PAIR_GEMV 12    /* mma.sync chain, K = 1024: 1 (default) = 16 weight rows per MMA (pair_gemv_kernel),
+                                  0 = 8 weight rows per MMA (stream_gemv_kernel) */
 #define DFB_OPT_BULK_X 13       /* FP32 chain: 1 (default) = the fused norm fetches x and the residual with bulk
-                                  copies (TMA), 0 = with ordinary loads (process-wide) */
+                                  copies (TMA), 0 = with ordinary loads */
 #define DFB_OPT_TP_FUSED 14     /* tensor parallel over peer windows: 1 (default) = the projections push and the next
-                                  fused norm pulls the partial results, 0 = a separate exchange kernel (per decoder) */
+                                  fused norm pulls the partial results, 0 = a separate exchange kernel */
+#define DFB_OPT_LOOK_AHEAD 15   /* 1 (default): every kernel of the chain also requests the weights of the kernel two
+                                  places further down into L2 (bulk prefetch); 0: no look-ahead */
+#define DFB_OPT_LMHEAD_AHEAD_MB 16 /* MB of the LM head that the last layer's kernels request into L2 (default 32) */
+#define DFB_OPT_PEER_WAIT_US 17 /* tensor parallel over peer windows: how long (microseconds) a kernel waits for a
+                                  peer's data before it records status 4 and goes on (default 2,000,000) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
@@ -175,11 +192,16 @@ int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp);
  * handles of all ranks, in rank order, and passes them to dfb_tp_open_peers on every rank, after which the
  * sums after o_proj / down_proj and the merge of the greedy winners are done by the library's own kernels
  * (a push into every peer's window, a flag, a bounded wait; all_reduce / all_gather may then be NULL).  A
- * peer that does not arrive within 2 s makes the waiting kernel record status 4 and finish; the step's
- * result is then invalid and dfb_read_status reports it. */
+ * peer that does not arrive within the wait limit (DFB_OPT_PEER_WAIT_US, 2 s by default) makes the waiting
+ * kernel record status 4 and finish; the step's result is then invalid and dfb_read_status reports it. */
 #define DFB_TP_HANDLE_BYTES 64
 int dfb_tp_window_handle(DfbHandle* h, void* handle_out);
 int dfb_tp_open_peers(DfbHandle* h, const void* handles);
+/* Diagnostic stand-in for dfb_tp_open_peers on ONE GPU in one process: the "peers'" windows are plain local
+ * allocations that nobody fills, so every wait for a peer runs into its limit (DFB_OPT_PEER_WAIT_US).  It
+ * exists to exercise the timeout path (status 4, the step still completes, the context stays usable) without
+ * a second rank and without leaving anything waiting; the tokens of such a step mean nothing. */
+int dfb_tp_open_loopback(DfbHandle* h);
 void dfb_destroy(DfbHandle* h);
 int dfb_set_option(DfbHandle* h, int option, int value);
 
@@ -205,7 +227,7 @@ const char* dfb_error_string(int code);
 /* Timeline of the last traced step (DFB_OPT_TRACE): for each of its kernels, in
  * launch order, eight uint64 words of globaltimer ns: {earliest CTA start,
  * latest return from the dependency wait, latest CTA end, earliest return from
- * the wait, latest end of the prologue, latest end of the first tile's MMAs,
+ * the wait, latest end of the prologue, latest end of the first tile's math,
  * latest end of the first tile, 0} (`out` holds 8 * max_kernels words).  Returns the number of kernels written (<= max_kernels) or a negative
  * code, and re-arms the buffer; call it once before the traced step to arm it.
  * This is the per-task-time-versus-CTA-count diagnostic the reference ran as an

@@ -48,7 +48,15 @@ def test_admission_reasons_in_order():
     assert f(c, [], False).reason == "Task-graph megakernel needs at least one sequence"
     assert "batch sizes 1..8" in f(c, [Seq()] * 9, False).reason
     assert f(cfg(max_num_seqs=2), [Seq()] * 3, False).reason == "batch 3 exceeds max_num_seqs=2"
-    assert f(cfg(tensor_parallel_size=2), [Seq()], False).reason == "Task-graph megakernel requires tensor_parallel_size=1"
+    # tensor parallelism: the reference admits size 1 only (taskgraph.py:119-122); this build admits 2, 4 and 8
+    # once a group of that size is attached, and says what is missing otherwise
+    assert f(cfg(tensor_parallel_size=3), [Seq()], False).reason == \
+        "Task-graph megakernel requires tensor_parallel_size in (1, 2, 4, 8)"
+    assert "needs a tensor-parallel group" in f(cfg(tensor_parallel_size=2), [Seq()], False).reason
+    group = SimpleNamespace(size=4, rank=0)
+    assert "has 4 ranks but tensor_parallel_size=2" in \
+        f(cfg(tensor_parallel_size=2, megakernel_tensor_parallel=group), [Seq()], False).reason
+    assert f(cfg(tensor_parallel_size=4, megakernel_tensor_parallel=group), [Seq()], False).supported
     assert f(c, [Seq(), Seq(temperature=0.7)], False).reason == "Task-graph megakernel supports greedy sampling only"
     assert f(c, [Seq(temperature=None)], False).supported is False
     ok = f(c, [Seq() for _ in range(8)], False)

@@ -139,7 +139,8 @@ def test_batch_equals_independent_rows(cuda_device, persistent):
     dec_a, dec_b = H.make_decoder(w, kv_a, persistent=persistent), H.make_decoder(w, kv_b, persistent=persistent)
     exact = not persistent
     if exact:
-        dec_a.set_option(native.DFB_OPT_ROW_GEMV, 0)   # process-wide switch, restored below
+        for dec in (dec_a, dec_b):                      # options belong to the decoder they are set on
+            dec.set_option(native.DFB_OPT_ROW_GEMV, 0)
     la = torch.zeros(3, g.vocab, device="cuda")
     lb = torch.zeros(1, g.vocab, device="cuda")
     cur = list(first)
@@ -164,7 +165,6 @@ def test_batch_equals_independent_rows(cuda_device, persistent):
         assert float((kv_a.float() - kv_b.float()).abs().max()) <= 2.0 ** -5
     else:
         assert torch.equal(kv_a, kv_b)
-        dec_a.set_option(native.DFB_OPT_ROW_GEMV, 2)   # the default: FP32 kernels for one or two rows
     dec_a.close(); dec_b.close()
 
 
@@ -207,6 +207,107 @@ def test_bad_block_id_is_reported_not_followed(cuda_device):
     dec.close()
 
 
+def test_options_are_per_decoder(cuda_device):
+    """An option set on one decoder leaves another decoder of the same process alone: with the FP32 kernels
+    switched off on A only, a two-row step of B still equals a fresh decoder's."""
+    from dfb_b200 import native
+    lens = [40, 300]
+    g, w, kv, tables, first = _setup(lens, seed=24)
+    outs = []
+    for touch_other in (False, True):
+        other = H.make_decoder(w, kv.cuda())
+        if touch_other:
+            other.set_option(native.DFB_OPT_ROW_GEMV, 0)
+            other.set_option(native.DFB_OPT_LOOK_AHEAD, 0)
+        dec = H.make_decoder(w, kv.cuda())
+        logits = torch.zeros(2, g.vocab, device="cuda")
+        dec.enqueue_rows(torch.tensor(first, device="cuda"), torch.tensor(lens, device="cuda"),
+                         H.padded_tables(tables, [n + 1 for n in lens], g.block_size), out_logits=logits)
+        torch.cuda.synchronize()
+        outs.append(logits.clone())
+        dec.close(); other.close()
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_look_ahead_prefetch_changes_nothing(cuda_device):
+    """The L2 look-ahead only moves bytes early: results are bit-identical with it on and off."""
+    from dfb_b200 import native
+    lens = [40, 300, 7, 64, 129]
+    g, w, kv, tables, first = _setup(lens, seed=25, layers=3)
+    outs = []
+    for ahead in (1, 0):
+        kvg = kv.cuda()
+        dec = H.make_decoder(w, kvg)
+        dec.set_option(native.DFB_OPT_LOOK_AHEAD, ahead)
+        for rows in (5, 2, 1):
+            logits = torch.zeros(rows, g.vocab, device="cuda")
+            dec.enqueue_rows(torch.tensor(first[:rows], device="cuda"), torch.tensor(lens[:rows], device="cuda"),
+                             H.padded_tables(tables[:rows], [n + 1 for n in lens[:rows]], g.block_size),
+                             out_logits=logits)
+            dec.enqueue_rows(torch.tensor(first[:rows], device="cuda"), torch.tensor(lens[:rows], device="cuda"),
+                             H.padded_tables(tables[:rows], [n + 1 for n in lens[:rows]], g.block_size))   # graph path
+            torch.cuda.synchronize()
+            outs.append((logits.clone(), dec.tokens_device()[:rows].tolist()))
+        code, st = dec.status()
+        assert code == 0
+        dec.close()
+    for a, b in zip(outs[:3], outs[3:]):
+        assert torch.equal(a[0], b[0]) and a[1] == b[1]
+
+
+def test_bad_token_id_is_reported_not_followed(cuda_device):
+    """A token id outside the embedding table, arriving on the DEVICE path (the host path refuses it before the
+    launch), sets status 5 in the staging kernel and row 0 of the table is used instead: no address is formed
+    from the id.  The decoder stays usable."""
+    g, w, kv, tables, first = _setup([10, 20], seed=26)
+    dec = H.make_decoder(w, kv.cuda())
+    pos = torch.tensor([10, 20], device="cuda")
+    bt = H.padded_tables(tables, [11, 21], g.block_size)
+    for bad in (g.vocab, -1, 2 ** 40):
+        dec.enqueue_rows(torch.tensor([first[0], bad], device="cuda"), pos, bt)
+        torch.cuda.synchronize()
+        code, st = dec.status()
+        assert code == -4 and st.device_status == 5 and st.detail[1] == 1, (bad, code, st.device_status, list(st.detail))
+    with pytest.raises(RuntimeError, match="bad argument"):
+        dec.decode_host([g.vocab], [10], [tables[0][:1]])
+    assert len(dec.decode_host([first[0]], [10], [tables[0][:1]])) == 1
+    code, st = dec.status()
+    assert code == 0
+    dec.close()
+
+
+def test_context_bound_too_small_is_reported(cuda_device):
+    """``max_context`` below a row's real context would leave the chunk with the new token without a CTA:
+    the kernel reports status 6, writes no K/V for that row and the merge tickets still balance (the next
+    correct step matches the oracle).  A position beyond the block-table columns given is status 2 with a
+    negative value, and the stale table entry is never read."""
+    lens = [200]
+    g, w, kv, tables, first = _setup(lens, seed=27)
+    kvg = kv.cuda()
+    before = kvg.clone()
+    dec = H.make_decoder(w, kvg)
+    ids, pos = torch.tensor(first, device="cuda"), torch.tensor(lens, device="cuda")
+    bt = H.padded_tables(tables, [201], g.block_size)
+    dec.enqueue_rows(ids, pos, bt, max_context=10)
+    torch.cuda.synchronize()
+    code, st = dec.status()
+    assert code == -4 and st.device_status == 6 and st.detail[0] == 2 and st.detail[2] == 200
+    assert torch.equal(kvg, before)
+    dec.enqueue_rows(ids, torch.tensor([300], device="cuda"), bt)      # position 300 needs a second column
+    torch.cuda.synchronize()
+    code, st = dec.status()
+    assert code == -4 and st.device_status == 2 and st.detail[2] == -2
+    assert torch.equal(kvg, before)
+    # and a correct step afterwards is still right
+    cos_sin = O.rope_cos_sin_table(g)
+    want_logits, want_tok = O.decode_step(w, kv, cos_sin, first, lens, tables)
+    logits = torch.zeros(1, g.vocab, device="cuda")
+    dec.enqueue_rows(ids, pos, bt, out_logits=logits)
+    torch.cuda.synchronize()
+    assert float((logits.cpu() - want_logits.float()).abs().max()) <= H.LOGIT_ATOL
+    dec.close()
+
+
 def test_capacity_errors(cuda_device):
     g, w, kv, tables, first = _setup([10], seed=19)
     dec = H.make_decoder(w, kv.cuda())
@@ -232,12 +333,14 @@ def test_option_and_tensor_parallel_argument_errors(cuda_device):
     for opt, bad in ((native.DFB_OPT_ROW_GEMV, 9), (native.DFB_OPT_STEP_MODE, 2), (native.DFB_OPT_SMEM_CARVEOUT, 101),
                      (native.DFB_OPT_SMEM_CARVEOUT_MMA, -2), (native.DFB_OPT_LATE_TRIGGER, 2),
                      (native.DFB_OPT_PAIR_GEMV, 5), (native.DFB_OPT_BULK_X, -1), (native.DFB_OPT_TP_FUSED, 3),
-                     (native.DFB_OPT_ATTN_WIDE, -1), (99, 0)):
+                     (native.DFB_OPT_ATTN_WIDE, -1), (native.DFB_OPT_LOOK_AHEAD, 2),
+                     (native.DFB_OPT_LMHEAD_AHEAD_MB, 101), (native.DFB_OPT_PEER_WAIT_US, 0), (99, 0)):
         assert lib.dfb_set_option(h, opt, bad) == -1, (opt, bad)          # DFB_E_BAD_ARG
     # a single-GPU decoder has no exchange window, and a tensor-parallel group needs 2, 4 or 8 ranks
     buf = C.create_string_buffer(native.DFB_TP_HANDLE_BYTES)
     assert lib.dfb_tp_window_handle(h, buf) == -1
     assert lib.dfb_tp_open_peers(h, buf) == -1
+    assert lib.dfb_tp_open_loopback(h) == -1
     for size, rank in ((3, 0), (1, 0), (2, 2), (2, -1)):
         tp = native.DfbTensorParallel(size=size, rank=rank, vocab_offset=0, dtype_bf16=9, dtype_int8=0, op_sum=0)
         assert lib.dfb_set_tensor_parallel(h, C.byref(tp)) == -1, (size, rank)

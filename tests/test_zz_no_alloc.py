@@ -53,6 +53,38 @@ def test_noalloc_matches_regular_entry_point_twice(cuda_device, rows):
     dec.close()
 
 
+def test_noalloc_full_vocabulary_and_no_allocation(cuda_device):
+    """The real vocabulary (151,936 rows: the 444-CTA grid of the one-row kernel) and a check that the call
+    leaves the amount of free device memory exactly as it found it."""
+    from dfb_b200 import native
+
+    lib = native.lib()
+    g = H.oracle_geometry(layers=1, vocab=151936)
+    w = O.make_weights(g, seed=33, norm="random").to(torch.bfloat16)
+    embed, fnorm = w.embed.cuda(), w.final_norm.cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    for rows in (1, 8):
+        h, res = _rand((rows, g.hidden), 70 + rows).cuda(), _rand((rows, g.hidden), 80 + rows).cuda()
+        tok = torch.full((8,), -1, dtype=torch.int32, device="cuda")
+        logits = torch.zeros(rows, g.vocab, dtype=torch.float32, device="cuda")
+        args = (embed.data_ptr(), fnorm.data_ptr(), h.data_ptr(), res.data_ptr(), rows, g.hidden, g.vocab, g.eps,
+                tok.data_ptr(), logits.data_ptr(), stream)
+        native.check(lib.dfb_lmhead_argmax_noalloc(*args), "noalloc warm-up")   # first call: symbol look-up, module load
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        for _ in range(2):
+            native.check(lib.dfb_lmhead_argmax_noalloc(*args), "noalloc")
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before
+        ref = O.op_final_norm_lmhead(h.cpu(), res.cpu(), w).float()
+        assert float((logits.cpu() - ref).abs().max()) <= 2.0 ** -5
+        got = tok[:rows].tolist()
+        assert got == logits.argmax(-1).tolist()
+        for r in range(rows):
+            assert H.token_gap_ok(ref[r], got[r], int(ref[r].argmax()))
+
+
 def test_noalloc_rejects_sizes_beyond_its_maximum(cuda_device):
     from dfb_b200 import native
 
