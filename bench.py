@@ -666,6 +666,9 @@ def run_own_arm(args):
     backend.set_kv_cache(kv)
     backend.ensure_ready()
     dec = backend.decoder
+    for item in args.set_option:
+        opt, val = item.split("=")
+        dec.set_option(int(opt), int(val))
     peak, peak_kind = measured_peaks()
 
     sampler = ClockSampler(local)
@@ -929,6 +932,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--row-gemv", type=int, default=-1, help="profile driver: DFB_OPT_ROW_GEMV of the decoder")
+    ap.add_argument("--set-option", action="append", default=[], metavar="ID=VALUE",
+                    help="dfb_set_option on the benchmarked decoder (tuning experiments), e.g. 15=0")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)

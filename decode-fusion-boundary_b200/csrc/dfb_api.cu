@@ -6,6 +6,7 @@
 #include "dfb_rowgemv.cuh"
 #include "dfb_exchange.cuh"
 #include "dfb_pairgemv.cuh"
+#include "dfb_tcgemv.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -13,6 +14,7 @@
 #include <map>
 #include <mutex>
 #include <new>
+#include <tuple>
 #include <utility>
 #include <vector>
 
@@ -46,6 +48,11 @@ typedef __nv_bfloat16 bf16;
 // for the same split; otherwise a kernel that prefers another one starts late.
 // `percent` is the share of the SM's 228 KB that goes to shared memory (-1:
 // leave the choice to the driver).
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v && *v ? atoi(v) : fallback;
+}
+
 // Tuning knobs of the kernel chain.  Every decoder owns a copy (dfb_set_option
 // changes that decoder only); the standalone dfb_launch_* entry points use the
 // defaults.
@@ -57,9 +64,22 @@ struct ChainOptions {
   int late_trigger = 0;        // FP32 chain: 1 = a kernel lets its successor start only after it has read its inputs
   int pair_gemv = 1;           // tensor-core chain, K = 1024: 16 weight rows per MMA; 0: stream_gemv_kernel
   int bulk_x = 1;              // FP32 chain: the fused norm fetches its inputs with bulk copies (TMA) instead of loads
-  int look_ahead = 1;          // every kernel requests the weights of the kernel two places down the chain into L2
-  int lmhead_ahead_mb = 32;    // ... and the last layer's kernels this many MB of the LM head
+  // L2 look-ahead (bulk prefetches issued by kernels with many CTAs for a kernel at least two places down the
+  // chain): 1 = gate/up requests the next layer's Wqkv, 2 = down_proj the next layer's Wo, 4 = QKV this layer's
+  // Wgu, 8 = o_proj this layer's Wd, 16 = the last layer's gate/up and down_proj request the head of the LM head,
+  // 32 = requests are issued after the kernel's own work instead of before its dependency wait (FP32 chain).
+  // Off by default: measured neutral to slightly negative at every batch size (the chain is bound by the
+  // latency of its dependent hops, not by how early the weights reach the chip).
+  int look_ahead = 0;
+  int lmhead_ahead_mb = 32;    // MB of the LM head requested by the last layer
   unsigned long long peer_wait_ns = kPeerWaitNs;   // tensor parallel: limit of a wait for a peer
+  // batches above row_max_rows: K = 1024 projections on tcgen05.mma (dfb_tcgemv.cuh).  DFB_TCGEN05=<mask> in the
+  // environment changes the initial value (a diagnostic switch for the handle-less standalone launchers).
+  // Bit mask: 1 = QKV, 2 = gate/up, 4 = LM head.  Default: the LM head only (equal to the mma.sync kernel in time);
+  // the two per-layer projections are parity-tested but measured slower inside the chain than their mma.sync
+  // counterparts (their longer post-dependency path: bulk copies of x, two issue loops, accumulator read).
+  int tcgen05 = env_int("DFB_TCGEN05", 4);
+  int carve_tc = 100;          // ... whose chain asks for all of an SM's L1/shared memory as shared memory
 };
 const ChainOptions kDefaultOptions;
 
@@ -106,12 +126,14 @@ struct Launcher {
   const ChainOptions* opt = &kDefaultOptions;
   const void* ahead_ptr = nullptr;        // look-ahead request the next launched kernel carries (cleared by it)
   unsigned long long ahead_bytes = 0;
+  bool ahead_late = false;
   int embed_rows = 0;                     // rows of the embedding table when a kernel gathers by token id
   bool plain_next = false;  // the next launch follows a foreign kernel (a collective): no programmatic dependency
   unsigned long long* next_trace() const { return trace ? trace + 8 * count : nullptr; }
   // what every GEMV launch of a step carries: the pending look-ahead request and the embedding row count
   void fill_common(GemvArgs& a) {
-    a.ahead_ptr = ahead_ptr; a.ahead_bytes = ahead_bytes; a.embed_rows = embed_rows;
+    a.ahead_ptr = ahead_ptr; a.ahead_bytes = ahead_bytes; a.ahead_late = ahead_late ? 1 : 0; a.embed_rows = embed_rows;
+    a.late_trigger = opt->late_trigger;
     ahead_ptr = nullptr; ahead_bytes = 0;
   }
   template <typename Args>
@@ -278,6 +300,74 @@ void launch_pair(Launcher& L, GemvArgs& a, int grid, bool allow_pdl = true, int 
   L.carve = chain_carve;
 }
 
+// ---- tcgen05 GEMV (dfb_tcgemv.cuh) ------------------------------------------------------------------------
+// The TMA descriptor of a weight matrix [rows, 1024] bf16 with boxes of {64 columns, box_rows rows} and the
+// 128-byte swizzle the MMA's shared-memory descriptors expect.  cuTensorMapEncodeTiled is a driver entry
+// point; it is looked up through the runtime so that the library links against no driver stub.  Encoded
+// maps are kept per (address, rows, box rows): weights do not move while a decoder lives.
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                           CUtensorMapFloatOOBfill);
+int tc_weight_map(const void* w, int rows, int box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static TensorMapEncodeTiledFn encode = nullptr;
+  static std::map<std::tuple<const void*, int, int>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(w, rows, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess) return (int)e;
+    if (!fn || qres != cudaDriverEntryPointSuccess) return (int)cudaErrorNotSupported;
+    encode = (TensorMapEncodeTiledFn)fn;
+  }
+  if ((uintptr_t)w % 16) return DFB_E_BAD_ARG;
+  const cuuint64_t dims[2] = {(cuuint64_t)kTcK, (cuuint64_t)rows};       // innermost first
+  const cuuint64_t strides[1] = {(cuuint64_t)kTcK * sizeof(bf16)};       // bytes between rows
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  CUtensorMap m;
+  CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (dfb_debug()) fprintf(stderr, "dfb: cuTensorMapEncodeTiled failed with %d\n", (int)r);
+    return (int)cudaErrorInvalidValue;
+  }
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return 0;
+}
+
+template <int MODE, int MT>
+void launch_tc(Launcher& L, GemvArgs& a, int n_rows, int box_rows, int grid, bool allow_pdl = true, int carve = -2) {
+  using SM = TcSmem<MT>;
+  auto kernel = tc_gemv_kernel<MODE, MT>;
+  cudaError_t e = ensure_dynamic_smem((const void*)kernel, SM::bytes());
+  if (e != cudaSuccess) { L.err = (int)e; return; }
+  a.trace = L.next_trace();
+  L.fill_common(a);
+  TcArgs t;
+  memset(&t, 0, sizeof(t));
+  t.g = a;
+  t.n_rows = n_rows;
+  const int rc = tc_weight_map(a.w, n_rows, box_rows, &t.wmap);
+  if (rc) { L.err = rc; return; }
+  const int chain_carve = L.carve;
+  if (carve != -2) L.carve = carve;   // this kernel wants another L1/shared split than the rest of its chain
+  L.launch(kernel, dim3(grid), dim3(kTcThreads), t, allow_pdl, SM::bytes());
+  L.carve = chain_carve;
+}
+// whether this launch takes the tcgen05 kernels: a batch above the FP32 kernels' range, no fused tensor-parallel pull
+bool use_tc(const Launcher& L, int rows, int which) {
+  return (L.opt->tcgen05 & which) && rows > L.opt->row_max_rows && L.pull_slot < 0;
+}
+
 // FP32 row-parallel GEMV (dfb_rowgemv.cuh), used for one or two batch rows.
 template <int K, int NB, int MODE>
 void launch_row_nb(Launcher& L, GemvArgs& a, int grid, bool allow_pdl) {
@@ -316,6 +406,11 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
     a.n_tiles = n / 16;
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormStore>(L, a, rows, a.n_tiles, allow_pdl);
+    return L.err;
+  }
+  if (use_tc(L, rows, 1) && n % 32 == 0) {
+    a.n_tiles = n / 32;
+    launch_tc<kModeNormStore, 64>(L, a, n, 32, a.n_tiles, allow_pdl);
     return L.err;
   }
   if (L.opt->pair_gemv && n % 16 == 0) {
@@ -378,6 +473,11 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
+  if (use_tc(L, rows, 2) && inter % 16 == 0) {
+    a.n_tiles = inter / 16;
+    launch_tc<kModeNormSwiglu, 64>(L, a, 2 * inter, 16, a.n_tiles);
+    return L.err;
+  }
   if (L.opt->pair_gemv && inter % 8 == 0) {
     a.n_tiles = inter / 8;
     tp_fill(L, L.tp, a, false);
@@ -404,6 +504,12 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     if (grid > a.n_tiles) grid = a.n_tiles;
     tp_fill(L, L.tp, a, false);
     launch_row<1024, kModeNormArgmax>(L, a, rows, grid);
+  } else if (use_tc(L, rows, 4) && !h->sharded()) {
+    // persistent CTAs, 64 vocabulary rows per tile, the weight ring never drains between tiles
+    a.n_tiles = (m.vocab + 63) / 64;
+    int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
+    if (grid > a.n_tiles) grid = a.n_tiles;
+    launch_tc<kModeNormArgmax, 128>(L, a, m.vocab, 64, grid, true, 100);
   } else if (L.opt->pair_gemv && m.vocab % 16 == 0) {
     // The LM head is long enough to be bound by its per-tile CTA barrier with one CTA per SM: two CTAs of two
     // stages each (93 KB) overlap one another's barriers; that needs more shared memory than the chain's split.
@@ -480,8 +586,8 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   // CTAs most SMs are idle during attention: 256 threads then halve each thread's
   // share of the chunk and with it the latency of the CTA.
   const int ctas = nsplit * m.kv_heads * rows;
+  a.late_trigger = L.opt->late_trigger;
   if (rows <= L.opt->row_max_rows) {
-    a.late_trigger = L.opt->late_trigger;
     if (ctas <= L.opt->attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
     else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
   } else if (ctas <= L.opt->attn_wide_ctas) {
@@ -513,7 +619,8 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t s
   const DfbModelDesc& m = h->m;
   Launcher L{stream, h->use_pdl, h->trace_on ? h->trace : nullptr};
   L.opt = &h->opt;
-  L.carve = rows <= h->opt.row_max_rows ? h->opt.carve_fp32 : h->opt.carve_mma;
+  L.carve = rows <= h->opt.row_max_rows ? h->opt.carve_fp32
+            : ((h->opt.tcgen05 & 3) && !h->sharded()) ? h->opt.carve_tc : h->opt.carve_mma;
   L.tp = h;
   L.embed_rows = h->embed_rows();
   // Tensor parallel over the windows: the projections push their partial results and the next fused norm
@@ -527,18 +634,20 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t s
     L.pull_slot = L.exchanges;
     return ++L.exchanges >= kExchangeSlots - 1 ? DFB_E_TOO_LARGE : 0;
   };
-  const bool ahead = h->opt.look_ahead != 0;
+  const int ahead = h->opt.look_ahead;
   const size_t b_qkv = sizeof(bf16) * (size_t)h->qkv_rows() * m.hidden, b_o = sizeof(bf16) * (size_t)m.hidden * h->q_size();
   const size_t b_gu = sizeof(bf16) * 2 * (size_t)m.intermediate * m.hidden, b_d = sizeof(bf16) * (size_t)m.hidden * m.intermediate;
   size_t b_lm = (size_t)h->opt.lmhead_ahead_mb << 20;
   if (b_lm > sizeof(bf16) * (size_t)m.vocab * m.hidden) b_lm = sizeof(bf16) * (size_t)m.vocab * m.hidden;
-  auto want = [&](const void* p, size_t bytes) { if (ahead) { L.ahead_ptr = p; L.ahead_bytes = bytes; } };
+  auto want = [&](int bit, const void* p, size_t bytes) {
+    if (ahead & bit) { L.ahead_ptr = p; L.ahead_bytes = bytes; L.ahead_late = (ahead & 32) != 0; }
+  };
   int rc = 0;
   int cur = 0;  // index of the residual buffer holding the current residual
   for (int l = 0; l < m.layers && !rc; ++l) {
     const DfbLayerWeights& w = h->layers[l];
     const bool last = l + 1 == m.layers;
-    want(w.wo, b_o);
+    want(4, w.wgu, b_gu);
     if (l == 0) {
       // embedding rows are gathered by token id; the residual starts as the embedding itself.
       // No PDL on the first kernel: it must observe the staged inputs of this step.
@@ -550,22 +659,23 @@ int enqueue_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t s
       cur ^= 1;
     }
     if (rc) break;
-    want(w.wgu, b_gu);
+    // attention requests nothing: at short contexts its grid is a handful of CTAs, far too few to issue from
     rc = launch_attention(L, h, l, h->qkv, h->st_pos(), h->st_bt(), h->max_pages, bt_cols, h->st_active(), h->attn, rows,
                           nsplit);
     if (rc) break;
     if (fused) L.push_slot = L.exchanges;
-    want(w.wd, b_d);
+    want(8, w.wd, b_d);
     rc = exchange(launch_linear(L, h->attn, (const bf16*)w.wo, h->hbuf, rows, m.hidden, h->q_size(), h->status));
     if (rc) break;
-    if (last) want(h->lm_head(), b_lm / 2);
-    else want(h->layers[l + 1].wqkv, b_qkv);
+    if (last) want(16, h->lm_head(), b_lm / 2);
+    else want(1, h->layers[l + 1].wqkv, b_qkv);
     rc = launch_gateup(L, h->hbuf, h->res[cur], h->res[cur ^ 1], (const bf16*)w.ln_post, (const bf16*)w.wgu, h->act,
                        rows, m.hidden, m.intermediate, m.eps, h->status);
     cur ^= 1;
     if (rc) break;
     if (fused) L.push_slot = L.exchanges;
-    if (last) want((const char*)h->lm_head() + b_lm / 2, b_lm - b_lm / 2);
+    if (last) want(16, (const char*)h->lm_head() + b_lm / 2, b_lm - b_lm / 2);
+    else want(2, h->layers[l + 1].wo, b_o);
     rc = exchange(launch_linear(L, h->act, (const bf16*)w.wd, h->hbuf, rows, m.hidden, m.intermediate, h->status));
   }
   if (!rc) rc = launch_lmhead(L, h, h->hbuf, h->res[cur], rows, nullptr, logits_out);
@@ -830,6 +940,7 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_SMEM_CARVEOUT_MMA:
       if (value < -1 || value > 100) return DFB_E_BAD_ARG;
       h->opt.carve_mma = value;
+      h->opt.carve_tc = value;
       break;
     case DFB_OPT_TP_FUSED:
       if (value != 0 && value != 1) return DFB_E_BAD_ARG;
@@ -852,12 +963,16 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
       h->opt.attn_wide_ctas = value;
       break;
     case DFB_OPT_LOOK_AHEAD:
-      if (value != 0 && value != 1) return DFB_E_BAD_ARG;
+      if (value < 0 || value > 63) return DFB_E_BAD_ARG;
       h->opt.look_ahead = value;
       break;
     case DFB_OPT_LMHEAD_AHEAD_MB:
       if (value < 0 || value > 100) return DFB_E_BAD_ARG;
       h->opt.lmhead_ahead_mb = value;
+      break;
+    case DFB_OPT_TCGEN05:
+      if (value < 0 || value > 7) return DFB_E_BAD_ARG;
+      h->opt.tcgen05 = value;
       break;
     case DFB_OPT_PEER_WAIT_US:
       if (value < 1) return DFB_E_BAD_ARG;
@@ -1003,6 +1118,7 @@ int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int
   if (!h || !qkv || !positions || !block_tables || !attn_out) return DFB_E_BAD_ARG;
   if (rows < 1 || rows > kMaxRows || layer < 0 || layer >= h->m.layers) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
+  L.opt = &h->opt;
   return launch_attention(L, h, layer, (const bf16*)qkv, positions, block_tables, block_table_stride, 0, row_active,
                           (bf16*)attn_out, rows, split_bucket(h, max_context > 0 ? max_context : h->m.max_model_len));
 }
@@ -1027,6 +1143,7 @@ int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* re
                              float* out_logits, int32_t rows, dfb_stream_t stream) {
   if (!h || !hidden_in || !residual || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
+  L.opt = &h->opt;
   return launch_lmhead(L, h, (const bf16*)hidden_in, (const bf16*)residual, rows, out_tokens, out_logits);
 }
 

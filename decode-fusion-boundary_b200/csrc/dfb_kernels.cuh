@@ -81,6 +81,7 @@ struct GemvArgs {
   // shared memory, nothing waits for them) so that the kernel that needs them finds them on chip
   const void* ahead_ptr;
   unsigned long long ahead_bytes;  // multiple of 16; 0 = none
+  int ahead_late;                // 1: issue the request after this kernel's own work, 0: before its dependency wait
   int embed_rows;                // rows of the embedding table behind `ids` (ids are clamped into it)
 };
 
@@ -258,7 +259,7 @@ stream_gemv_kernel(const GemvArgs a) {
   constexpr int kWarps = WARPS;
   using SM = GemvSmem<LOADS, WARPS>;
   constexpr int K = SM::kK;
-  pdl_launch_dependents();
+  if (!a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
   extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -369,6 +370,7 @@ stream_gemv_kernel(const GemvArgs a) {
     }
   }
 
+  if (a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
   // ---- main loop over this CTA's tiles ----
   const int eb = tid >> 3, er = tid & 7;  // epilogue thread -> (batch row, tile row)

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   constexpr bool kNorm = MODE != kModeStore;
   constexpr int K = PairSmem::kK, kWarps = 8;
   using SM = PairSmem;
-  pdl_launch_dependents();
+  if (!a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
   extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   uint4 xa[4];   // B fragments: x[batch g], this lane's 8 columns of each 32-column block
 #pragma unroll
   for (int j = 0; j < 4; ++j) xa[j] = *reinterpret_cast<const uint4*>(xsb + g * SM::kRowStride + 2 * (kbase + 32 * j));
+  if (a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_max(a.trace, 4);
 
   // ---- main loop over this CTA's tiles ----

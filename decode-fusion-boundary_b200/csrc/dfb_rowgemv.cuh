@@ -72,7 +72,7 @@ row_gemv_kernel(const GemvArgs a) {
   }
   uint2 nwv = make_uint2(0, 0);
   if (kNorm) nwv = *reinterpret_cast<const uint2*>(a.norm_w + 4 * tid);
-  if (warp == 0) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
+  if (warp == 0 && !a.ahead_late) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   // Norm modes fetch x and the residual with two bulk copies per batch row (TMA) into
   // the bytes that later hold the fp32 copy of x: ordinary loads would queue in the
   // load/store unit behind the weight requests of the kernels that were let in early
@@ -315,6 +315,7 @@ row_gemv_kernel(const GemvArgs a) {
     if (nxt < n_groups) __syncthreads();   // `red` is reused by the next group
   }
 
+  if (warp == 0 && a.ahead_late) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   if (MODE == kModeNormArgmax) {
     // threads (b, r) -> one partial per batch row and CTA -> grid (the last CTA to arrive finishes)
     if (tid < 128) {

@@ -163,7 +163,8 @@ typedef struct DfbStatus {
                                  instead of 128-thread ones (default 296 = two per SM) */
 #define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
                                         kernels of the FP32 chain ask for as shared memory (default 12) */
-#define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chain (default 50) */
+#define DFB_OPT_SMEM_CARVEOUT_MMA 10 /* the same for the tensor-core chains (default 50; 100 when a per-layer
+                                        projection runs on tcgen05) */
 #define DFB_OPT_LATE_TRIGGER 11 /* FP32 chain: 0 (default) = a kernel lets its successor start (and request its
                                   weights) at once, 1 = only after it has read its own inputs */
 #define DFB_OPT_PAIR_GEMV 12    /* mma.sync chain, K = 1024: 1 (default) = 16 weight rows per MMA (pair_gemv_kernel),
@@ -172,11 +173,18 @@ typedef struct DfbStatus {
                                   copies (TMA), 0 = with ordinary loads */
 #define DFB_OPT_TP_FUSED 14     /* tensor parallel over peer windows: 1 (default) = the projections push and the next
                                   fused norm pulls the partial results, 0 = a separate exchange kernel */
-#define DFB_OPT_LOOK_AHEAD 15   /* 1 (default): every kernel of the chain also requests the weights of the kernel two
-                                  places further down into L2 (bulk prefetch); 0: no look-ahead */
+#define DFB_OPT_LOOK_AHEAD 15   /* L2 look-ahead, a bit mask (default 0 = none; measured neutral): kernels with many CTAs also request
+                                  weights of a kernel at least two places further down the chain into L2 (bulk
+                                  prefetch): 1 = gate/up asks for the next layer's Wqkv, 2 = down_proj for the next
+                                  layer's Wo, 4 = QKV for this layer's Wgu, 8 = o_proj for this layer's Wd, 16 = the
+                                  last layer asks for the head of the LM head, 32 = ask after the kernel's own work
+                                  instead of before its dependency wait */
 #define DFB_OPT_LMHEAD_AHEAD_MB 16 /* MB of the LM head that the last layer's kernels request into L2 (default 32) */
 #define DFB_OPT_PEER_WAIT_US 17 /* tensor parallel over peer windows: how long (microseconds) a kernel waits for a
                                   peer's data before it records status 4 and goes on (default 2,000,000) */
+#define DFB_OPT_TCGEN05 18      /* batches above DFB_OPT_ROW_GEMV: which K = 1024 projections run on tcgen05.mma with
+                                  TMA-fed shared-memory stages and accumulators in tensor memory instead of the
+                                  mma.sync kernels; a bit mask: 1 = QKV, 2 = gate/up, 4 = LM head (default 4) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

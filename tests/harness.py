@@ -72,7 +72,7 @@ def token_gap_ok(oracle_logits: torch.Tensor, got: int, want: int, atol=TOKEN_GA
 
 def run_parity_case(layers=2, vocab=4096, prompt_lens=(3, 70, 250), steps=4, seed=3, norm="random",
                     block_permutation=None, use_graph=True, use_pdl=True, host_path=False, max_pos=2048,
-                    check_kv=True, persistent=False):
+                    check_kv=True, persistent=False, options=None):
     """Prefill by the oracle, then ``steps`` teacher-forced decode steps on both
     sides; returns the worst differences seen."""
     g = oracle_geometry(layers=layers, vocab=vocab, max_pos=max_pos)
@@ -89,6 +89,8 @@ def run_parity_case(layers=2, vocab=4096, prompt_lens=(3, 70, 250), steps=4, see
         cur.append(int(O.greedy(O.prefill(w, kv, cos_sin, p, t))))
     kv_gpu = kv.cuda()
     dec = make_decoder(w, kv_gpu, use_graph=use_graph, use_pdl=use_pdl, persistent=persistent)
+    for opt, value in (options or {}).items():
+        dec.set_option(opt, value)
     rows = len(prompts)
     lens = [n + 1 for n in prompt_lens]
     logits_gpu = torch.zeros(rows, g.vocab, dtype=torch.float32, device="cuda")

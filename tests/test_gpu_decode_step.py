@@ -30,6 +30,19 @@ def test_step_matches_oracle_for_every_batch_size(cuda_device, rows, persistent)
     assert r["kernels_per_step"] == (1 if persistent else 2 * 5 + 1)
 
 
+@pytest.mark.parametrize("mask", [0, 1, 2, 4, 7])
+@pytest.mark.parametrize("rows", [3, 4, 5, 8])
+def test_tcgen05_projections_match_oracle(cuda_device, rows, mask):
+    """The K = 1024 projections on tcgen05.mma (bit mask: 1 = QKV, 2 = gate/up, 4 = LM head) and on the
+    mma.sync kernels (0), each against the oracle; the vocabulary of 4,160 rows ends in a partial tile of
+    the LM head (64 rows per tile)."""
+    from dfb_b200 import native
+    lens = [3, 70, 250, 129, 64, 1, 300, 17][:rows]
+    r = H.run_parity_case(layers=2, vocab=4160, prompt_lens=lens, steps=3, seed=30 + rows,
+                          options={native.DFB_OPT_TCGEN05: mask})
+    _check(r)
+
+
 @pytest.mark.parametrize("prompt", [254, 255, 256, 257])
 def test_block_boundary(cuda_device, prompt):
     """Decode across the 256-token block boundary (the reference's
@@ -235,7 +248,7 @@ def test_look_ahead_prefetch_changes_nothing(cuda_device):
     lens = [40, 300, 7, 64, 129]
     g, w, kv, tables, first = _setup(lens, seed=25, layers=3)
     outs = []
-    for ahead in (1, 0):
+    for ahead in (31, 0):
         kvg = kv.cuda()
         dec = H.make_decoder(w, kvg)
         dec.set_option(native.DFB_OPT_LOOK_AHEAD, ahead)
@@ -279,8 +292,8 @@ def test_bad_token_id_is_reported_not_followed(cuda_device):
 def test_context_bound_too_small_is_reported(cuda_device):
     """``max_context`` below a row's real context would leave the chunk with the new token without a CTA:
     the kernel reports status 6, writes no K/V for that row and the merge tickets still balance (the next
-    correct step matches the oracle).  A position beyond the block-table columns given is status 2 with a
-    negative value, and the stale table entry is never read."""
+    correct step matches the oracle).  A position beyond the block-table columns given is caught the same
+    way (the grid never covers more than the given columns), so a stale table entry is never read."""
     lens = [200]
     g, w, kv, tables, first = _setup(lens, seed=27)
     kvg = kv.cuda()
@@ -296,7 +309,7 @@ def test_context_bound_too_small_is_reported(cuda_device):
     dec.enqueue_rows(ids, torch.tensor([300], device="cuda"), bt)      # position 300 needs a second column
     torch.cuda.synchronize()
     code, st = dec.status()
-    assert code == -4 and st.device_status == 2 and st.detail[2] == -2
+    assert code == -4 and st.device_status == 6 and st.detail[2] == 300
     assert torch.equal(kvg, before)
     # and a correct step afterwards is still right
     cos_sin = O.rope_cos_sin_table(g)
@@ -333,7 +346,7 @@ def test_option_and_tensor_parallel_argument_errors(cuda_device):
     for opt, bad in ((native.DFB_OPT_ROW_GEMV, 9), (native.DFB_OPT_STEP_MODE, 2), (native.DFB_OPT_SMEM_CARVEOUT, 101),
                      (native.DFB_OPT_SMEM_CARVEOUT_MMA, -2), (native.DFB_OPT_LATE_TRIGGER, 2),
                      (native.DFB_OPT_PAIR_GEMV, 5), (native.DFB_OPT_BULK_X, -1), (native.DFB_OPT_TP_FUSED, 3),
-                     (native.DFB_OPT_ATTN_WIDE, -1), (native.DFB_OPT_LOOK_AHEAD, 2),
+                     (native.DFB_OPT_ATTN_WIDE, -1), (native.DFB_OPT_LOOK_AHEAD, 64),
                      (native.DFB_OPT_LMHEAD_AHEAD_MB, 101), (native.DFB_OPT_PEER_WAIT_US, 0), (99, 0)):
         assert lib.dfb_set_option(h, opt, bad) == -1, (opt, bad)          # DFB_E_BAD_ARG
     # a single-GPU decoder has no exchange window, and a tensor-parallel group needs 2, 4 or 8 ranks

@@ -152,11 +152,13 @@ def test_full_depth_long_context_vs_oracle(full, rows):
         for r in range(rows):
             identical += toks[r] == int(want_tok[r])
             assert H.token_gap_ok(want_logits[r].float(), toks[r], int(want_tok[r])), (s, r)
-            # the new K/V rows: layer 0 sees identical inputs on both sides, so one bf16 step at most
+            # the new K/V rows: layer 0 sees identical inputs on both sides, so one bf16 step at most; the
+            # deeper layers inherit the rounding differences of the residual stream (K is normalised to
+            # unit RMS with entries up to about 5, so a 2 % difference of the stream is 0.1 there)
             blk, off = tables[r][positions[r] // g.block_size], positions[r] % g.block_size
             a, b = kv_gpu[:, :, blk, off].cpu().float(), kv[:, :, blk, off].float()
             assert float(((a[:, 0] - b[:, 0]).abs() / b[:, 0].abs().clamp(min=1.0)).max()) <= 2.0 ** -7, (s, r)
-            assert float((a - b).abs().max()) <= 2.0 ** -4, (s, r)
+            assert float((a - b).abs().max()) <= 0.25 and float((a - b).abs().mean()) <= 1.0e-2, (s, r)
         cur = [int(t) for t in want_tok]
         lens = [n + 1 for n in lens]
     print(f"rows {rows}: max|dlogit|={worst:.4f} mean={mean_worst:.5f} identical tokens {identical}/{rows * steps}")
