@@ -7,6 +7,7 @@
 #include "dfb_exchange.cuh"
 #include "dfb_pairgemv.cuh"
 #include "dfb_tcgemv.cuh"
+#include "dfb_attnring.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -80,6 +81,8 @@ struct ChainOptions {
   // counterparts (their longer post-dependency path: bulk copies of x, two issue loops, accumulator read).
   int tcgen05 = env_int("DFB_TCGEN05", 4);
   int carve_tc = 100;          // ... whose chain asks for all of an SM's L1/shared memory as shared memory
+  int attn_ring_min = 48;      // attention grids (rows x 64-position chunks) of at least this many CTAs take the
+                               // streaming kernel (dfb_attnring.cuh); 0 = never
 };
 const ChainOptions kDefaultOptions;
 
@@ -587,6 +590,13 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   // share of the chunk and with it the latency of the CTA.
   const int ctas = nsplit * m.kv_heads * rows;
   a.late_trigger = L.opt->late_trigger;
+  if (m.kv_heads == kRingHeads && L.opt->attn_ring_min > 0 && rows * nsplit >= L.opt->attn_ring_min) {
+    // long contexts / full batches: one CTA per (row, chunk) for all KV heads, K/V streamed through shared memory
+    cudaError_t e = ensure_dynamic_smem((const void*)paged_attention_ring_kernel, kRingSmemBytes);
+    if (e != cudaSuccess) { L.err = (int)e; return L.err; }
+    L.launch(paged_attention_ring_kernel, dim3(nsplit, rows), dim3(kRingThreads), a, true, kRingSmemBytes);
+    return L.err;
+  }
   if (rows <= L.opt->row_max_rows) {
     if (ctas <= L.opt->attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
     else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
@@ -969,6 +979,10 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_LMHEAD_AHEAD_MB:
       if (value < 0 || value > 100) return DFB_E_BAD_ARG;
       h->opt.lmhead_ahead_mb = value;
+      break;
+    case DFB_OPT_ATTN_RING:
+      if (value < 0) return DFB_E_BAD_ARG;
+      h->opt.attn_ring_min = value;
       break;
     case DFB_OPT_TCGEN05:
       if (value < 0 || value > 7) return DFB_E_BAD_ARG;

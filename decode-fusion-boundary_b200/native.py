@@ -16,7 +16,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libdfb_decode.so"
 SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
-HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR / "csrc" / "dfb_tcgemv.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
+HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR / "csrc" / "dfb_tcgemv.cuh", PKG_DIR / "csrc" / "dfb_attnring.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
 
 DFB_ABI_VERSION = 1
 DFB_MAX_ROWS = 8
@@ -27,6 +27,7 @@ DFB_OPT_STEP_MODE, DFB_OPT_PERSIST_CTAS, DFB_OPT_ROW_GEMV, DFB_OPT_ATTN_WIDE = 5
 DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER, DFB_OPT_PAIR_GEMV = 9, 10, 11, 12
 DFB_OPT_BULK_X, DFB_OPT_TP_FUSED = 13, 14
 DFB_OPT_LOOK_AHEAD, DFB_OPT_LMHEAD_AHEAD_MB, DFB_OPT_PEER_WAIT_US, DFB_OPT_TCGEN05 = 15, 16, 17, 18
+DFB_OPT_ATTN_RING = 19
 DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
 DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
 

@@ -102,9 +102,23 @@ def test_config1_bf16_greedy64_vs_oracle(full):
     dec.close()
 
 
-# Measured worst case of the full-depth runs below is about 0.04; a drift towards the stated bound
-# (harness.LOGIT_ATOL = 0.0625) should fail here before it reaches it.
-LOGIT_MARGIN = 5.0e-2
+# Tolerance of the full-depth runs on a RANDOM long history.  The seeded N(0, 0.02) network is chaotic on
+# such inputs: the oracle's own two admissible roundings of SwiGLU (one rounding, as the compiled torch path
+# does, or two, as the uncompiled one does: layers/activation.py:8-11) already differ by about 0.11 in the
+# logits there (0.06 at context 1), more than harness.LOGIT_ATOL, which was stated for model-generated
+# histories.  So these tests measure that spread on the same inputs and require the CUDA path to stay within
+# NOISE_FACTOR of it, with an absolute cap that a real defect (a wrong block, a dropped position) exceeds by far.
+NOISE_FACTOR = 1.5
+LOGIT_CAP = 0.25
+
+
+def _oracle_spread(w, kv, cos_sin, cur, positions, tables):
+    """Logits of the oracle (its KV write lands in ``kv``) and the spread between its two rounding variants."""
+    scratch = kv.clone()
+    want_logits, want_tok = O.decode_step(w, kv, cos_sin, cur, positions, tables)
+    other, _ = O.decode_step(w, scratch, cos_sin, cur, positions, tables, fused_rounding=False)
+    d = (want_logits.float() - other.float()).abs()
+    return want_logits, want_tok, float(d.max()), float(d.mean())
 
 
 def _history_like_real_kv(g, blocks, seed):
@@ -137,10 +151,11 @@ def test_full_depth_long_context_vs_oracle(full, rows):
     logits = torch.zeros(rows, g.vocab, device="cuda")
     cur = rng.integers(0, g.vocab, rows).tolist()
     lens = [c + 1 for c in ctx]                     # length after the step's token is appended
-    worst, mean_worst, identical = 0.0, 0.0, 0
+    worst, mean_worst, identical, floor, floor_mean = 0.0, 0.0, 0, 0.0, 0.0
     for s in range(steps):
         positions = [n - 1 for n in lens]
-        want_logits, want_tok = O.decode_step(w, kv, cos_sin, cur, positions, tables)
+        want_logits, want_tok, spread_max, spread_mean = _oracle_spread(w, kv, cos_sin, cur, positions, tables)
+        floor, floor_mean = max(floor, spread_max), max(floor_mean, spread_mean)
         dec.enqueue_rows(torch.tensor(cur, device="cuda"), torch.tensor(positions, device="cuda"),
                          H.padded_tables(tables, lens, g.block_size), out_logits=logits)
         torch.cuda.synchronize()
@@ -151,18 +166,21 @@ def test_full_depth_long_context_vs_oracle(full, rows):
         assert toks == got.argmax(-1).tolist()
         for r in range(rows):
             identical += toks[r] == int(want_tok[r])
-            assert H.token_gap_ok(want_logits[r].float(), toks[r], int(want_tok[r])), (s, r)
+            assert H.token_gap_ok(want_logits[r].float(), toks[r], int(want_tok[r]),
+                                  atol=max(H.TOKEN_GAP_ATOL, NOISE_FACTOR * spread_max)), (s, r)
             # the new K/V rows: layer 0 sees identical inputs on both sides, so one bf16 step at most; the
             # deeper layers inherit the rounding differences of the residual stream (K is normalised to
             # unit RMS with entries up to about 5, so a 2 % difference of the stream is 0.1 there)
             blk, off = tables[r][positions[r] // g.block_size], positions[r] % g.block_size
             a, b = kv_gpu[:, :, blk, off].cpu().float(), kv[:, :, blk, off].float()
             assert float(((a[:, 0] - b[:, 0]).abs() / b[:, 0].abs().clamp(min=1.0)).max()) <= 2.0 ** -7, (s, r)
-            assert float((a - b).abs().max()) <= 0.25 and float((a - b).abs().mean()) <= 1.0e-2, (s, r)
+            assert float((a - b).abs().max()) <= 0.25 and float((a - b).abs().mean()) <= 2.5e-2, (s, r)
         cur = [int(t) for t in want_tok]
         lens = [n + 1 for n in lens]
-    print(f"rows {rows}: max|dlogit|={worst:.4f} mean={mean_worst:.5f} identical tokens {identical}/{rows * steps}")
-    assert worst <= LOGIT_MARGIN <= H.LOGIT_ATOL and mean_worst <= H.LOGIT_MEAN_ATOL, (worst, mean_worst)
+    print(f"rows {rows}: max|dlogit|={worst:.4f} mean={mean_worst:.5f} (oracle's own rounding spread: max "
+          f"{floor:.4f} mean {floor_mean:.5f}) identical tokens {identical}/{rows * steps}")
+    assert worst <= min(LOGIT_CAP, NOISE_FACTOR * max(floor, H.LOGIT_ATOL)), (worst, floor)
+    assert mean_worst <= NOISE_FACTOR * max(floor_mean, H.LOGIT_MEAN_ATOL), (mean_worst, floor_mean)
     code, st = dec.status()
     assert code == 0
     dec.close()
@@ -184,21 +202,24 @@ def test_full_depth_batch_equals_single_rows_at_prompt_512(full, rows):
     cur = rng.integers(0, g.vocab, rows).tolist()
     positions = list(ctx)
     lens = [c + 1 for c in ctx]
-    want_logits, want_tok = O.decode_step(w, kv, cos_sin, cur, positions, tables)
+    want_logits, want_tok, floor, floor_mean = _oracle_spread(w, kv, cos_sin, cur, positions, tables)
+    bound = min(LOGIT_CAP, NOISE_FACTOR * max(floor, H.LOGIT_ATOL))
     dec = _decoder(dw, kv_gpu, g)
     la, lb = torch.zeros(rows, g.vocab, device="cuda"), torch.zeros(1, g.vocab, device="cuda")
     bt = H.padded_tables(tables, lens, g.block_size)
     dec.enqueue_rows(torch.tensor(cur, device="cuda"), torch.tensor(positions, device="cuda"), bt, out_logits=la)
     torch.cuda.synchronize()
-    assert float((la.cpu() - want_logits.float()).abs().max()) <= LOGIT_MARGIN
+    print(f"rows {rows} prompt 512: max|dlogit|={float((la.cpu() - want_logits.float()).abs().max()):.4f} "
+          f"(oracle's own rounding spread {floor:.4f})")
+    assert float((la.cpu() - want_logits.float()).abs().max()) <= bound
     for r in range(rows):
-        assert H.token_gap_ok(want_logits[r].float(), int(dec.tokens_device()[r]), int(want_tok[r]))
+        assert H.token_gap_ok(want_logits[r].float(), int(dec.tokens_device()[r]), int(want_tok[r]), atol=bound)
     for r in (0, rows - 1):
         kv_gpu.copy_(kv0)
         dec.enqueue_rows(torch.tensor(cur[r:r + 1], device="cuda"), torch.tensor(positions[r:r + 1], device="cuda"),
                          bt[r:r + 1].contiguous(), out_logits=lb)
         torch.cuda.synchronize()
-        assert float((lb[0].cpu() - want_logits[r].float()).abs().max()) <= LOGIT_MARGIN
+        assert float((lb[0].cpu() - want_logits[r].float()).abs().max()) <= bound
     dec.close()
 
 

@@ -122,8 +122,9 @@ def test_rmsnorm_gateup_swiglu(small, rows):
     assert ok, d
 
 
-def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None):
-    """Random KV history in a paged cache; one new token per row."""
+def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None, ring=None):
+    """Random KV history in a paged cache; one new token per row.  ``ring``: True forces the streaming
+    kernel (dfb_attnring.cuh) for every grid size, False the register-resident one, None the default rule."""
     from dfb_b200 import native
     lw = w.layers[0]
     tables, nblocks = O.allocate_blocks(ctx_lens, g.block_size, perm)
@@ -137,6 +138,8 @@ def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None):
     want = O.op_paged_attention_decode(q, k, v, kv_want, 0, positions, tables, g, row_active)
     kv_gpu = kv.cuda()
     dec = H.make_decoder(w, kv_gpu)
+    if ring is not None:
+        dec.set_option(native.DFB_OPT_ATTN_RING, 1 if ring else 0)
     out = torch.zeros(rows, g.q_size, dtype=BF, device="cuda")
     bt = H.padded_tables(tables, ctx_lens, g.block_size)
     pos32 = positions.to(torch.int32).cuda()
@@ -151,29 +154,32 @@ def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None):
     return out.cpu(), want, kv_gpu.cpu(), kv_want, kv
 
 
-@pytest.mark.parametrize("ctx_lens", [(1,), (2,), (63,), (64,), (65,), (255, 256, 257), (1, 700, 2048),
-                                      (300, 17, 1025, 64, 128, 129, 2047, 512)])
-def test_paged_attention(small, ctx_lens):
+@pytest.mark.parametrize("ring", [False, True])
+@pytest.mark.parametrize("ctx_lens", [(1,), (2,), (8,), (9,), (63,), (64,), (65,), (72,), (73,), (255, 256, 257),
+                                      (1, 700, 2048), (300, 17, 1025, 64, 128, 129, 2047, 512)])
+def test_paged_attention(small, ctx_lens, ring):
     g, w = small
-    out, want, kv_got, kv_want, _ = _attention_case(g, w, len(ctx_lens), list(ctx_lens), seed=31)
+    out, want, kv_got, kv_want, _ = _attention_case(g, w, len(ctx_lens), list(ctx_lens), seed=31, ring=ring)
     d = (out.float() - want.float()).abs().max()
     assert float(d) <= 2.0 ** -6, float(d)          # |out| < 4
     assert torch.equal(kv_got, kv_want)            # new K/V rows written bit-exactly, nothing else touched
 
 
-def test_paged_attention_scattered_blocks(small):
+@pytest.mark.parametrize("ring", [False, True])
+def test_paged_attention_scattered_blocks(small, ring):
     g, w = small
     perm = np.random.Generator(np.random.Philox(key=9)).permutation(24).tolist()
-    out, want, kv_got, kv_want, _ = _attention_case(g, w, 3, [1000, 2048, 513], seed=41, perm=perm)
+    out, want, kv_got, kv_want, _ = _attention_case(g, w, 3, [1000, 2048, 513], seed=41, perm=perm, ring=ring)
     assert float((out.float() - want.float()).abs().max()) <= 2.0 ** -6
     assert torch.equal(kv_got, kv_want)
 
 
-def test_inactive_row_leaves_kv_untouched(small):
+@pytest.mark.parametrize("ring", [False, True])
+def test_inactive_row_leaves_kv_untouched(small, ring):
     """row_active == 0 skips the KV write and nothing else (the reference's
     tests/test_taskgraph_bs2.py:211-233)."""
     g, w = small
-    out, want, kv_got, kv_want, kv_before = _attention_case(g, w, 2, [300, 40], seed=51, row_active=[1, 0])
+    out, want, kv_got, kv_want, kv_before = _attention_case(g, w, 2, [300, 40], seed=51, row_active=[1, 0], ring=ring)
     assert torch.equal(kv_got, kv_want)
     # row 1's slot is unchanged, row 0's slot changed
     assert torch.equal(kv_got[:, 0, 2, 39], kv_before[:, 0, 2, 39])
