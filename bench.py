@@ -938,7 +938,7 @@ def main():
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        # a rank that dies while its memory is bound to an NVLink multicast object faults its peers
+        # a rank that dies while its memory is bound to an in-switch reduction (NVLS) group faults its peers
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if args.profile_step:
         run_profile_step(args)

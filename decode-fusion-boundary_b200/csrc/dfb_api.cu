@@ -81,8 +81,9 @@ struct ChainOptions {
   // counterparts (their longer post-dependency path: bulk copies of x, two issue loops, accumulator read).
   int tcgen05 = env_int("DFB_TCGEN05", 4);
   int carve_tc = 100;          // ... whose chain asks for all of an SM's L1/shared memory as shared memory
-  int attn_ring_min = 48;      // attention grids (rows x 64-position chunks) of at least this many CTAs take the
-                               // streaming kernel (dfb_attnring.cuh); 0 = never
+  int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
+                               // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
+                               // to pay; smaller ones stay on the register-resident kernel; 0 = never
 };
 const ChainOptions kDefaultOptions;
 
@@ -273,6 +274,8 @@ int sm_count_cached() {
   return count[dev];
 }
 int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
+
+constexpr int kRingFlag = 256;   // bit of the split-bucket value that selects the streaming attention kernel
 
 // ---- kernel launch wrappers -------------------------------------------------
 // Launch one instantiation of the GEMV kernel; its dynamic shared memory (the
@@ -476,9 +479,9 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
     launch_row<1024, kModeNormSwiglu>(L, a, rows, a.n_tiles);
     return L.err;
   }
-  if (use_tc(L, rows, 2) && inter % 16 == 0) {
-    a.n_tiles = inter / 16;
-    launch_tc<kModeNormSwiglu, 64>(L, a, 2 * inter, 16, a.n_tiles);
+  if (use_tc(L, rows, 2) && inter % 32 == 0) {
+    a.n_tiles = inter / 32;   // a tile = 32 gate rows + the 32 matching up rows
+    launch_tc<kModeNormSwiglu, 128>(L, a, 2 * inter, 32, a.n_tiles);
     return L.err;
   }
   if (L.opt->pair_gemv && inter % 8 == 0) {
@@ -570,7 +573,9 @@ int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
 }
 
 int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
-                     int bt_stride, int bt_cols, const int* row_active, bf16* out, int rows, int nsplit) {
+                     int bt_stride, int bt_cols, const int* row_active, bf16* out, int rows, int nsplit_arg) {
+  const bool ring = (nsplit_arg & kRingFlag) != 0;   // set by split_bucket for long contexts
+  const int nsplit = nsplit_arg & (kRingFlag - 1);
   const DfbModelDesc& m = h->m;
   AttnArgs a = {};
   a.qkv = qkv; a.qkv_stride = h->qkv_rows(); a.q_size = h->q_size(); a.kv_size = h->kv_size();
@@ -590,11 +595,14 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   // share of the chunk and with it the latency of the CTA.
   const int ctas = nsplit * m.kv_heads * rows;
   a.late_trigger = L.opt->late_trigger;
-  if (m.kv_heads == kRingHeads && L.opt->attn_ring_min > 0 && rows * nsplit >= L.opt->attn_ring_min) {
+  if (ring && m.kv_heads == kRingHeads) {
     // long contexts / full batches: one CTA per (row, chunk) for all KV heads, K/V streamed through shared memory
     cudaError_t e = ensure_dynamic_smem((const void*)paged_attention_ring_kernel, kRingSmemBytes);
     if (e != cudaSuccess) { L.err = (int)e; return L.err; }
+    const int chain_carve = L.carve;
+    L.carve = 100;   // two CTAs of about 104 KB per SM
     L.launch(paged_attention_ring_kernel, dim3(nsplit, rows), dim3(kRingThreads), a, true, kRingSmemBytes);
+    L.carve = chain_carve;
     return L.err;
   }
   if (rows <= L.opt->row_max_rows) {
@@ -608,13 +616,18 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   return L.err;
 }
 
-int split_bucket(const DfbHandle* h, int max_context) {
+// Grid of the attention kernel for a context bound: the number of 64-position chunks rounded up to a power
+// of two (one captured graph per bucket), plus kRingFlag when rows x chunks is large enough for the streaming
+// kernel to keep about two CTAs per SM busy.
+int split_bucket(const DfbHandle* h, int max_context, int rows) {
   if (max_context < 1) max_context = 1;
   if (max_context > h->m.max_model_len) max_context = h->m.max_model_len;
   const int need = (max_context + kAttnChunk - 1) / kAttnChunk;
   int b = 1;
   while (b < need) b <<= 1;
-  return b > kMaxSplits ? kMaxSplits : b;
+  if (b > kMaxSplits) b = kMaxSplits;
+  const bool ring = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
+  return b | (ring ? kRingFlag : 0);
 }
 
 // The whole step as one chain of 5 kernels per layer + the LM head.
@@ -724,7 +737,7 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t strea
     return persistent ? enqueue_persistent(h, rows, stream, logits_out)
                       : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
   // one graph per (rows, split bucket, filled block-table columns)
-  const int key = persistent ? (1 << 20) + rows : ((bt_cols * 16 + rows) * 64 + nsplit) * 2 + (h->use_pdl ? 1 : 0);
+  const int key = persistent ? (1 << 24) + rows : ((bt_cols * 16 + rows) * 1024 + nsplit) * 2 + (h->use_pdl ? 1 : 0);
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
     cudaGraph_t graph = nullptr;
@@ -1038,7 +1051,7 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
     const int lowest = (s->block_table_cols - 1) * h->m.block_size + 1;   // the last column holds at least one token
     if (bound < lowest) bound = lowest;
   }
-  int rc = run_step(h, s->rows, split_bucket(h, bound), s->block_table_cols, stream, s->out_logits);
+  int rc = run_step(h, s->rows, split_bucket(h, bound, s->rows), s->block_table_cols, stream, s->out_logits);
   if (rc) return rc;
   if (s->out_tokens)
     DFB_CUDA(cudaMemcpyAsync(s->out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
@@ -1067,7 +1080,7 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
     for (int c = 0; c < cols; ++c) hs[24 + r * h->max_pages + c] = block_tables[r * cols + c];
   }
   DFB_CUDA(cudaMemcpyAsync(h->stage, hs, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
-  int rc = run_step(h, rows, split_bucket(h, max_ctx), cols, stream, nullptr);
+  int rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, stream, nullptr);
   if (rc) return rc;
   DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   DFB_CUDA(cudaStreamSynchronize(stream));
@@ -1134,7 +1147,7 @@ int dfb_launch_attention(DfbHandle* h, int32_t layer, const void* qkv, const int
   Launcher L{(cudaStream_t)stream, false};
   L.opt = &h->opt;
   return launch_attention(L, h, layer, (const bf16*)qkv, positions, block_tables, block_table_stride, 0, row_active,
-                          (bf16*)attn_out, rows, split_bucket(h, max_context > 0 ? max_context : h->m.max_model_len));
+                          (bf16*)attn_out, rows, split_bucket(h, max_context > 0 ? max_context : h->m.max_model_len, rows));
 }
 
 int dfb_launch_linear(const void* x, const void* w, void* out, int32_t rows, int32_t n, int32_t k,

@@ -4,20 +4,25 @@
 //
 // A CTA owns one batch row and one chunk of 64 context positions for ALL eight
 // KV heads.  In the cache ([block][position][kv_head][128]) the eight heads of a
-// position are one contiguous 2 KB run for K and one for V, so the chunk is
-// fetched position by position with bulk copies (TMA, completion on an
-// mbarrier) into a ring of three shared-memory stages of 8 positions each; the
-// stages of the next positions are in flight while the current one is scored,
-// and the first three are requested before the dependency wait (the old entries
-// do not depend on the previous kernel).  Position rows are padded by 16 bytes
-// in shared memory, which makes the 16-byte reads of eight different positions
-// by the lanes of a quarter warp conflict-free.
+// position are one contiguous 2 KB run for K and one for V, and consecutive
+// positions of a block follow one another, so a stage of 8 positions is ONE
+// bulk copy (TMA, completion on an mbarrier) of 16 KB for K and one for V into
+// a ring of three shared-memory stages; the next stages are in flight while
+// the current one is scored, and the first three are requested before the
+// dependency wait (the old entries do not depend on the previous kernel).  A
+// stage is always fetched whole: slots of the block beyond the row's context,
+// and the new token's own slot, are allocated memory whose contents are
+// ignored (masked, respectively replaced from shared memory).  The warp that
+// finishes a stage last requests the next one into it, so nobody waits to
+// refill.
 //
 // Warp w owns KV head w and its two query heads.  Scores: lane (p, quarter)
-// takes position p of the stage and 32 of the 128 dimensions (four 16-byte
-// reads of K against q values held in registers as packed bf16), two shuffles
-// add the quarters; the online softmax needs one warp reduction per stage, not
-// one per position.  P.V: lane l owns output dimensions [4 l, 4 l + 4) and walks
+// takes position p of the stage and four 16-byte pieces of its K row against q
+// values held in registers as packed bf16; the pieces are dealt so that the
+// eight lanes of a quarter warp read eight different 16-byte bank groups (piece
+// (4 quarter + i + p) mod 16 in step i), which keeps the dense rows free of
+// bank conflicts; two shuffles add the quarters; the online softmax needs one
+// warp reduction per stage, not one per position.  P.V: lane l owns output dimensions [4 l, 4 l + 4) and walks
 // the positions of the stage (8-byte reads of V, the probabilities by shuffle).
 // Per context position this is about a third of the instructions of the
 // register-resident kernel, whose CTAs load, then compute with nothing in
@@ -35,13 +40,25 @@ namespace dfb {
 constexpr int kRingPos = 8;                          // positions per stage
 constexpr int kRingStages = 3;
 constexpr int kRingHeads = 8;                        // KV heads = warps
-constexpr int kRingRowBytes = kRingHeads * kHeadDim * 2 + 16;    // one position, padded
+constexpr int kRingRowBytes = kRingHeads * kHeadDim * 2;         // one position: 2 KB, dense
 constexpr int kRingStageBytes = 2 * kRingPos * kRingRowBytes;    // K rows, then V rows
 constexpr int kRingSubs = kAttnChunk / kRingPos;     // stages a full chunk goes through
 constexpr int kRingThreads = 32 * kRingHeads;
 constexpr int kRingSmemBytes = kRingStages * kRingStageBytes + 128;
 constexpr int kKernelAttnRing = 7;
 
+__device__ __forceinline__ void fence_async_smem_ring() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// reductions over the 8 positions of a stage: lanes that differ only in bits 3-4 (the quarters) hold equal values
+__device__ __forceinline__ float pos_max(float v) {
+#pragma unroll
+  for (int m = 4; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+__device__ __forceinline__ float pos_sum(float v) {
+#pragma unroll
+  for (int m = 4; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
@@ -77,7 +94,8 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
   if (split >= nsplits) return;
 
   extern __shared__ __align__(128) unsigned char ring_smem[];
-  __shared__ uint64_t full[kRingStages], empty[kRingStages];
+  __shared__ uint64_t full[kRingStages];
+  __shared__ unsigned int done[kRingStages];    // warps that have finished the stage's current contents
   __shared__ __align__(16) __nv_bfloat16 qsm[kRingHeads][2][kHeadDim];   // q after norm + RoPE (bf16 values)
   __shared__ __align__(16) __nv_bfloat16 knew[kRingHeads][kHeadDim];
   __shared__ __align__(16) __nv_bfloat16 vnew[kRingHeads][kHeadDim];
@@ -103,30 +121,20 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kRingStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kRingHeads); }
+    for (int s = 0; s < kRingStages; ++s) { mbar_init(&full[s], 1); done[s] = 0u; }
     fence_mbar_init();
   }
   __syncthreads();
 
-  // warp 0 requests stage j: lanes 0-7 the K rows, lanes 8-15 the V rows; the new token's own slot is not
-  // in the cache yet and is left out (its row of the stage is filled in from shared memory later)
+  // one elected lane requests stage j: the 8 positions' K rows as one copy, their V rows as another
   auto issue_stage = [&](int j) {
     const int s = j % kRingStages;
-    const int p0 = start + j * kRingPos;
-    int cnt = min(kRingPos, end - p0);
-    if (owner && pos >= p0 && pos < p0 + kRingPos) --cnt;
-    if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(cnt * 2 * (kRingRowBytes - 16)));
-    __syncwarp();
-    if (lane < 2 * kRingPos) {
-      const int p = lane & (kRingPos - 1), isv = lane >> 3;
-      const int gp = p0 + p;
-      if (gp < end && gp != pos) {
-        const __nv_bfloat16* src = (isv ? a.v_cache : a.k_cache) + chunk_base + (size_t)(j * kRingPos + p) * tok_stride;
-        bulk_g2s(ring_smem + s * kRingStageBytes + (isv * kRingPos + p) * kRingRowBytes, src, kRingRowBytes - 16, &full[s]);
-      }
-    }
+    mbar_expect_tx(&full[s], (uint32_t)kRingStageBytes);
+    const size_t off = chunk_base + (size_t)(j * kRingPos) * tok_stride;
+    bulk_g2s(ring_smem + s * kRingStageBytes, a.k_cache + off, kRingPos * kRingRowBytes, &full[s]);
+    bulk_g2s(ring_smem + s * kRingStageBytes + kRingPos * kRingRowBytes, a.v_cache + off, kRingPos * kRingRowBytes, &full[s]);
   };
-  if (warp == 0) {
+  if (tid == 0) {
     for (int j = 0; j < kRingStages && j < nsub; ++j) issue_stage(j);
   }
   if (tid >= 32 && tid < 64)
@@ -194,13 +202,15 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
     *reinterpret_cast<uint4*>((lane < 16 ? a.k_cache : a.v_cache) + off) = piece;
   }
 
-  // this lane's quarter (32 dimensions) of the two query heads, packed bf16
+  // this lane's four 16-byte pieces (8 dimensions each) of the two query heads, packed bf16: piece
+  // (4 quarter + i + p) mod 16 in step i, the same pieces it reads of its position's K row
   const int qp = lane & (kRingPos - 1), quarter = lane >> 3;
   uint4 q0r[4], q1r[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    q0r[c] = reinterpret_cast<const uint4*>(qsm[warp][0] + 32 * quarter)[c];
-    q1r[c] = reinterpret_cast<const uint4*>(qsm[warp][1] + 32 * quarter)[c];
+    const int piece = (4 * quarter + c + qp) & 15;
+    q0r[c] = reinterpret_cast<const uint4*>(qsm[warp][0])[piece];
+    q1r[c] = reinterpret_cast<const uint4*>(qsm[warp][1])[piece];
   }
 
   constexpr float kLog2e = 1.4426950408889634f;
@@ -225,16 +235,22 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
     // ---- scores of position qp: this lane's 32 dimensions, then the four quarters are added ----
     float d0 = 0.f, d1 = 0.f;
     {
-      const unsigned char* krow = kst + qp * kRingRowBytes + warp * (kHeadDim * 2) + 64 * quarter;
+      const unsigned char* krow = kst + qp * kRingRowBytes + warp * (kHeadDim * 2);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const uint4 kv = *reinterpret_cast<const uint4*>(krow + 16 * c);
+        const uint4 kv = *reinterpret_cast<const uint4*>(krow + 16 * ((4 * quarter + c + qp) & 15));
         float kf[8], qa[8], qb[8];
         unpack8(kv, kf);
         unpack8(q0r[c], qa);
         unpack8(q1r[c], qb);
+        float t0 = kf[0] * qa[0], t1 = kf[0] * qb[0], u0 = kf[1] * qa[1], u1 = kf[1] * qb[1];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { d0 = fmaf(kf[e], qa[e], d0); d1 = fmaf(kf[e], qb[e], d1); }
+        for (int e = 2; e < 8; e += 2) {
+          t0 = fmaf(kf[e], qa[e], t0); t1 = fmaf(kf[e], qb[e], t1);
+          u0 = fmaf(kf[e + 1], qa[e + 1], u0); u1 = fmaf(kf[e + 1], qb[e + 1], u1);
+        }
+        d0 += t0 + u0;
+        d1 += t1 + u1;
       }
     }
     d0 += __shfl_xor_sync(0xffffffffu, d0, 8);  d1 += __shfl_xor_sync(0xffffffffu, d1, 8);
@@ -242,12 +258,11 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
     const bool valid = qp < npos;
     const float s0 = valid ? d0 * a.scale : -INFINITY, s1 = valid ? d1 * a.scale : -INFINITY;
     // ---- online softmax over the stages (every lane holds the same running maximum and sum) ----
-    const float n0 = fmaxf(m0, warp_max(s0)), n1 = fmaxf(m1, warp_max(s1));   // a stage has at least one position
+    const float n0 = fmaxf(m0, pos_max(s0)), n1 = fmaxf(m1, pos_max(s1));   // a stage has at least one position
     const float c0 = exp2f((m0 - n0) * kLog2e), c1 = exp2f((m1 - n1) * kLog2e);   // first stage: exp2(-inf) = 0
     const float p0v = exp2f((s0 - n0) * kLog2e), p1v = exp2f((s1 - n1) * kLog2e); // invalid positions: 0
-    // the four quarters hold the same probabilities: a quarter's sum is a fourth of the warp's (exact)
-    l0 = l0 * c0 + 0.25f * warp_sum(p0v);
-    l1 = l1 * c1 + 0.25f * warp_sum(p1v);
+    l0 = l0 * c0 + pos_sum(p0v);
+    l1 = l1 * c1 + pos_sum(p1v);
     m0 = n0; m1 = n1;
 #pragma unroll
     for (int e = 0; e < 4; ++e) { o0[e] *= c0; o1[e] *= c1; }
@@ -264,17 +279,21 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
       }
     }
     __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
-    if (warp == 0 && j + kRingStages < nsub) {
-      // every warp is done with stage s: request the positions three stages ahead into it
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (j / kRingStages) & 1))) { ok = false; break; }
-      issue_stage(j + kRingStages);
+    if (j + kRingStages < nsub && lane == 0) {
+      // the warp that finishes the stage last requests the positions three stages ahead into it
+      __threadfence_block();
+      if (atomicAdd(&done[s], 1u) == kRingHeads - 1) {
+        done[s] = 0u;
+        __threadfence_block();
+        fence_async_smem_ring();
+        issue_stage(j + kRingStages);
+      }
     }
   }
   if (!ok) {
     report_status(a.status, kStatusCopyTimeout, kKernelAttnRing, blockIdx.x, row);
     // give the copies in flight a bounded chance to land before the CTA goes away
-    if (warp == 0) for (int s = 0; s < kRingStages; ++s) mbar_wait_bounded(&full[s], 0);
+    if (warp == 0) for (int s = 0; s < kRingStages; ++s) { mbar_wait_bounded(&full[s], 0); mbar_wait_bounded(&full[s], 1); }
   }
   if (tid == 0) trace_max(a.trace, 5);
 

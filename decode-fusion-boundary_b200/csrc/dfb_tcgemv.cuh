@@ -22,17 +22,18 @@
 // ring of eight shared-memory stages = one tile; the requests of the first tile
 // are issued BEFORE the dependency wait (the weights do not depend on the
 // previous kernel), so for the per-layer projections, whose CTAs own one tile,
-// the whole tile is on its way before the activations exist.  Two issuer warps
-// (one elected thread each) take alternate stages: 4 MMAs per stage (K = 16
+// the whole tile is on its way before the activations exist.  Four issuer warps
+// (one elected thread each) take every fourth stage: 4 MMAs per stage (K = 16
 // each) into the issuer's own accumulator, a commit to the stage's "empty"
-// barrier and, after the tile's last stage, to the accumulators' "full"
-// barrier.  Four epilogue warps first build the B operand: the rows of h and
+// barrier and, after the issuer's last stage of the tile, to the accumulators'
+// "full" barrier.  Eight prologue warps build the B operand: the rows of h and
 // of the residual arrive by bulk copies (TMA), then add + RMSNorm, bf16,
-// written in the swizzled K-major layout.  Then they read the accumulators with
-// tcgen05.ld, add the issuers' accumulators and the two diagonal blocks (the
-// latter through shared memory), round once to bf16 and run the epilogue.  Two
-// accumulator buffers let the MMAs of the next tile run under the epilogue of
-// the current one (LM head).  There is no CTA-wide barrier inside the loop.
+// written in the swizzled K-major layout.  Four of them go on as the epilogue:
+// they read the accumulators with tcgen05.ld, add the issuers' accumulators and
+// the two diagonal blocks (the latter through shared memory), round once to
+// bf16 and run the epilogue.  Two accumulator buffers let the MMAs of the next
+// tile run under the epilogue of the current one (LM head).  There is no
+// CTA-wide barrier inside the loop.
 //
 // Every wait is bounded: on expiry the waiting thread records status 3 in the
 // decoder's status word, raises the CTA's abort flag, every role drains, the
@@ -53,8 +54,11 @@ struct TcArgs {
   alignas(64) CUtensorMap wmap;     // W as [n_rows, 1024] bf16, box {64 columns, BOX rows}, 128-byte swizzle
 };
 
-constexpr int kTcIssuers = 2;       // MMA-issuing warps; each owns every kTcIssuers-th k-block and its own accumulator
-constexpr int kTcThreads = 32 * (1 + kTcIssuers + 4);   // warp 0: TMA, warps 1-2: MMA, warps 3-6: prologue + epilogue
+constexpr int kTcIssuers = 4;       // MMA-issuing warps; each owns every kTcIssuers-th k-block and its own accumulator
+constexpr int kTcProWarps = 8;      // warps building the B operand; the first four of them also run the epilogue
+constexpr int kTcProThreads = 32 * kTcProWarps;
+constexpr int kTcFirstPro = 1 + kTcIssuers;             // warp 0: TMA, warps 1-4: MMA, warps 5-12: prologue (5-8: epilogue)
+constexpr int kTcThreads = 32 * (kTcFirstPro + kTcProWarps);
 constexpr int kTcK = 1024;
 constexpr int kTcKbPairs = kTcK / 128;   // stages per tile: 64 columns of each half of K
 constexpr int kTcAccCols = 16 * kTcIssuers;   // tensor-memory columns of one accumulator buffer
@@ -113,7 +117,7 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate));
 }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -132,6 +136,17 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 8 consecutive accumulator columns of this thread's lane
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Bounded mbarrier wait that also gives up when another role of the CTA has failed.
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (int i = 0; i < kMbarSpinLimit; ++i) {
@@ -141,16 +156,16 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile
   return false;
 }
 
-// MT = 2 x (weight rows per tile): 64 for the per-layer projections (32 rows, SwiGLU: 16 gate + 16 up),
-// 128 for the LM head (64 rows per tile, persistent CTAs).
+// MT = 2 x (weight rows per tile): 64 for QKV (32 rows per tile), 128 for gate/up (32 gate + 32 up rows)
+// and for the LM head (64 rows per tile, persistent CTAs).
 //
 // Issue rate.  One thread issues a tcgen05.mma of this size (N = 16) about every 51 cycles at best,
-// whatever M is, while the tensor core needs only 8-16; two issuing warps double the rate until the
+// whatever M is, while the tensor core needs only 8-16; several issuing warps multiply the rate until the
 // operand reads from shared memory (about 110 bytes per cycle) become the limit.  So the k-blocks of a
-// tile alternate between two issuer warps, each with its own accumulator, the issue loops are fully
-// unrolled with the descriptors advanced by additions only, and the epilogue adds the two accumulators.
+// tile are dealt to four issuer warps, each with its own accumulator, the issue loops are fully unrolled
+// with the descriptors advanced by additions only, and the epilogue adds the four accumulators.
 template <int MODE, int MT>
-__global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(const __grid_constant__ TcArgs args) {
+__global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_constant__ TcArgs args) {
   const GemvArgs& a = args.g;
   constexpr int R = MT / 2;
   constexpr bool kSwiglu = MODE == kModeNormSwiglu;
@@ -159,7 +174,6 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
   constexpr int STAGES = SM::kStages;
   static_assert(MODE != kModeStore, "the plain projections (K = 2048 / 3072) have their own kernels");
   static_assert(MT == 64 || MT == 128, "M of the MMA");
-  static_assert(!kSwiglu || R == 32, "one SwiGLU output per epilogue thread");
   if (!a.late_trigger) pdl_launch_dependents();
   if (threadIdx.x == 0) trace_min(a.trace, 0);
 
@@ -179,7 +193,7 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_in + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
-  __shared__ __align__(16) float ssq[4][kMaxRows];
+  __shared__ __align__(16) float ssq[kTcProWarps][kMaxRows];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = a.n_tiles, stride = gridDim.x;
@@ -189,7 +203,7 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(&acc_full[0], kTcIssuers); mbar_init(&acc_full[1], kTcIssuers);
     mbar_init(&acc_empty[0], 128); mbar_init(&acc_empty[1], 128);
-    mbar_init(x_ready, 128);
+    mbar_init(x_ready, kTcProThreads);
     mbar_init(x_in, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -240,15 +254,12 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
     }
     __syncwarp();
   } else if (warp <= kTcIssuers) {
-    // ---------------- MMA issuers: warp 1 takes the even k-blocks, warp 2 the odd ones ----------------
+    // ---------------- MMA issuers: issuer i takes the k-blocks i, i + 4 ----------------
     if (lane == 0) {
       const int issuer = warp - 1;
       constexpr uint32_t idesc = tc_idesc(MT, 16);
       const uint64_t a_desc = tc_smem_desc(smem_u32(stages)), b_desc = tc_smem_desc(smem_u32(xs));
       bool ok = tc_wait(x_ready, 0, abort_flag);
-#ifdef DFB_TC_PROBE
-      if (a.trace && issuer == 0) atomicMax(a.trace + 5, global_ns());
-#endif
       tc_fence_after();
       int it = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += stride, ++it) {
@@ -271,9 +282,6 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
         }
         if (!ok) break;
         tc_commit(&acc_full[buf]);
-#ifdef DFB_TC_PROBE
-        if (a.trace && it == 0) atomicMax(a.trace + 6, global_ns());
-#endif
       }
       if (!ok) {
         if (!*abort_flag) report_status(a.status, kStatusCopyTimeout, kKernelTcGemv, blockIdx.x, 2);
@@ -282,80 +290,65 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
     }
     __syncwarp();
   } else {
-    // ---------------- prologue + epilogue: 128 threads ----------------
-    const int et = tid - 32 * (1 + kTcIssuers), ewarp = warp - (1 + kTcIssuers);
-    const uint4 nw = ldg_stream(a.norm_w + 8 * et);
+    // ---------------- prologue: 256 threads; epilogue: the first 128 of them ----------------
+    const int pt = tid - 32 * kTcFirstPro, pwarp = warp - kTcFirstPro;
+    const uint2 nw = *reinterpret_cast<const uint2*>(a.norm_w + 4 * pt);
     // The rows of h and of the residual come in by bulk copies (TMA): ordinary loads issued here would
     // queue in the load/store unit behind the loads of the successor kernel that was let in early.
     const bool bulk_x = a.ids == nullptr && a.res_in != nullptr;
-    if (bulk_x && et == 0) mbar_expect_tx(x_in, (uint32_t)(a.rows * 2 * kTcK * 2));
-    named_sync(1, 128);      // the byte count is posted before any copy can complete
+    if (bulk_x && pt == 0) mbar_expect_tx(x_in, (uint32_t)(a.rows * 2 * kTcK * 2));
+    named_sync(1, kTcProThreads);      // the byte count is posted before any copy can complete
     pdl_wait();
-#ifdef DFB_TC_PROBE2
-    const unsigned long long q_a = global_ns();
-#endif
-    if (et == 0) {
-      trace_max(a.trace, 1); trace_min(a.trace, 3);
-    }
-    if (bulk_x && et < 16) {
+    if (pt == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
+    if (bulk_x && pt < 16) {
       // sixteen threads issue one row copy each (one thread issuing all of them is slower than the copies)
-      const int b = et & 7;
+      const int b = pt & 7;
       if (b < a.rows) {
-        if (et < 8) bulk_g2s(xs + b * 2 * kTcK, a.x + (size_t)b * kTcK, 2 * kTcK, x_in);
+        if (pt < 8) bulk_g2s(xs + b * 2 * kTcK, a.x + (size_t)b * kTcK, 2 * kTcK, x_in);
         else bulk_g2s(rstage + b * 2 * kTcK, a.res_in + (size_t)b * kTcK, 2 * kTcK, x_in);
       }
     }
 
-#ifdef DFB_TC_PROBE2
-    unsigned long long q_b = 0, q_c = 0;
-#endif
     // x = h (+ residual), bf16 residual out, RMSNorm, bf16 y in the swizzled layout of the B operand:
-    // this thread owns columns [8 et, 8 et + 8) = one 16-byte chunk of every batch row
+    // this thread owns columns [4 pt, 4 pt + 4) = half of one 16-byte chunk of every batch row
     {
-      const int k0 = 8 * et, half = k0 >> 9, kk = k0 & 511, kb = kk >> 6, c = (kk & 63) >> 3;
-      uint4 hv[kMaxRows], rv[kMaxRows];
+      const int k0 = 4 * pt, half = k0 >> 9, kk = k0 & 511, kb = kk >> 6, c = (kk & 63) >> 3, sub = (k0 >> 2) & 1;
+      uint2 hv[kMaxRows], rv[kMaxRows];
       if (bulk_x) {
-        if (!named_sync_and(1, 128, tc_wait(x_in, 0, abort_flag))) {
-          if (et == 0 && !*abort_flag) report_status(a.status, kStatusCopyTimeout, kKernelTcGemv, blockIdx.x, 4);
+        if (!named_sync_and(1, kTcProThreads, tc_wait(x_in, 0, abort_flag))) {
+          if (pt == 0 && !*abort_flag) report_status(a.status, kStatusCopyTimeout, kKernelTcGemv, blockIdx.x, 4);
           *abort_flag = 1;
         }
 #pragma unroll
         for (int b = 0; b < kMaxRows; ++b) {
-          hv[b] = make_uint4(0, 0, 0, 0);
-          rv[b] = make_uint4(0, 0, 0, 0);
+          hv[b] = make_uint2(0, 0);
+          rv[b] = make_uint2(0, 0);
           if (b < a.rows) {
-            hv[b] = *reinterpret_cast<const uint4*>(xs + b * 2 * kTcK + 16 * et);
-            rv[b] = *reinterpret_cast<const uint4*>(rstage + b * 2 * kTcK + 16 * et);
+            hv[b] = *reinterpret_cast<const uint2*>(xs + b * 2 * kTcK + 8 * pt);
+            rv[b] = *reinterpret_cast<const uint2*>(rstage + b * 2 * kTcK + 8 * pt);
           }
         }
       } else {
 #pragma unroll
         for (int b = 0; b < kMaxRows; ++b) {
-          hv[b] = make_uint4(0, 0, 0, 0);
-          rv[b] = make_uint4(0, 0, 0, 0);
+          hv[b] = make_uint2(0, 0);
+          rv[b] = make_uint2(0, 0);
           if (b < a.rows) {
             const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[b], a.embed_rows, a.status, b) : (size_t)b;
-            hv[b] = ldg_cg(a.x + xrow * kTcK + k0);
-            if (a.res_in) rv[b] = ldg_cg(a.res_in + (size_t)b * kTcK + k0);
+            hv[b] = __ldcg(reinterpret_cast<const uint2*>(a.x + xrow * kTcK + k0));
+            if (a.res_in) rv[b] = __ldcg(reinterpret_cast<const uint2*>(a.res_in + (size_t)b * kTcK + k0));
           }
         }
       }
-#ifdef DFB_TC_PROBE2
-      q_b = global_ns();
-#endif
       if (a.late_trigger) pdl_launch_dependents();   // the successor's prefetch traffic starts after x is here
       // All eight rows advance in lockstep through every dependent step (sums, butterflies, roots), so the
       // latency of a step is paid once, not once per row.
-      float x[kMaxRows][8], ss[kMaxRows];
+      float x[kMaxRows][4], ss[kMaxRows];
 #pragma unroll
       for (int b = 0; b < kMaxRows; ++b) {
-        float hf[8], rf[8];
-        unpack8(hv[b], hf);
-        unpack8(rv[b], rf);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) x[b][e] = hf[e] + rf[e];
-        ss[b] = ((x[b][0] * x[b][0] + x[b][1] * x[b][1]) + (x[b][2] * x[b][2] + x[b][3] * x[b][3])) +
-                ((x[b][4] * x[b][4] + x[b][5] * x[b][5]) + (x[b][6] * x[b][6] + x[b][7] * x[b][7]));
+        x[b][0] = bf_lo(hv[b].x) + bf_lo(rv[b].x); x[b][1] = bf_hi(hv[b].x) + bf_hi(rv[b].x);
+        x[b][2] = bf_lo(hv[b].y) + bf_lo(rv[b].y); x[b][3] = bf_hi(hv[b].y) + bf_hi(rv[b].y);
+        ss[b] = (x[b][0] * x[b][0] + x[b][1] * x[b][1]) + (x[b][2] * x[b][2] + x[b][3] * x[b][3]);
       }
 #pragma unroll
       for (int m = 16; m >= 1; m >>= 1) {
@@ -366,48 +359,39 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
         for (int b = 0; b < kMaxRows; ++b) ss[b] += other[b];
       }
       if (lane == 0) {
-        *reinterpret_cast<float4*>(&ssq[ewarp][0]) = make_float4(ss[0], ss[1], ss[2], ss[3]);
-        *reinterpret_cast<float4*>(&ssq[ewarp][4]) = make_float4(ss[4], ss[5], ss[6], ss[7]);
+        *reinterpret_cast<float4*>(&ssq[pwarp][0]) = make_float4(ss[0], ss[1], ss[2], ss[3]);
+        *reinterpret_cast<float4*>(&ssq[pwarp][4]) = make_float4(ss[4], ss[5], ss[6], ss[7]);
       }
       if (a.res_out && blockIdx.x == 0) {
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) {
-          if (b < a.rows) {
-            uint4 o;
-            o.x = pack_bf16(x[b][0], x[b][1]); o.y = pack_bf16(x[b][2], x[b][3]);
-            o.z = pack_bf16(x[b][4], x[b][5]); o.w = pack_bf16(x[b][6], x[b][7]);
-            *reinterpret_cast<uint4*>(a.res_out + (size_t)b * kTcK + k0) = o;
-          }
-        }
+        for (int b = 0; b < kMaxRows; ++b)
+          if (b < a.rows)
+            *reinterpret_cast<uint2*>(a.res_out + (size_t)b * kTcK + k0) =
+                make_uint2(pack_bf16(x[b][0], x[b][1]), pack_bf16(x[b][2], x[b][3]));
       }
-      named_sync(1, 128);    // also: every thread has read its chunks of xs before anyone overwrites them
-      float wf[8], rstd[kMaxRows];
-      unpack8(nw, wf);
+      named_sync(1, kTcProThreads);    // also: every thread has read its pieces of xs before anyone overwrites them
+      const float w0 = bf_lo(nw.x), w1 = bf_hi(nw.x), w2 = bf_lo(nw.y), w3 = bf_hi(nw.y);
+      float rstd[kMaxRows];
 #pragma unroll
       for (int b = 0; b < kMaxRows; ++b) {
-        const float4 s4 = make_float4(ssq[0][b], ssq[1][b], ssq[2][b], ssq[3][b]);
-        rstd[b] = 1.0f / sqrtf(((s4.x + s4.y) + (s4.z + s4.w)) / (float)kTcK + a.eps);
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kTcProWarps; ++w) tot += ssq[w][b];
+        rstd[b] = 1.0f / sqrtf(tot / (float)kTcK + a.eps);
       }
 #pragma unroll
-      for (int b = 0; b < kMaxRows; ++b) {
-        float y[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = round_bf16(x[b][e] * rstd[b]) * wf[e];   // rows beyond the batch are zero
-        uint4 o;
-        o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
+      for (int b = 0; b < kMaxRows; ++b) {   // rows beyond the batch are zero
+        const uint2 o = make_uint2(pack_bf16(round_bf16(x[b][0] * rstd[b]) * w0, round_bf16(x[b][1] * rstd[b]) * w1),
+                                   pack_bf16(round_bf16(x[b][2] * rstd[b]) * w2, round_bf16(x[b][3] * rstd[b]) * w3));
         const int n = b + 8 * half;
-        *reinterpret_cast<uint4*>(xs + kb * 2048 + n * 128 + ((c ^ (n & 7)) << 4)) = o;
+        *reinterpret_cast<uint2*>(xs + kb * 2048 + n * 128 + ((c ^ (n & 7)) << 4) + 8 * sub) = o;
       }
     }
     fence_async_smem();      // the MMAs read shared memory through the async proxy
     tc_mbar_arrive(x_ready);
-#ifdef DFB_TC_PROBE2
-    if (a.trace && et == 5) {
-      const unsigned long long q_d = global_ns();
-      atomicMax(a.trace + 5, q_b - q_a); atomicMax(a.trace + 6, q_c - q_b); atomicMax(a.trace + 7, q_d - q_c);
-    }
-#endif
-    if (et == 0) trace_max(a.trace, 4);
+    if (pt == 0) trace_max(a.trace, 4);
+    if (pwarp < 4) {
+    const int et = pt, ewarp = pwarp;
 
     // epilogue thread -> batch row eb and rows er, er + 16, ... of the tile
     const int eb = et >> 4, er = et & 15;
@@ -421,34 +405,35 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles; tile += stride, ++it) {
       const int buf = it & 1;
-      if (!named_sync_and(1, 128, tc_wait(&acc_full[buf], (it >> 1) & 1, abort_flag))) { ok = false; break; }
-#ifdef DFB_TC_PROBE
-      if (a.trace && it == 0 && et == 0) atomicMax(a.trace + 7, global_ns());
-#endif
+      if (!named_sync_and(2, 128, tc_wait(&acc_full[buf], (it >> 1) & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
-      float v[16], v2[16];
-      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + buf * kTcAccCols;
-      tc_ld16(taddr, v);
-      tc_ld16(taddr + 16, v2);                    // the second issuer's accumulator
+      // this lane's 8 useful columns (its half of K) of every issuer's accumulator
+      float v[kTcIssuers][8];
+      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + buf * kTcAccCols + 8 * h;
+#pragma unroll
+      for (int u = 0; u < kTcIssuers; ++u) tc_ld8(taddr + 16 * u, v[u]);
+      tc_wait_ld();
       tc_fence_before();
       tc_mbar_arrive(&acc_empty[buf]);            // the accumulators may be overwritten by the tile after next
       float* rb = red + (size_t)buf * 2 * kMaxRows * R;
       if (lvalid) {
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) rb[(h * kMaxRows + b) * R + lrow] = v[8 * h + b] + v2[8 * h + b];
+        for (int b = 0; b < kMaxRows; ++b) rb[(h * kMaxRows + b) * R + lrow] = (v[0][b] + v[1][b]) + (v[2][b] + v[3][b]);
       }
-      named_sync(1, 128);
-#if !defined(DFB_TC_PROBE) && !defined(DFB_TC_PROBE2)
+      named_sync(2, 128);
       if (et == 0 && it == 0) trace_max(a.trace, 5);
-#endif
       if (kSwiglu) {
         // tile rows [0, R/2) are gate rows, [R/2, R) the matching up rows
-        float gv = rb[eb * R + er] + rb[(kMaxRows + eb) * R + er];
-        float uv = rb[eb * R + er + 16] + rb[(kMaxRows + eb) * R + er + 16];
-        gv = round_bf16(gv);
-        uv = round_bf16(uv);
-        if (eb < a.rows)
-          a.out[(size_t)eb * a.out_stride + tile * (R / 2) + er] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+#pragma unroll
+        for (int i = 0; i < R / 32; ++i) {
+          const int r = er + 16 * i;
+          float gv = rb[eb * R + r] + rb[(kMaxRows + eb) * R + r];
+          float uv = rb[eb * R + r + R / 2] + rb[(kMaxRows + eb) * R + r + R / 2];
+          gv = round_bf16(gv);
+          uv = round_bf16(uv);
+          if (eb < a.rows)
+            a.out[(size_t)eb * a.out_stride + tile * (R / 2) + r] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < R / 16; ++i) {
@@ -465,9 +450,7 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
           }
         }
       }
-#if !defined(DFB_TC_PROBE) && !defined(DFB_TC_PROBE2)
       if (et == 0 && it == 0) trace_max(a.trace, 6);
-#endif
     }
     if (!ok) {
       if (!*abort_flag) report_status(a.status, kStatusCopyTimeout, kKernelTcGemv, blockIdx.x, 3);
@@ -484,9 +467,9 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
       }
       if (er == 0) a.parts[blockIdx.x * kMaxRows + eb] = ArgmaxPart{best_v, best_i};
       __threadfence();
-      named_sync(1, 128);
+      named_sync(2, 128);
       if (et == 0) *last_flag = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
-      named_sync(1, 128);
+      named_sync(2, 128);
       if (*last_flag) {
         __threadfence();
         for (int b = ewarp; b < a.rows; b += 4) {
@@ -513,6 +496,7 @@ __global__ void __launch_bounds__(kTcThreads, MT == 64 ? 2 : 1) tc_gemv_kernel(c
       }
     }
     if (et == 0) trace_max(a.trace, 2);
+    }   // epilogue warps
   }
 
   // every MMA has completed (the epilogue waited for the last accumulator) or the CTA has given up

@@ -185,9 +185,10 @@ typedef struct DfbStatus {
 #define DFB_OPT_TCGEN05 18      /* batches above DFB_OPT_ROW_GEMV: which K = 1024 projections run on tcgen05.mma with
                                   TMA-fed shared-memory stages and accumulators in tensor memory instead of the
                                   mma.sync kernels; a bit mask: 1 = QKV, 2 = gate/up, 4 = LM head (default 4) */
-#define DFB_OPT_ATTN_RING 19    /* attention grids of at least this many (row, 64-position chunk) pairs run the streaming
-                                  kernel (one CTA per pair for all KV heads, K/V through a shared-memory ring fed by
-                                  bulk copies) instead of the register-resident one; 0 = never (default 48) */
+#define DFB_OPT_ATTN_RING 19    /* steps whose rows x ceil(context bound / 64) reach this value run the streaming attention
+                                  kernel (one CTA per row and 64-position chunk for all KV heads, K/V through a
+                                  shared-memory ring fed by bulk copies) instead of the register-resident one;
+                                  0 = never (default 200) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
