@@ -145,7 +145,9 @@ class StreamDecoder:
 
         # persistent per-step buffers: no allocation on the step path
         self._result = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cuda")
-        self._result_host = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32).pin_memory()
+        # explicit devices everywhere: the engine builds this object while torch's default device is "cuda"
+        # (engine/model_runner.py:68-72), where a bare torch.zeros(...).pin_memory() fails
+        self._result_host = torch.zeros(native.DFB_MAX_ROWS + 4, dtype=torch.int32, device="cpu").pin_memory()
         self._row_active = torch.ones(self._max_rows, dtype=torch.int32, device="cuda")
         self._h_ids = (C.c_int64 * self._max_rows)()
         self._h_pos = (C.c_int64 * self._max_rows)()
@@ -224,7 +226,7 @@ class StreamDecoder:
         s.block_tables = block_tables.data_ptr()
         if active_rows is not None:
             mask = row_active_mask(active_rows, rows)
-            self._row_active[:rows].copy_(torch.tensor(mask, dtype=torch.int32))
+            self._row_active[:rows].copy_(torch.tensor(mask, dtype=torch.int32, device="cpu"))
             s.row_active = self._row_active.data_ptr()
         else:
             s.row_active = None

@@ -72,8 +72,8 @@ def rope_cos_sin_table(geom: ModelGeometry) -> torch.Tensor:
     and sin in the second, built with the reference's formula
     (layers/rotary_embedding.py:27-35)."""
     d = geom.head_dim
-    inv_freq = 1.0 / (geom.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float) / d))
-    t = torch.arange(geom.max_model_len, dtype=torch.float)
+    inv_freq = 1.0 / (geom.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float, device="cpu") / d))
+    t = torch.arange(geom.max_model_len, dtype=torch.float, device="cpu")
     freqs = torch.einsum("i,j -> ij", t, inv_freq)
     return torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous()
 
@@ -126,5 +126,15 @@ def weights_from_nano_model(model, hf_config, max_model_len: int = 2048, block_s
             ln_post=layer.post_attention_layernorm.weight.data, wgu=layer.mlp.gate_up_proj.weight.data,
             wd=layer.mlp.down_proj.weight.data))
     device = qwen.embed_tokens.weight.device
-    return DecoderWeights(geom, qwen.embed_tokens.weight.data, layers, qwen.norm.weight.data,
-                          rope_cos_sin_table(geom).to(device))
+    # The model's own cos/sin cache when it has one (layers/rotary_embedding.py:27-35 builds it on whatever
+    # device the engine constructs the model on, so its last bits can differ from a table computed elsewhere):
+    # the decode kernels then rotate with exactly the values the torch path uses.
+    cos_sin = None
+    rotary = getattr(getattr(qwen.layers[0], "self_attn", None), "rotary_emb", None) if len(qwen.layers) else None
+    cache = getattr(rotary, "cos_sin_cache", None)
+    if torch.is_tensor(cache) and cache.dtype == torch.float32 and cache.numel() >= geom.max_model_len * geom.head_dim \
+            and cache.shape[-1] == geom.head_dim:
+        cos_sin = cache.reshape(-1, geom.head_dim)[: geom.max_model_len].to(device).contiguous()
+    if cos_sin is None:
+        cos_sin = rope_cos_sin_table(geom).to(device)
+    return DecoderWeights(geom, qwen.embed_tokens.weight.data, layers, qwen.norm.weight.data, cos_sin)

@@ -51,6 +51,7 @@ def model_dir(cuda_device, tmp_path_factory):
 
 
 def test_megakernel_switch_inside_the_reference_engine(model_dir):
+    R.import_reference()
     from nanovllm import SamplingParams
 
     steps = 64
