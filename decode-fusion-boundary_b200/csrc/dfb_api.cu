@@ -214,7 +214,19 @@ struct DfbHandle {
   int* host_stage = nullptr;
   int* host_tokens = nullptr;
   cudaStream_t capture_stream = nullptr;
-  std::map<int, cudaGraphExec_t> graphs;
+  // One captured step: the input staging (a kernel for device inputs, a host-to-device copy for host inputs),
+  // the kernel chain and the copy-out of tokens + status, so that a step is ONE graph launch with no
+  // stream-level gaps between its parts.  The staging kernel's arguments and the copy-out's destination follow
+  // the caller's pointers: they are patched into the instantiated graph when they change.
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    cudaGraph_t graph = nullptr;            // kept: the node handles below belong to it
+    cudaGraphNode_t stage_node = nullptr;   // stage_inputs_kernel (device-input steps)
+    cudaGraphNode_t out_node = nullptr;     // device-to-device copy of tokens + status (device-input steps with out_tokens)
+    StageArgs stage_args = {};
+    void* out_ptr = nullptr;
+  };
+  std::map<long long, StepGraph> graphs;
   int64_t steps = 0;
   int kernels_per_step = 0;
   int last_status[4] = {0, 0, 0, 0};  // last non-zero status word seen by a host-buffer step
@@ -731,29 +743,94 @@ int enqueue_persistent(DfbHandle* h, int rows, cudaStream_t stream, float* logit
   return L.err;
 }
 
-int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, cudaStream_t stream, float* logits_out) {
+// What surrounds the kernel chain of one step.
+struct StepIo {
+  const StageArgs* stage = nullptr;   // device inputs: arguments of stage_inputs_kernel
+  bool host = false;                  // host inputs: h->host_stage -> h->stage before, h->tokens -> h->host_tokens after
+  int* out_tokens = nullptr;          // device inputs: optional copy of tokens + status
+};
+
+int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream,
+                       float* logits_out) {
+  if (io.host) {
+    DFB_CUDA(cudaMemcpyAsync(h->stage, h->host_stage, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
+  } else if (io.stage) {
+    stage_inputs_kernel<<<1, 128, 0, stream>>>(*io.stage);
+    DFB_CUDA(cudaGetLastError());
+  }
+  int rc = h->step_mode == 1 ? enqueue_persistent(h, rows, stream, logits_out)
+                             : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
+  if (rc) return rc;
+  if (io.host) {
+    DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
+  } else if (io.out_tokens) {
+    DFB_CUDA(cudaMemcpyAsync(io.out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
+  }
+  return 0;
+}
+
+int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream, float* logits_out) {
   const bool persistent = h->step_mode == 1;
-  if (!h->use_graph || logits_out)
-    return persistent ? enqueue_persistent(h, rows, stream, logits_out)
-                      : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
-  // one graph per (rows, split bucket, filled block-table columns)
-  const int key = persistent ? (1 << 24) + rows : ((bt_cols * 16 + rows) * 1024 + nsplit) * 2 + (h->use_pdl ? 1 : 0);
+  if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
+  // one graph per (rows, split bucket, filled block-table columns, kind of inputs / outputs)
+  const int io_kind = io.host ? 3 : (io.out_tokens ? 2 : 1);
+  const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 1024 + nsplit) * 2 +
+                         (h->use_pdl ? 1 : 0)) * 4 + io_kind;
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
     cudaGraph_t graph = nullptr;
     DFB_CUDA(cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal));
-    int rc = persistent ? enqueue_persistent(h, rows, h->capture_stream, nullptr)
-                        : enqueue_step(h, rows, nsplit, bt_cols, h->capture_stream, nullptr);
+    int rc = enqueue_whole_step(h, rows, nsplit, bt_cols, io, h->capture_stream, nullptr);
     cudaError_t e = cudaStreamEndCapture(h->capture_stream, &graph);
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) return (int)e;
-    cudaGraphExec_t exec = nullptr;
-    e = cudaGraphInstantiate(&exec, graph, 0);
-    cudaGraphDestroy(graph);
-    if (e != cudaSuccess) return (int)e;
-    it = h->graphs.emplace(key, exec).first;
+    DfbHandle::StepGraph g;
+    if (!io.host) {
+      // find the two nodes whose parameters follow the caller's pointers
+      size_t n = 0;
+      e = cudaGraphGetNodes(graph, nullptr, &n);
+      std::vector<cudaGraphNode_t> nodes(n);
+      if (e == cudaSuccess && n) e = cudaGraphGetNodes(graph, nodes.data(), &n);
+      for (size_t i = 0; e == cudaSuccess && i < n; ++i) {
+        cudaGraphNodeType type;
+        e = cudaGraphNodeGetType(nodes[i], &type);
+        if (e != cudaSuccess) break;
+        if (type == cudaGraphNodeTypeKernel && !g.stage_node) {
+          cudaKernelNodeParams kp = {};
+          e = cudaGraphKernelNodeGetParams(nodes[i], &kp);
+          if (e == cudaSuccess && kp.func == (void*)stage_inputs_kernel) g.stage_node = nodes[i];
+        } else if (type == cudaGraphNodeTypeMemcpy && io.out_tokens) {
+          g.out_node = nodes[i];
+        }
+      }
+      if (e == cudaSuccess && (!g.stage_node || (io.out_tokens && !g.out_node))) e = cudaErrorInvalidValue;
+      if (e != cudaSuccess) { cudaGraphDestroy(graph); return (int)e; }
+      g.stage_args = *io.stage;
+      g.out_ptr = io.out_tokens;
+    }
+    e = cudaGraphInstantiate(&g.exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); return (int)e; }
+    g.graph = graph;
+    it = h->graphs.emplace(key, g).first;
   }
-  DFB_CUDA(cudaGraphLaunch(it->second, stream));
+  DfbHandle::StepGraph& g = it->second;
+  if (!io.host) {
+    if (memcmp(&g.stage_args, io.stage, sizeof(StageArgs)) != 0) {
+      StageArgs args = *io.stage;
+      void* params[1] = {&args};
+      cudaKernelNodeParams kp = {};
+      kp.func = (void*)stage_inputs_kernel;
+      kp.gridDim = dim3(1); kp.blockDim = dim3(128); kp.sharedMemBytes = 0; kp.kernelParams = params; kp.extra = nullptr;
+      DFB_CUDA(cudaGraphExecKernelNodeSetParams(g.exec, g.stage_node, &kp));
+      g.stage_args = args;
+    }
+    if (io.out_tokens && g.out_ptr != io.out_tokens) {
+      DFB_CUDA(cudaGraphExecMemcpyNodeSetParams1D(g.exec, g.out_node, io.out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4),
+                                                  cudaMemcpyDeviceToDevice));
+      g.out_ptr = io.out_tokens;
+    }
+  }
+  DFB_CUDA(cudaGraphLaunch(g.exec, stream));
   return 0;
 }
 
@@ -864,7 +941,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
 
 void dfb_destroy(DfbHandle* h) {
   if (!h) return;
-  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
   if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   for (int r = 0; r < kMaxRanks; ++r) {
     if (h->loopback[r]) cudaFree(h->loopback[r]);
@@ -884,7 +961,7 @@ int dfb_set_tensor_parallel(DfbHandle* h, const DfbTensorParallel* tp) {
     return DFB_E_BAD_ARG;
   if (h->step_mode != 0 || h->steps != 0) return DFB_E_BAD_ARG;  // before the first step, kernel chain only
   h->tp = *tp;
-  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
   h->graphs.clear();
   return 0;
 }
@@ -919,7 +996,7 @@ int dfb_tp_open_peers(DfbHandle* h, const void* handles) {
     h->windows[r] = (unsigned char*)mapped;
   }
   h->direct = true;
-  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
   h->graphs.clear();
   return 0;
 }
@@ -937,7 +1014,7 @@ int dfb_tp_open_loopback(DfbHandle* h) {
     h->windows[r] = h->loopback[r];
   }
   h->direct = true;
-  for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
   h->graphs.clear();
   return 0;
 }
@@ -946,7 +1023,7 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
   if (!h) return DFB_E_BAD_ARG;
   // every option below may change which kernels a captured step holds
   auto drop_graphs = [&]() {
-    for (auto& kv : h->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
     h->graphs.clear();
   };
   switch (option) {
@@ -1041,8 +1118,6 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
   a.embed_rows = h->embed_rows(); a.status = h->status;
   a.ids_out = h->st_ids(); a.positions_out = h->st_pos(); a.bt_out = h->st_bt();
   a.row_active_out = h->st_active();
-  stage_inputs_kernel<<<1, 128, 0, stream>>>(a);
-  DFB_CUDA(cudaGetLastError());
   // The attention grid is sized from the caller's bound; a bound that does not cover the filled
   // block-table columns would only be caught on the device (status 6), so never go below one column.
   int bound = s->block_table_cols * h->m.block_size;
@@ -1051,10 +1126,11 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
     const int lowest = (s->block_table_cols - 1) * h->m.block_size + 1;   // the last column holds at least one token
     if (bound < lowest) bound = lowest;
   }
-  int rc = run_step(h, s->rows, split_bucket(h, bound, s->rows), s->block_table_cols, stream, s->out_logits);
+  StepIo io;
+  io.stage = &a;
+  io.out_tokens = s->out_tokens;
+  int rc = run_step(h, s->rows, split_bucket(h, bound, s->rows), s->block_table_cols, io, stream, s->out_logits);
   if (rc) return rc;
-  if (s->out_tokens)
-    DFB_CUDA(cudaMemcpyAsync(s->out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
   ++h->steps;
   return 0;
 }
@@ -1079,10 +1155,10 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
     if (positions[r] + 1 > max_ctx) max_ctx = (int)positions[r] + 1;
     for (int c = 0; c < cols; ++c) hs[24 + r * h->max_pages + c] = block_tables[r * cols + c];
   }
-  DFB_CUDA(cudaMemcpyAsync(h->stage, hs, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
-  int rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, stream, nullptr);
+  StepIo io;
+  io.host = true;      // the two copies between the pinned staging buffers and the device are part of the step's graph
+  int rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, io, stream, nullptr);
   if (rc) return rc;
-  DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   DFB_CUDA(cudaStreamSynchronize(stream));
   for (int r = 0; r < rows; ++r) out_tokens[r] = h->host_tokens[r];
   ++h->steps;
