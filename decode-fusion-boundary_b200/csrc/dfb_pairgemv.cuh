@@ -14,8 +14,14 @@
 //     reads 16 bytes of rows g and g+8 per 32-column block (A fragments of two
 //     MMAs, conflict-free thanks to the padding) and the matching 16 bytes of
 //     x[batch g] (B fragments) from a bf16 copy of x in shared memory;
-//   * the residual add + RMSNorm is done by the whole CTA, 4 elements per
-//     thread and batch row, all loads in flight together;
+//   * the residual add + RMSNorm is done ONE WARP PER BATCH ROW: the rows of h
+//     and of the residual arrive by bulk copies (TMA), a lane owns four 16-byte
+//     pieces of its row, the sum of squares needs one butterfly and no
+//     cross-warp step, every lane computes one root, and the normalised row is
+//     written in place; the eight rows proceed in parallel without a barrier
+//     between them (with every thread handling all rows, the cross-warp
+//     reduction and eight roots per thread made this prologue the longest part
+//     of the kernel after its dependency);
 //   * cross-warp reduction in shared memory, one thread per output for the
 //     epilogue (store / SwiGLU / logits + greedy argmax).
 #pragma once
@@ -30,7 +36,8 @@ struct PairSmem {
   static constexpr int kRowStride = 2 * kK + 64;       // bytes
   static constexpr int kStageBytes = 16 * kRowStride;  // 33,792
   static constexpr int kXBytes = kMaxRows * kRowStride; // bf16 copy of x, same padding
-  static constexpr int bytes(int stages) { return stages * kStageBytes + kXBytes + 8 * stages + 16; }
+  static constexpr int kResBytes = kMaxRows * 2 * kK;   // residual rows as fetched by the bulk copies
+  static constexpr int bytes(int stages) { return stages * kStageBytes + kXBytes + kResBytes + 8 * (stages + 1) + 16; }
 };
 
 template <int PSTAGES, int MODE>
@@ -44,7 +51,9 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   unsigned char* stage_base = dyn_smem;
   unsigned char* xsb = dyn_smem + PSTAGES * SM::kStageBytes;                 // [8][kRowStride] bf16 x
-  uint64_t* full = reinterpret_cast<uint64_t*>(xsb + SM::kXBytes);
+  unsigned char* rstage = xsb + SM::kXBytes;                                 // [8][2 K] residual rows
+  uint64_t* full = reinterpret_cast<uint64_t*>(rstage + SM::kResBytes);
+  uint64_t* x_in = full + PSTAGES;
   __shared__ float red[2][kWarps][128];
   __shared__ float ssq[kWarps][kMaxRows];
   __shared__ ArgmaxPart wpart[4][kMaxRows];
@@ -74,7 +83,10 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
     if (lane == 0) {
 #pragma unroll
       for (int s = 0; s < PSTAGES; ++s) mbar_init(&full[s], 1);
+      mbar_init(x_in, 1);
       fence_mbar_init();
+      // the activation rows' byte count is posted here, long before any of their copies can complete
+      if (kNorm && a.ids == nullptr && a.res_in != nullptr && a.tp_mode != 2) mbar_expect_tx(x_in, (uint32_t)(a.rows * 4 * K));
     }
     __syncwarp();
 #pragma unroll
@@ -85,6 +97,9 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   }
   uint2 nwv = make_uint2(0, 0);
   if (kNorm) nwv = *reinterpret_cast<const uint2*>(a.norm_w + 4 * tid);
+  uint4 nw4[4];   // row-per-warp prologue: the norm weights of this lane's four 16-byte pieces
+#pragma unroll
+  for (int c = 0; c < 4; ++c) nw4[c] = kNorm ? ldg_stream(a.norm_w + 8 * (32 * c + lane)) : make_uint4(0, 0, 0, 0);
   if (warp == 1) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
   __syncthreads();  // the barriers are initialised before anyone polls them
 
@@ -92,7 +107,61 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   if (threadIdx.x == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
 
   // ---- x (bf16) into shared memory, with the fused residual add + RMSNorm ----
-  if (kNorm) {
+  const bool bulk_x = kNorm && a.ids == nullptr && a.res_in != nullptr && a.tp_mode != 2;
+  if (kNorm && bulk_x) {
+    // warp b owns batch row b; lane l owns the 16-byte pieces l, l + 32, l + 64, l + 96 of the row
+    if (tid < 16) {                       // sixteen threads issue one row copy each
+      const int b = tid & 7;
+      if (b < a.rows) {
+        if (tid < 8) bulk_g2s(xsb + b * SM::kRowStride, a.x + (size_t)b * K, 2 * K, x_in);
+        else bulk_g2s(rstage + b * 2 * K, a.res_in + (size_t)b * K, 2 * K, x_in);
+      }
+    }
+    if (!__syncthreads_and(mbar_wait_bounded(x_in, 0) ? 1 : 0))
+      report_status(a.status, kStatusCopyTimeout, kKernelGemv, blockIdx.x, -1);
+    if (a.late_trigger) pdl_launch_dependents();
+    const int b = warp;
+    unsigned char* xrow = xsb + b * SM::kRowStride;
+    if (b < a.rows) {
+      float x[4][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(xrow + 16 * (32 * c + lane));
+        const uint4 rv = *reinterpret_cast<const uint4*>(rstage + b * 2 * K + 16 * (32 * c + lane));
+        float hf[8], rf[8];
+        unpack8(hv, hf);
+        unpack8(rv, rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { x[c][e] = hf[e] + rf[e]; ss = fmaf(x[c][e], x[c][e], ss); }
+      }
+      if (a.res_out && blockIdx.x == 0) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack_bf16(x[c][0], x[c][1]); o.y = pack_bf16(x[c][2], x[c][3]);
+          o.z = pack_bf16(x[c][4], x[c][5]); o.w = pack_bf16(x[c][6], x[c][7]);
+          *reinterpret_cast<uint4*>(a.res_out + (size_t)b * K + 8 * (32 * c + lane)) = o;
+        }
+      }
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      const float rstd = 1.0f / sqrtf(ss / (float)K + a.eps);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float wf[8], y[8];
+        unpack8(nw4[c], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = round_bf16(x[c][e] * rstd) * wf[e];
+        uint4 o;
+        o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
+        *reinterpret_cast<uint4*>(xrow + 16 * (32 * c + lane)) = o;    // in place: this lane read exactly these bytes
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(xrow + 16 * (32 * c + lane)) = make_uint4(0, 0, 0, 0);
+    }
+  } else if (kNorm) {
     float x[kMaxRows][4];
     uint2 hv[kMaxRows], rv[kMaxRows];
 #pragma unroll
