@@ -193,7 +193,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_in + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
-  __shared__ __align__(16) float ssq[kTcProWarps][kMaxRows];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = a.n_tiles, stride = gridDim.x;
@@ -290,9 +289,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
     }
     __syncwarp();
   } else {
-    // ---------------- prologue: 256 threads; epilogue: the first 128 of them ----------------
+    // ---------------- prologue: 8 warps, one per batch row; epilogue: the first four of them ----------------
     const int pt = tid - 32 * kTcFirstPro, pwarp = warp - kTcFirstPro;
-    const uint2 nw = *reinterpret_cast<const uint2*>(a.norm_w + 4 * pt);
+    uint4 nw4[4];   // the norm weights of this lane's four 16-byte pieces (pieces lane, lane + 32, + 64, + 96 of a row)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) nw4[c] = ldg_stream(a.norm_w + 8 * (32 * c + lane));
     // The rows of h and of the residual come in by bulk copies (TMA): ordinary loads issued here would
     // queue in the load/store unit behind the loads of the successor kernel that was let in early.
     const bool bulk_x = a.ids == nullptr && a.res_in != nullptr;
@@ -309,82 +310,69 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
       }
     }
 
-    // x = h (+ residual), bf16 residual out, RMSNorm, bf16 y in the swizzled layout of the B operand:
-    // this thread owns columns [4 pt, 4 pt + 4) = half of one 16-byte chunk of every batch row
+    // x = h (+ residual), bf16 residual out, RMSNorm, bf16 y in the swizzled layout of the B operand.
+    // Warp b owns batch row b: a lane holds four 16-byte pieces of the row, the sum of squares needs one
+    // butterfly and no cross-warp step, every lane computes one root; the eight rows proceed in parallel.
     {
-      const int k0 = 4 * pt, half = k0 >> 9, kk = k0 & 511, kb = kk >> 6, c = (kk & 63) >> 3, sub = (k0 >> 2) & 1;
-      uint2 hv[kMaxRows], rv[kMaxRows];
+      const int b = pwarp;
+      uint4 hv[4], rv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) { hv[c] = make_uint4(0, 0, 0, 0); rv[c] = make_uint4(0, 0, 0, 0); }
       if (bulk_x) {
         if (!named_sync_and(1, kTcProThreads, tc_wait(x_in, 0, abort_flag))) {
           if (pt == 0 && !*abort_flag) report_status(a.status, kStatusCopyTimeout, kKernelTcGemv, blockIdx.x, 4);
           *abort_flag = 1;
         }
+        if (b < a.rows) {
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) {
-          hv[b] = make_uint2(0, 0);
-          rv[b] = make_uint2(0, 0);
-          if (b < a.rows) {
-            hv[b] = *reinterpret_cast<const uint2*>(xs + b * 2 * kTcK + 8 * pt);
-            rv[b] = *reinterpret_cast<const uint2*>(rstage + b * 2 * kTcK + 8 * pt);
+          for (int c = 0; c < 4; ++c) {
+            hv[c] = *reinterpret_cast<const uint4*>(xs + b * 2 * kTcK + 16 * (32 * c + lane));
+            rv[c] = *reinterpret_cast<const uint4*>(rstage + b * 2 * kTcK + 16 * (32 * c + lane));
           }
         }
-      } else {
+      } else if (b < a.rows) {
+        const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[b], a.embed_rows, a.status, b) : (size_t)b;
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) {
-          hv[b] = make_uint2(0, 0);
-          rv[b] = make_uint2(0, 0);
-          if (b < a.rows) {
-            const size_t xrow = a.ids ? (size_t)clamp_token(a.ids[b], a.embed_rows, a.status, b) : (size_t)b;
-            hv[b] = __ldcg(reinterpret_cast<const uint2*>(a.x + xrow * kTcK + k0));
-            if (a.res_in) rv[b] = __ldcg(reinterpret_cast<const uint2*>(a.res_in + (size_t)b * kTcK + k0));
-          }
+        for (int c = 0; c < 4; ++c) {
+          hv[c] = ldg_cg(a.x + xrow * kTcK + 8 * (32 * c + lane));
+          if (a.res_in) rv[c] = ldg_cg(a.res_in + (size_t)b * kTcK + 8 * (32 * c + lane));
         }
       }
       if (a.late_trigger) pdl_launch_dependents();   // the successor's prefetch traffic starts after x is here
-      // All eight rows advance in lockstep through every dependent step (sums, butterflies, roots), so the
-      // latency of a step is paid once, not once per row.
-      float x[kMaxRows][4], ss[kMaxRows];
+      named_sync(1, kTcProThreads);    // every row has been read before any y is written over the staging bytes
+      float x[4][8];
+      float ss = 0.f;
 #pragma unroll
-      for (int b = 0; b < kMaxRows; ++b) {
-        x[b][0] = bf_lo(hv[b].x) + bf_lo(rv[b].x); x[b][1] = bf_hi(hv[b].x) + bf_hi(rv[b].x);
-        x[b][2] = bf_lo(hv[b].y) + bf_lo(rv[b].y); x[b][3] = bf_hi(hv[b].y) + bf_hi(rv[b].y);
-        ss[b] = (x[b][0] * x[b][0] + x[b][1] * x[b][1]) + (x[b][2] * x[b][2] + x[b][3] * x[b][3]);
+      for (int c = 0; c < 4; ++c) {
+        float hf[8], rf[8];
+        unpack8(hv[c], hf);
+        unpack8(rv[c], rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { x[c][e] = hf[e] + rf[e]; ss = fmaf(x[c][e], x[c][e], ss); }
+      }
+      if (a.res_out && blockIdx.x == 0 && b < a.rows) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack_bf16(x[c][0], x[c][1]); o.y = pack_bf16(x[c][2], x[c][3]);
+          o.z = pack_bf16(x[c][4], x[c][5]); o.w = pack_bf16(x[c][6], x[c][7]);
+          *reinterpret_cast<uint4*>(a.res_out + (size_t)b * kTcK + 8 * (32 * c + lane)) = o;
+        }
       }
 #pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) {
-        float other[kMaxRows];
+      for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      const float rstd = 1.0f / sqrtf(ss / (float)kTcK + a.eps);
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) other[b] = __shfl_xor_sync(0xffffffffu, ss[b], m);
+      for (int c = 0; c < 4; ++c) {
+        float wf[8], y[8];
+        unpack8(nw4[c], wf);
 #pragma unroll
-        for (int b = 0; b < kMaxRows; ++b) ss[b] += other[b];
-      }
-      if (lane == 0) {
-        *reinterpret_cast<float4*>(&ssq[pwarp][0]) = make_float4(ss[0], ss[1], ss[2], ss[3]);
-        *reinterpret_cast<float4*>(&ssq[pwarp][4]) = make_float4(ss[4], ss[5], ss[6], ss[7]);
-      }
-      if (a.res_out && blockIdx.x == 0) {
-#pragma unroll
-        for (int b = 0; b < kMaxRows; ++b)
-          if (b < a.rows)
-            *reinterpret_cast<uint2*>(a.res_out + (size_t)b * kTcK + k0) =
-                make_uint2(pack_bf16(x[b][0], x[b][1]), pack_bf16(x[b][2], x[b][3]));
-      }
-      named_sync(1, kTcProThreads);    // also: every thread has read its pieces of xs before anyone overwrites them
-      const float w0 = bf_lo(nw.x), w1 = bf_hi(nw.x), w2 = bf_lo(nw.y), w3 = bf_hi(nw.y);
-      float rstd[kMaxRows];
-#pragma unroll
-      for (int b = 0; b < kMaxRows; ++b) {
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < kTcProWarps; ++w) tot += ssq[w][b];
-        rstd[b] = 1.0f / sqrtf(tot / (float)kTcK + a.eps);
-      }
-#pragma unroll
-      for (int b = 0; b < kMaxRows; ++b) {   // rows beyond the batch are zero
-        const uint2 o = make_uint2(pack_bf16(round_bf16(x[b][0] * rstd[b]) * w0, round_bf16(x[b][1] * rstd[b]) * w1),
-                                   pack_bf16(round_bf16(x[b][2] * rstd[b]) * w2, round_bf16(x[b][3] * rstd[b]) * w3));
-        const int n = b + 8 * half;
-        *reinterpret_cast<uint2*>(xs + kb * 2048 + n * 128 + ((c ^ (n & 7)) << 4) + 8 * sub) = o;
+        for (int e = 0; e < 8; ++e) y[e] = round_bf16(x[c][e] * rstd) * wf[e];   // rows beyond the batch are zero
+        uint4 o;
+        o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
+        // piece q of the row -> half of K, k-block, 16-byte chunk inside the 128-byte swizzle atom
+        const int q = 32 * c + lane, half = q >> 6, kb = (q & 63) >> 3, cc = q & 7, n = b + 8 * half;
+        *reinterpret_cast<uint4*>(xs + kb * 2048 + n * 128 + ((cc ^ (n & 7)) << 4)) = o;
       }
     }
     fence_async_smem();      // the MMAs read shared memory through the async proxy
