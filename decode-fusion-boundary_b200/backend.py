@@ -193,10 +193,17 @@ class MegakernelBackend:
             debug_bounds=bool(_get_attr(self.config, "megakernel_debug_bounds", False)),
             tensor_parallel=group,
         )
+        seed = _get_attr(self.config, "megakernel_seed", None)
+        if seed is not None:
+            self.decoder.set_seed(int(seed))
 
-    def decode_batch(self, input_ids, positions, block_tables) -> list[int]:
-        """Decode one token for each scheduler-selected sequence."""
+    def decode_batch(self, input_ids, positions, block_tables, temperatures=None) -> list[int]:
+        """Decode one token for each scheduler-selected sequence.  ``temperatures``
+        (not passed by the stock ``ModelRunner.run``): the float32 CUDA tensor of
+        ``ModelRunner.prepare_sample``; rows above 1e-10 are sampled."""
         self._ensure_decoder()
+        if temperatures is not None:
+            return self.decoder.decode_rows(input_ids, positions, block_tables, temperatures=temperatures)
         return self.decoder.decode_rows(input_ids, positions, block_tables)
 
     def decode(self, seq, block_table) -> list[int]:
@@ -204,4 +211,11 @@ class MegakernelBackend:
         new K/V goes into the scheduler-owned paged cache; earlier positions are
         read from that same cache (no prompt replay, no private cache)."""
         self._ensure_decoder()
+        temperature = 0.0
+        if _get_attr(self.config, "megakernel_sampling", False):
+            # admitted by the opt-in of ``taskgraph_compatibility``; a greedy row stays on the plain argmax
+            temperature = float(getattr(seq, "temperature", 0.0) or 0.0)
+        if temperature > 1e-10:
+            return [int(self.decoder.step(seq.last_token, position=decode_position(len(seq)),
+                                          block_table=block_table, temperature=temperature))]
         return [int(self.decoder.step(seq.last_token, position=decode_position(len(seq)), block_table=block_table))]

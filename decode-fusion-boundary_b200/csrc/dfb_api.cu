@@ -213,6 +213,9 @@ struct DfbHandle {
   // pinned host staging
   int* host_stage = nullptr;
   int* host_tokens = nullptr;
+  unsigned long long sample_seed = 0;   // dfb_set_seed
+  unsigned int* sample_ctr = nullptr;   // device: sampled LM-head launches so far (position in the noise stream)
+  const float* lm_temps = nullptr;      // temperatures the LM head being enqueued samples with (null = greedy)
   cudaStream_t capture_stream = nullptr;
   // One captured step: the input staging (a kernel for device inputs, a host-to-device copy for host inputs),
   // the kernel chain and the copy-out of tokens + status, so that a step is ONE graph launch with no
@@ -251,7 +254,8 @@ struct DfbHandle {
   int* st_pos() const { return stage + 8; }
   int* st_active() const { return stage + 16; }
   int* st_bt() const { return stage + 24; }
-  int stage_ints() const { return 24 + 8 * max_pages; }
+  float* st_temps() const { return reinterpret_cast<float*>(stage + 24 + 8 * max_pages); }   // [8] sampling temperatures
+  int stage_ints() const { return 32 + 8 * max_pages; }
 };
 
 namespace {
@@ -516,6 +520,8 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
   a.parts = h->parts; a.ticket = h->tickets + kMaxRows * m.kv_heads; a.tokens = h->tokens;
   a.tokens_out = h->sharded() ? nullptr : tokens_out;
   a.best_out = h->sharded() ? h->best_local : nullptr;
+  a.temps = h->lm_temps; a.sample_ctr = h->sample_ctr; a.sample_seed = h->sample_seed;
+  a.sample_idx_offset = h->sharded() ? h->tp.vocab_offset : 0;
   if (rows <= L.opt->row_max_rows && m.vocab % 16 == 0) {
     a.n_tiles = m.vocab / 16;
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 3 * h->sm_count;
@@ -748,6 +754,7 @@ struct StepIo {
   const StageArgs* stage = nullptr;   // device inputs: arguments of stage_inputs_kernel
   bool host = false;                  // host inputs: h->host_stage -> h->stage before, h->tokens -> h->host_tokens after
   int* out_tokens = nullptr;          // device inputs: optional copy of tokens + status
+  bool sampling = false;              // the staged temperatures are live: the LM head samples rows with T > 1e-10
 };
 
 int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream,
@@ -758,8 +765,11 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
     stage_inputs_kernel<<<1, 128, 0, stream>>>(*io.stage);
     DFB_CUDA(cudaGetLastError());
   }
+  if (io.sampling && h->step_mode == 1) return DFB_E_BAD_ARG;   // the persistent kernel's LM head is greedy only
+  h->lm_temps = io.sampling ? h->st_temps() : nullptr;
   int rc = h->step_mode == 1 ? enqueue_persistent(h, rows, stream, logits_out)
                              : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
+  h->lm_temps = nullptr;
   if (rc) return rc;
   if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
@@ -773,9 +783,9 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
   const bool persistent = h->step_mode == 1;
   if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
   // one graph per (rows, split bucket, filled block-table columns, kind of inputs / outputs)
-  const int io_kind = io.host ? 3 : (io.out_tokens ? 2 : 1);
+  const int io_kind = (io.host ? 3 : (io.out_tokens ? 2 : 1)) + (io.sampling ? 4 : 0);
   const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 1024 + nsplit) * 2 +
-                         (h->use_pdl ? 1 : 0)) * 4 + io_kind;
+                         (h->use_pdl ? 1 : 0)) * 8 + io_kind;
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
     cudaGraph_t graph = nullptr;
@@ -908,6 +918,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_tok = carve(sizeof(int) * (kMaxRows + 4));  // tokens[8] | status[4], contiguous
   const size_t o_best = carve(sizeof(ArgmaxPart) * kMaxRows * 9);  // this rank's winners | all ranks' (up to 8)
   const size_t o_tpstep = carve(sizeof(unsigned) * 4);
+  const size_t o_sctr = carve(sizeof(unsigned) * 4);
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
@@ -935,6 +946,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   h->tokens = (int*)(s + o_tok); h->status = h->tokens + kMaxRows;
   h->best_local = (ArgmaxPart*)(s + o_best); h->best_all = h->best_local + kMaxRows;
   h->tp_step = (unsigned int*)(s + o_tpstep);
+  h->sample_ctr = (unsigned int*)(s + o_sctr);
   *out = h;
   return 0;
 }
@@ -1104,6 +1116,16 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
   return 0;
 }
 
+int dfb_set_seed(DfbHandle* h, uint64_t seed) {
+  if (!h) return DFB_E_BAD_ARG;
+  // the seed is a kernel argument of every captured LM head; the noise stream restarts at step 0
+  for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
+  h->graphs.clear();
+  h->sample_seed = seed;
+  DFB_CUDA(cudaMemset(h->sample_ctr, 0, sizeof(unsigned)));
+  return 0;
+}
+
 int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
   if (!h || !s) return DFB_E_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -1118,6 +1140,7 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
   a.embed_rows = h->embed_rows(); a.status = h->status;
   a.ids_out = h->st_ids(); a.positions_out = h->st_pos(); a.bt_out = h->st_bt();
   a.row_active_out = h->st_active();
+  a.temps = s->temperatures; a.temps_out = h->st_temps();
   // The attention grid is sized from the caller's bound; a bound that does not cover the filled
   // block-table columns would only be caught on the device (status 6), so never go below one column.
   int bound = s->block_table_cols * h->m.block_size;
@@ -1129,6 +1152,8 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
   StepIo io;
   io.stage = &a;
   io.out_tokens = s->out_tokens;
+  io.sampling = s->temperatures != nullptr;
+  if (io.sampling && s->out_logits && h->step_mode == 1) return DFB_E_BAD_ARG;
   int rc = run_step(h, s->rows, split_bucket(h, bound, s->rows), s->block_table_cols, io, stream, s->out_logits);
   if (rc) return rc;
   ++h->steps;
@@ -1138,6 +1163,13 @@ int dfb_decode_step(DfbHandle* h, const DfbStepDesc* s, dfb_stream_t stream_) {
 int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
                          const int32_t* block_tables, int32_t cols, const int32_t* row_active, int32_t* out_tokens,
                          dfb_stream_t stream_) {
+  return dfb_decode_step_host_sampled(h, rows, input_ids, positions, block_tables, cols, row_active, nullptr,
+                                      out_tokens, stream_);
+}
+
+int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
+                                 const int32_t* block_tables, int32_t cols, const int32_t* row_active,
+                                 const float* temperatures, int32_t* out_tokens, dfb_stream_t stream_) {
   if (!h || !input_ids || !positions || !block_tables || !out_tokens) return DFB_E_BAD_ARG;
   if (rows < 1 || rows > kMaxRows || cols < 1) return DFB_E_BAD_ARG;
   if (cols > h->max_pages) return DFB_E_TOO_LARGE;
@@ -1154,8 +1186,13 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
     hs[16 + r] = row_active ? row_active[r] : 1;
     if (positions[r] + 1 > max_ctx) max_ctx = (int)positions[r] + 1;
     for (int c = 0; c < cols; ++c) hs[24 + r * h->max_pages + c] = block_tables[r * cols + c];
+    if (temperatures) {
+      if (!(temperatures[r] >= 0.f)) return DFB_E_BAD_ARG;   // negative or NaN (sampling_params.py:14-15)
+      memcpy(&hs[24 + 8 * h->max_pages + r], &temperatures[r], sizeof(float));
+    }
   }
   StepIo io;
+  io.sampling = temperatures != nullptr;
   io.host = true;      // the two copies between the pinned staging buffers and the device are part of the step's graph
   int rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, io, stream, nullptr);
   if (rc) return rc;
@@ -1244,10 +1281,18 @@ int dfb_launch_rmsnorm_gateup_swiglu(const void* hh, const void* residual, void*
 
 int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,
                              float* out_logits, int32_t rows, dfb_stream_t stream) {
+  return dfb_launch_lmhead_sample(h, hidden_in, residual, nullptr, out_tokens, out_logits, rows, stream);
+}
+
+int dfb_launch_lmhead_sample(DfbHandle* h, const void* hidden_in, const void* residual, const float* temperatures,
+                             int32_t* out_tokens, float* out_logits, int32_t rows, dfb_stream_t stream) {
   if (!h || !hidden_in || !residual || rows < 1 || rows > kMaxRows) return DFB_E_BAD_ARG;
   Launcher L{(cudaStream_t)stream, false};
   L.opt = &h->opt;
-  return launch_lmhead(L, h, (const bf16*)hidden_in, (const bf16*)residual, rows, out_tokens, out_logits);
+  h->lm_temps = temperatures;
+  const int rc = launch_lmhead(L, h, (const bf16*)hidden_in, (const bf16*)residual, rows, out_tokens, out_logits);
+  h->lm_temps = nullptr;
+  return rc;
 }
 
 // ---- LM head + argmax without any allocation -----------------------------------

@@ -83,6 +83,12 @@ struct GemvArgs {
   unsigned long long ahead_bytes;  // multiple of 16; 0 = none
   int ahead_late;                // 1: issue the request after this kernel's own work, 0: before its dependency wait
   int embed_rows;                // rows of the embedding table behind `ids` (ids are clamped into it)
+  // sampling (argmax mode): rows with temps[r] > 1e-10 pick argmax(logit / T + Gumbel noise), i.e. a draw from
+  // softmax(logits / T); the others stay greedy
+  const float* temps;            // [rows] device, or null = every row greedy
+  unsigned int* sample_ctr;      // device counter of sampled LM-head launches: the noise stream's step index
+  unsigned long long sample_seed;
+  int sample_idx_offset;         // first vocabulary row of this rank's shard (noise is a function of the global index)
 };
 
 // ---------------------------------------------------------------------------
@@ -108,6 +114,51 @@ __device__ __forceinline__ uint4 ldg_cg(const void* p) {
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+// ---------------------------------------------------------------------------
+// Sampling fused after the LM head (layers/sampler.py:7-16 of the reference:
+// argmax(softmax(logits / T) / E) with E ~ Exp(1), clamped at 1e-10).  Since the
+// softmax's normalisation is one positive factor per row, the same draw is
+// argmax(logit / T - log E): no softmax pass, no second look at the logits.
+// E comes from a counter-based generator, a function of (seed, step, row, global
+// vocabulary index) only, so that every CTA, every kernel variant and every
+// tensor-parallel rank sees the same noise: the splitmix64 finaliser over
+// seed + counter * 0x9E3779B97F4A7C15, its top 23 bits as a uniform in (0, 1).
+// ---------------------------------------------------------------------------
+struct SampleRow {
+  float temp;       // <= 1e-10: greedy
+  unsigned step;
+};
+// The per-row state lives in shared memory and the key function is not inlined, so that the greedy path of
+// the LM-head kernels keeps its registers: a step that samples nothing pays one uniform branch per logit.
+__device__ __forceinline__ void sample_rows_load(const GemvArgs& a, SampleRow* rows_smem, int tid) {
+  if (a.temps && tid < kMaxRows) {
+    SampleRow s{0.f, 0u};
+    if (tid < a.rows) {
+      s.temp = a.temps[tid];
+      if (s.temp > 1e-10f) s.step = *(volatile unsigned int*)a.sample_ctr;
+    }
+    rows_smem[tid] = s;
+  }
+}
+__device__ __noinline__ float sample_key(unsigned long long seed, int idx_offset, const SampleRow* rows_smem, int row,
+                                         int idx, float logit) {
+  const SampleRow s = rows_smem[row];
+  if (!(s.temp > 1e-10f)) return logit;
+  const unsigned long long ctr =
+      ((unsigned long long)(s.step * 8u + (unsigned)row) << 32) | (unsigned)(idx + idx_offset);
+  unsigned long long z = seed + ctr * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  const float u = ((float)(unsigned)(z >> 41) + 0.5f) * 1.1920928955078125e-07f;   // 2^-23: u in (0, 1)
+  const float e = fmaxf(-logf(u), 1e-10f);
+  return __fdiv_rn(logit, s.temp) - logf(e);
+}
+// called by the one thread that publishes the step's tokens
+__device__ __forceinline__ void sample_advance(const GemvArgs& a) {
+  if (a.temps) *a.sample_ctr += 1u;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -376,6 +427,8 @@ stream_gemv_kernel(const GemvArgs a) {
   const int eb = tid >> 3, er = tid & 7;  // epilogue thread -> (batch row, tile row)
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
+  __shared__ SampleRow srows[kMaxRows];
+  if (MODE == kModeNormArgmax) sample_rows_load(a, srows, tid);   // a CTA barrier follows before the first epilogue
   int it = 0;
   bool copy_ok = true;
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += stride, ++it) {
@@ -417,7 +470,8 @@ stream_gemv_kernel(const GemvArgs a) {
         const int idx = tile * kTileRows + er;
         if (eb < a.rows) {
           if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + idx] = v;
-          if (v > best_v || (v == best_v && idx < best_i)) { best_v = v; best_i = idx; }
+          const float key = a.temps ? sample_key(a.sample_seed, a.sample_idx_offset, srows, eb, idx, v) : v;
+          if (key > best_v || (key == best_v && idx < best_i)) { best_v = key; best_i = idx; }
         }
       }
     }
@@ -468,7 +522,7 @@ stream_gemv_kernel(const GemvArgs a) {
           if (a.best_out) a.best_out[b] = ArgmaxPart{v, i};
         }
       }
-      if (tid == 0) *a.ticket = 0u;
+      if (tid == 0) { *a.ticket = 0u; sample_advance(a); }
     }
   }
   if (threadIdx.x == 0) trace_max(a.trace, 2);
@@ -850,6 +904,8 @@ struct StageArgs {
   const int* block_tables;
   int bt_cols, bt_stride_in, bt_stride_out;
   const int* row_active;     // null: all active
+  const float* temps;        // null: greedy step (temps_out is then left alone)
+  float* temps_out;
   int rows;
   int embed_rows;
   int* ids_out;
@@ -869,6 +925,10 @@ __global__ void stage_inputs_kernel(const StageArgs a) {
     a.ids_out[tid] = (int)id;
     a.positions_out[tid] = (int)a.positions[tid];
     a.row_active_out[tid] = a.row_active ? a.row_active[tid] : 1;
+    if (a.temps) {
+      const float t = a.temps[tid];
+      a.temps_out[tid] = t >= 0.f ? t : 0.f;   // negative or NaN: greedy
+    }
   }
   for (int i = tid; i < a.rows * a.bt_cols; i += blockDim.x) {
     const int r = i / a.bt_cols, c = i % a.bt_cols;

@@ -253,6 +253,8 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   const int er = tid >> 3, eb = tid & 7;  // epilogue thread (tid < 128) -> (tile row, batch row)
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
+  __shared__ SampleRow srows[kMaxRows];
+  if (MODE == kModeNormArgmax) sample_rows_load(a, srows, tid);   // a CTA barrier follows before the first epilogue
   int it = 0;
   bool copy_ok = true;
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += stride, ++it) {
@@ -301,7 +303,8 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
       if (eb < a.rows) {
         if (MODE == kModeNormArgmax) {
           if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + idx] = v;
-          if (v > best_v || (v == best_v && idx < best_i)) { best_v = v; best_i = idx; }
+          const float key = a.temps ? sample_key(a.sample_seed, a.sample_idx_offset, srows, eb, idx, v) : v;
+          if (key > best_v || (key == best_v && idx < best_i)) { best_v = key; best_i = idx; }
         } else {
           a.out[(size_t)eb * a.out_stride + idx] = __float2bfloat16_rn(v);
         }
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
           if (a.best_out) a.best_out[b] = ArgmaxPart{v, i};
         }
       }
-      if (tid == 0) *a.ticket = 0u;
+      if (tid == 0) { *a.ticket = 0u; sample_advance(a); }
     }
   }
   if (threadIdx.x == 0) trace_max(a.trace, 2);

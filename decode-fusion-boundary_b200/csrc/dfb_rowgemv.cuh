@@ -198,6 +198,8 @@ row_gemv_kernel(const GemvArgs a) {
   float best_v = -INFINITY;   // epilogue thread (b, r): running argmax of its rows
   int best_i = 0x7fffffff;
   const int eb = tid / RC, er = tid % RC;   // epilogue thread -> (batch row, row of the group), tid < RC * NB
+  __shared__ SampleRow srows[kMaxRows];
+  if (MODE == kModeNormArgmax) sample_rows_load(a, srows, tid);   // a CTA barrier follows before the first epilogue
 
   // ---- row groups of this CTA ----
   for (int it = 0; grp < n_groups; grp += gridDim.x, ++it) {
@@ -306,7 +308,8 @@ row_gemv_kernel(const GemvArgs a) {
         const int row = grp * RC + er;
         if (MODE == kModeNormArgmax) {
           if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + row] = v;
-          if (v > best_v || (v == best_v && row < best_i)) { best_v = v; best_i = row; }
+          const float key = a.temps ? sample_key(a.sample_seed, a.sample_idx_offset, srows, eb, row, v) : v;
+          if (key > best_v || (key == best_v && row < best_i)) { best_v = key; best_i = row; }
         } else {
           a.out[(size_t)eb * a.out_stride + row] = __float2bfloat16_rn(v);
         }
@@ -353,7 +356,7 @@ row_gemv_kernel(const GemvArgs a) {
           if (a.best_out) a.best_out[b] = ArgmaxPart{v, i};
         }
       }
-      if (tid == 0) *a.ticket = 0u;
+      if (tid == 0) { *a.ticket = 0u; sample_advance(a); }
     }
   }
   if (threadIdx.x == 0) trace_max(a.trace, 2);

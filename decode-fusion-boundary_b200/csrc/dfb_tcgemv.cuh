@@ -389,6 +389,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
     const bool lvalid = lane < R / 2;             // M = 64 keeps 16 rows in each quarter, M = 128 all 32
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
+    __shared__ SampleRow srows[kMaxRows];
+    if (MODE == kModeNormArgmax) {
+      sample_rows_load(a, srows, et);
+      named_sync(2, 128);
+    }
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles; tile += stride, ++it) {
@@ -431,7 +436,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
           if (eb < a.rows && row < args.n_rows) {
             if (MODE == kModeNormArgmax) {
               if (a.logits_out) a.logits_out[(size_t)eb * a.vocab + row] = val;
-              if (val > best_v || (val == best_v && row < best_i)) { best_v = val; best_i = row; }
+              const float key = a.temps ? sample_key(a.sample_seed, a.sample_idx_offset, srows, eb, row, val) : val;
+              if (key > best_v || (key == best_v && row < best_i)) { best_v = key; best_i = row; }
             } else {
               a.out[(size_t)eb * a.out_stride + row] = __float2bfloat16_rn(val);
             }
@@ -480,7 +486,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemv_kernel(const __grid_con
             if (a.best_out) a.best_out[b] = ArgmaxPart{bv, bi};
           }
         }
-        if (et == 0) *a.ticket = 0u;
+        if (et == 0) { *a.ticket = 0u; sample_advance(a); }
       }
     }
     if (et == 0) trace_max(a.trace, 2);

@@ -65,12 +65,24 @@ def taskgraph_compatibility(config: Any, seqs: list[Any], is_prefill: bool) -> T
             return TaskGraphCompatibility(
                 False, f"tensor-parallel group has {getattr(group, 'size', None)} ranks but "
                        f"tensor_parallel_size={tp_size}")
+    # Sampling.  The reference hands every non-greedy row back to torch (taskgraph.py:123-130); that stays the
+    # default.  ``config.megakernel_sampling`` opts in to the sampler fused after the LM head
+    # (layers/sampler.py:7-16 restated as a Gumbel-max draw): any true value admits a sampled single row, whose
+    # temperature ``MegakernelBackend.decode`` reads from the sequence; the value "batch" also admits sampled
+    # rows in batches, for engines that pass ``temperatures`` to ``MegakernelBackend.decode_batch`` (the stock
+    # ``ModelRunner.run`` does not).
+    sampling = getattr(config, "megakernel_sampling", False)
     for seq in seqs:
         if bool(getattr(seq, "is_greedy", False)):
             continue
         temperature = getattr(seq, "temperature", None)
         if temperature is None or temperature > 1e-10:
-            return TaskGraphCompatibility(False, "Task-graph megakernel supports greedy sampling only")
+            if temperature is None or not sampling:
+                return TaskGraphCompatibility(False, "Task-graph megakernel supports greedy sampling only")
+            if len(seqs) > 1 and sampling != "batch":
+                return TaskGraphCompatibility(
+                    False, "Task-graph megakernel samples batches only when the engine passes temperatures to "
+                           "decode_batch (config.megakernel_sampling = 'batch')")
     return TaskGraphCompatibility(True)
 
 
@@ -198,11 +210,17 @@ class StreamDecoder:
             f"(kernel {st.detail[0]}, index {st.detail[1]}, value {st.detail[2]})")
 
     # -- decode --------------------------------------------------------------
+    def set_seed(self, seed: int) -> None:
+        """Seed of the sampling noise; restarts the noise stream (``dfb_set_seed``)."""
+        self._native.check(self._lib.dfb_set_seed(self._handle, int(seed) & (2 ** 64 - 1)), "dfb_set_seed")
+
     def enqueue_rows(self, input_ids, positions, block_tables, active_rows=None, max_context: int = 0,
-                     out_logits=None) -> None:
+                     out_logits=None, temperatures=None) -> None:
         """Enqueue one step on the current stream without reading the result
         (device-resident loops; ``input_ids=None`` feeds the previous tokens
-        back).  ``tokens_device()`` holds the token ids once the stream is done."""
+        back).  ``tokens_device()`` holds the token ids once the stream is done.
+        ``temperatures``: ``None`` (greedy) or a float32 CUDA tensor ``[rows]``;
+        rows above 1e-10 are sampled as ``layers/sampler.py:7-16`` does."""
         torch = self._torch
         rows = int(positions.numel())
         if rows > self._max_rows:
@@ -232,12 +250,18 @@ class StreamDecoder:
             s.row_active = None
         s.out_tokens = self._result.data_ptr()
         s.out_logits = out_logits.data_ptr() if out_logits is not None else None
+        if temperatures is not None:
+            if temperatures.dtype != torch.float32 or not temperatures.is_cuda or temperatures.numel() != rows:
+                raise TypeError("temperatures must be a float32 CUDA tensor with one value per row")
+            s.temperatures = temperatures.data_ptr()
+        else:
+            s.temperatures = None
         self._native.check(self._lib.dfb_decode_step(self._handle, C.byref(s), self._stream()), "dfb_decode_step")
 
     def tokens_device(self):
         return self._result
 
-    def decode_rows(self, input_ids, positions, block_tables, active_rows=None) -> list[int]:
+    def decode_rows(self, input_ids, positions, block_tables, active_rows=None, temperatures=None) -> list[int]:
         """One decode step for every row.  ``input_ids`` / ``positions`` are 1-D
         int64 CUDA tensors, ``block_tables`` the padded ``[rows, <= max_pages]``
         int32 CUDA tensor of ``ModelRunner.prepare_block_tables``; returns one
@@ -245,7 +269,7 @@ class StreamDecoder:
         rows = int(input_ids.numel())
         if rows == 0:
             return []
-        self.enqueue_rows(input_ids, positions, block_tables, active_rows)
+        self.enqueue_rows(input_ids, positions, block_tables, active_rows, temperatures=temperatures)
         self._result_host.copy_(self._result, non_blocking=True)
         self._torch.cuda.current_stream().synchronize()
         out = self._result_host.tolist()
@@ -253,10 +277,11 @@ class StreamDecoder:
             self._raise_device_status()
         return out[:rows]
 
-    def decode_host(self, token_ids, positions, block_tables, active_rows=None) -> list[int]:
+    def decode_host(self, token_ids, positions, block_tables, active_rows=None, temperatures=None) -> list[int]:
         """One step from HOST data (lists of ints; one block-table list per
         row): one packed host-to-device copy, the step, one device-to-host
-        copy, one synchronisation -- all inside the native call."""
+        copy, one synchronisation -- all inside the native call.
+        ``temperatures``: ``None`` (greedy) or one float per row."""
         rows = len(token_ids)
         if rows == 0:
             return []
@@ -277,26 +302,32 @@ class StreamDecoder:
         active = None
         if active_rows is not None:
             active = (C.c_int32 * rows)(*row_active_mask(active_rows, rows))
-        code = self._lib.dfb_decode_step_host(self._handle, rows, self._h_ids, self._h_pos, self._h_bt, cols,
-                                              active, self._h_out, self._stream())
+        temps = None
+        if temperatures is not None:
+            if len(temperatures) != rows:
+                raise ValueError("one temperature per row")
+            temps = (C.c_float * rows)(*[float(t) for t in temperatures])
+        code = self._lib.dfb_decode_step_host_sampled(self._handle, rows, self._h_ids, self._h_pos, self._h_bt, cols,
+                                                      active, temps, self._h_out, self._stream())
         if code == -4:
             self._raise_device_status()
-        self._native.check(code, "dfb_decode_step_host")
+        self._native.check(code, "dfb_decode_step_host_sampled")
         return [int(self._h_out[r]) for r in range(rows)]
 
-    def decode_row(self, token_id: int, position: int, block_table) -> int:
+    def decode_row(self, token_id: int, position: int, block_table, temperature: float = 0.0) -> int:
         """Single-row path of ``ModelRunner`` (batch 1): takes the scheduler's
         host block table directly."""
         if self._torch.is_tensor(block_table):
             block_table = block_table.tolist()
         table = list(block_table)[: self._max_pages]
-        return self.decode_host([int(token_id)], [int(position)], [table])[0]
+        temps = [float(temperature)] if temperature and temperature > 1e-10 else None
+        return self.decode_host([int(token_id)], [int(position)], [table], temperatures=temps)[0]
 
     # -- the one-step interface MegakernelBackend calls -----------------------
-    def step(self, token_id: int, position: int | None = None, block_table=None) -> int:
+    def step(self, token_id: int, position: int | None = None, block_table=None, temperature: float = 0.0) -> int:
         if position is None or block_table is None:
             raise ValueError("task-graph decode requires position and block_table")
-        return self.decode_row(token_id, position, block_table)
+        return self.decode_row(token_id, position, block_table, temperature)
 
-    def step_batch(self, input_token_ids, positions, block_tables) -> list[int]:
-        return self.decode_rows(input_token_ids, positions, block_tables)
+    def step_batch(self, input_token_ids, positions, block_tables, temperatures=None) -> list[int]:
+        return self.decode_rows(input_token_ids, positions, block_tables, temperatures=temperatures)

@@ -18,7 +18,7 @@ LIB_PATH = PKG_DIR / "libdfb_decode.so"
 SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
 HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR / "csrc" / "dfb_tcgemv.cuh", PKG_DIR / "csrc" / "dfb_attnring.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
 
-DFB_ABI_VERSION = 1
+DFB_ABI_VERSION = 2
 DFB_MAX_ROWS = 8
 DFB_ATTN_CHUNK = 64
 DFB_TP_HANDLE_BYTES = 64
@@ -41,7 +41,7 @@ EXPORTS = (
     "dfb_read_status", "dfb_error_string", "dfb_read_trace", "dfb_launch_rmsnorm_qkv", "dfb_launch_attention",
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
-    "dfb_tp_open_loopback",
+    "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
 )
 
 
@@ -74,7 +74,7 @@ class DfbStepDesc(C.Structure):
         ("rows", C.c_int32), ("block_table_cols", C.c_int32), ("block_table_stride", C.c_int32),
         ("max_context", C.c_int32), ("input_ids", C.c_void_p), ("positions", C.c_void_p),
         ("block_tables", C.c_void_p), ("row_active", C.c_void_p), ("out_tokens", C.c_void_p),
-        ("out_logits", C.c_void_p),
+        ("out_logits", C.c_void_p), ("temperatures", C.c_void_p),
     ]
 
 
@@ -130,6 +130,9 @@ def lib() -> C.CDLL:
     L.dfb_set_option.argtypes = [vp, C.c_int, C.c_int]
     L.dfb_decode_step.argtypes = [vp, C.POINTER(DfbStepDesc), vp]
     L.dfb_decode_step_host.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp]
+    L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
+    L.dfb_set_seed.argtypes = [vp, C.c_uint64]
+    L.dfb_launch_lmhead_sample.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp]
     L.dfb_read_status.argtypes = [vp, C.POINTER(DfbStatus)]
     L.dfb_read_trace.argtypes = [vp, vp, i32]
     L.dfb_error_string.argtypes = [C.c_int]

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define DFB_ABI_VERSION 1
+#define DFB_ABI_VERSION 2
 #define DFB_MAX_ROWS 8          /* TG_MAX_BATCH, backends/megakernel/taskgraph.py:33 */
 #define DFB_ATTN_CHUNK 64       /* context positions handled by one attention CTA */
 
@@ -97,6 +97,9 @@ typedef struct DfbStepDesc {
                                  decoder's status word (see DfbStatus) in [DFB_MAX_ROWS, DFB_MAX_ROWS + 4),
                                  so one device-to-host read returns both */
   float* out_logits;          /* [rows, vocab] or NULL; bf16-rounded logits as fp32 (parity checks) */
+  const float* temperatures;  /* NULL = greedy step, or [rows] sampling temperatures (device): rows with a
+                                 temperature above 1e-10 draw from softmax(logits / T), the others stay greedy
+                                 (layers/sampler.py:7-16; see dfb_set_seed) */
 } DfbStepDesc;
 
 /* Tensor-parallel shard of the step.  The reference's megakernel backend runs
@@ -231,6 +234,25 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
                          const int32_t* block_tables, int32_t cols, const int32_t* row_active,
                          int32_t* out_tokens, dfb_stream_t stream);
 
+/* dfb_decode_step_host with one sampling temperature per row (host array, NULL = greedy for every row; a
+ * negative or NaN temperature is DFB_E_BAD_ARG, as sampling_params.py:14-15 rejects it).  The temperatures
+ * travel in the same host-to-device copy as the other inputs.  Replaces prepare_sample + Sampler.forward
+ * (engine/model_runner.py:286-289,374, layers/sampler.py:7-16) for the rows the backend would otherwise hand
+ * back with "greedy sampling only" (backends/megakernel/taskgraph.py:123-130). */
+int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
+                                 const int32_t* block_tables, int32_t cols, const int32_t* row_active,
+                                 const float* temperatures, int32_t* out_tokens, dfb_stream_t stream);
+
+/* Seed of the sampling noise (default 0) and restart of its stream.  A sampled row takes
+ * argmax_i(logit_i / T - log E_i), E_i ~ Exp(1) clamped at 1e-10, which is the reference's
+ * argmax(softmax(logits / T) / E) without the softmax pass.  E_i = -log(u_i), u_i = (top 23 bits of
+ * splitmix64_finalise(seed + c * 0x9E3779B97F4A7C15) + 0.5) / 2^23 with the 64-bit counter
+ * c = ((n * 8 + row) << 32) | i, n = the number of sampled LM-head launches of this decoder since the seed was
+ * set (greedy steps do not advance it), i = the token's index in the whole vocabulary: the draw is a
+ * function of (seed, n, row, i) alone, identical on every tensor-parallel rank and reproducible on the host.
+ * torch's own generator stream is not reproduced: parity with the reference's sampler is in distribution. */
+int dfb_set_seed(DfbHandle* h, uint64_t seed);
+
 /* Read (and clear) the device status word; synchronises nothing by itself, so
  * call it after the stream has been synchronised. */
 int dfb_read_status(DfbHandle* h, DfbStatus* out);
@@ -274,6 +296,9 @@ int dfb_launch_rmsnorm_gateup_swiglu(const void* h, const void* residual, void* 
  * LM head, bf16-rounded logits, greedy argmax (lowest index wins ties). */
 int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* residual, int32_t* out_tokens,
                              float* out_logits, int32_t rows, dfb_stream_t stream);
+/* The same with sampling: `temperatures` is a DEVICE array [rows] (NULL = greedy); layers/sampler.py:7-16. */
+int dfb_launch_lmhead_sample(DfbHandle* h, const void* hidden_in, const void* residual, const float* temperatures,
+                             int32_t* out_tokens, float* out_logits, int32_t rows, dfb_stream_t stream);
 
 /* Final add+RMSNorm, tied LM head and greedy argmax WITHOUT any allocation.
  * (No counterpart in the reference: its LM head always runs inside a decoder

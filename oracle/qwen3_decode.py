@@ -332,6 +332,50 @@ def greedy(logits: torch.Tensor) -> torch.Tensor:
     return logits.float().argmax(dim=-1)
 
 
+def sample(logits: torch.Tensor, temperatures: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
+    """layers/sampler.py:7-16 with the exponential draw passed in (``noise``,
+    fp32 ``[rows, vocab]``, what ``torch.empty_like(probs).exponential_(1)``
+    returned): softmax of logits / T, divided by the clamped noise, argmax;
+    rows with T <= 1e-10 take the plain argmax."""
+    logits = logits.float()
+    greedy_rows = temperatures <= 1e-10
+    safe = temperatures.clamp_min(1e-10).unsqueeze(1)
+    probs = torch.softmax(logits / safe, dim=-1)
+    sampled = (probs / noise.clamp_min(1e-10)).argmax(dim=-1)
+    return torch.where(greedy_rows, logits.argmax(dim=-1), sampled)
+
+
+def sample_keys(logits: torch.Tensor, temperatures: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
+    """The same draw in log space: argmax(probs / E) = argmax(logit / T - log E),
+    since the softmax divides a row by one positive number.  Used to judge how
+    close a second candidate was (fp32 ``[rows, vocab]``; greedy rows: the logits)."""
+    logits = logits.float()
+    safe = temperatures.clamp_min(1e-10).unsqueeze(1)
+    keys = logits / safe - torch.log(noise.clamp_min(1e-10))
+    return torch.where((temperatures <= 1e-10).unsqueeze(1), logits, keys)
+
+
+def counter_noise(seed: int, step: int, rows: int, vocab: int, index_offset: int = 0) -> torch.Tensor:
+    """The exponential noise of the CUDA backend's fused sampler, as its
+    interface documents it (include/dfb_decode.h, dfb_set_seed): for row r and
+    vocabulary index i the 64-bit counter c = ((step * 8 + r) << 32) | i, the
+    splitmix64 finaliser of seed + c * 0x9E3779B97F4A7C15, its top 23 bits + 0.5
+    over 2^23 as the uniform u, and E = max(-log u, 1e-10).  (The reference
+    draws from torch's generator instead; only the distribution is shared.)"""
+    mask = (1 << 64) - 1
+    r = np.arange(rows, dtype=np.uint64)[:, None]
+    i = (np.arange(vocab, dtype=np.uint64) + np.uint64(index_offset))[None, :]
+    with np.errstate(over="ignore"):
+        ctr = ((np.uint64(step * 8) + r) << np.uint64(32)) | i
+        z = np.uint64(seed & mask) + ctr * np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    u = ((z >> np.uint64(41)).astype(np.float32) + np.float32(0.5)) * np.float32(2.0 ** -23)
+    e = np.maximum(-np.log(u, dtype=np.float32), np.float32(1e-10))
+    return torch.from_numpy(e.astype(np.float32))
+
+
 # ----------------------------------------------------------------------------
 # Whole-step and whole-sequence drivers.
 # ----------------------------------------------------------------------------

@@ -212,12 +212,37 @@ def _summarise(logits, probe):
                 top_logits=np.take_along_axis(logits, top, -1).astype(np.float32))
 
 
+def sampler_fixture(ref) -> None:
+    """The reference's ``Sampler.forward`` (layers/sampler.py:7-16) on seeded
+    logits with greedy and sampled rows.  The exponential noise it draws is
+    stored too: the generator is re-seeded, the same-shaped fp32 draw is taken
+    once outside and once (after re-seeding again) inside the sampler."""
+    Sampler = ref[1]
+    rows, vocab = 6, 1024
+    torch.manual_seed(1234)
+    logits = (torch.randn(rows, vocab) * 3.0).to(torch.bfloat16)
+    temps = torch.tensor([0.0, 1e-12, 0.5, 0.7, 1.0, 1.6], dtype=torch.float32)
+    tokens, noises = [], []
+    for draw in range(8):
+        torch.manual_seed(9000 + draw)
+        noises.append(torch.empty(rows, vocab, dtype=torch.float32).exponential_(1))
+        torch.manual_seed(9000 + draw)
+        tokens.append(Sampler()(logits, temps))
+    np.savez_compressed(HERE / "sampler_rows6_vocab1024.npz", logits=logits.float().numpy(), temperatures=temps.numpy(),
+                        noise=torch.stack(noises).numpy(), tokens=torch.stack(tokens).numpy().astype(np.int64))
+    print("sampler tokens", torch.stack(tokens).tolist())
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory holding src/nanovllm)")
     ap.add_argument("--skip-full", action="store_true")
+    ap.add_argument("--only-sampler", action="store_true", help="write only the sampler fixture")
     args = ap.parse_args()
     ref = _import_reference(args.reference)
+    sampler_fixture(ref)
+    if args.only_sampler:
+        return
 
     # (B) small geometry, three rows crossing the 256-token block boundary,
     # blocks scattered by a permutation; fp32 and bf16 activations.

@@ -36,7 +36,8 @@ def test_struct_layouts():
     assert C.sizeof(native.DfbLayerWeights) == 64
     assert C.sizeof(native.DfbModelDesc) == 12 * 4 + 6 * 8
     assert native.DfbModelDesc.embed.offset == 48
-    assert C.sizeof(native.DfbStepDesc) == 16 + 6 * 8
+    assert C.sizeof(native.DfbStepDesc) == 16 + 7 * 8
+    assert native.DfbStepDesc.temperatures.offset == 16 + 6 * 8
     assert C.sizeof(native.DfbStatus) == 32
 
 

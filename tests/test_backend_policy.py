@@ -63,6 +63,21 @@ def test_admission_reasons_in_order():
     assert ok.supported and ok.reason == ""
 
 
+def test_sampling_is_admitted_only_on_request():
+    """Default: the reference's answer for every sampled row (taskgraph.py:123-130).  With
+    ``megakernel_sampling`` a sampled single row is taken (its temperature comes from the sequence); batches
+    need the value "batch", because the stock ModelRunner.run passes no temperatures to decode_batch."""
+    f = MegakernelBackend.compatibility
+    only = "Task-graph megakernel supports greedy sampling only"
+    assert f(cfg(), [Seq(temperature=0.7)], False).reason == only
+    on = cfg(megakernel_sampling=True)
+    assert f(on, [Seq(temperature=0.7)], False).supported
+    assert f(on, [Seq(temperature=None)], False).reason == only
+    assert f(on, [Seq(), Seq()], False).supported                      # greedy batches as before
+    assert "passes temperatures to decode_batch" in f(on, [Seq(), Seq(temperature=0.7)], False).reason
+    assert f(cfg(megakernel_sampling="batch"), [Seq(), Seq(temperature=0.7)], False).supported
+
+
 def test_is_greedy_flag_short_circuits_temperature():
     s = Seq(temperature=0.9)
     s.is_greedy = True
@@ -139,10 +154,10 @@ class FakeDecoder:
     def __init__(self, fail=False):
         self.calls, self.fail = [], fail
 
-    def step(self, token, position=None, block_table=None):
+    def step(self, token, position=None, block_table=None, **sampling):
         if self.fail:
             raise RuntimeError("boom")
-        self.calls.append(("step", token, position, list(block_table)))
+        self.calls.append(("step", token, position, list(block_table), *sampling.values()))
         return 42
 
     def decode_rows(self, ids, positions, tables):
@@ -158,6 +173,14 @@ def test_decode_passes_pre_decode_length_as_position():
     assert b.decode(s, s.block_table) == [42]
     assert b.decoder.calls == [("step", 11, 299, [4, 9])]
     assert b.decode_batch("i", "p", "t") == [1, 2]
+    # a sampled row reaches the decoder with its temperature only when sampling was asked for
+    hot = Seq(temperature=0.8, n=300, block_table=(4, 9))
+    assert b.decode(hot, hot.block_table) == [42] and b.decoder.calls[-1] == ("step", 11, 299, [4, 9])
+    b2 = MegakernelBackend(cfg(megakernel_sampling=True), model=None)
+    b2.kv_cache = object()
+    b2.decoder = FakeDecoder()
+    assert b2.decode(hot, hot.block_table) == [42] and b2.decoder.calls[-1] == ("step", 11, 299, [4, 9], 0.8)
+    assert b2.decode(s, s.block_table) == [42] and b2.decoder.calls[-1] == ("step", 11, 299, [4, 9])
 
 
 def test_dispatch_fallback_contract():

@@ -85,3 +85,32 @@ def test_byte_accounting():
     g = O.QWEN3_06B
     assert g.weight_bytes_per_step() == 1_192_099_840
     assert g.kv_bytes_per_token() == 114_688
+
+
+def test_sampler_matches_reference_sampler():
+    """``O.sample`` against the reference's ``Sampler.forward`` (layers/sampler.py:7-16) run by
+    ``tests/golden/make_golden.py`` on the same logits, temperatures and exponential noise; the log-space
+    form the CUDA kernels use picks the same tokens."""
+    d = np.load(GOLDEN / "sampler_rows6_vocab1024.npz")
+    logits, temps = torch.from_numpy(d["logits"]), torch.from_numpy(d["temperatures"])
+    for k in range(d["noise"].shape[0]):
+        noise = torch.from_numpy(d["noise"][k])
+        assert O.sample(logits, temps, noise).tolist() == d["tokens"][k].tolist()
+        assert O.sample_keys(logits, temps, noise).argmax(-1).tolist() == d["tokens"][k].tolist()
+    assert len({tuple(t) for t in d["tokens"].tolist()}) > 1          # the draws differ: the fixture samples
+
+
+def test_counter_noise_is_exponential():
+    """The documented counter-based noise: Exp(1) moments and tail, no repeats across rows, steps or seeds."""
+    e = O.counter_noise(seed=5, step=3, rows=8, vocab=151936).double()
+    n = e.numel()
+    assert abs(float(e.mean()) - 1.0) < 5e-3 and abs(float(e.var()) - 1.0) < 2e-2
+    for x in (0.1, 1.0, 3.0):
+        assert abs(float((e > x).double().mean()) - float(np.exp(-x))) < 4.0 * (np.exp(-x) / n) ** 0.5 + 1e-3
+    assert float(e.min()) > 0.0
+    assert not torch.equal(e[0], e[1])
+    assert not torch.equal(e, O.counter_noise(5, 4, 8, 151936).double())
+    assert not torch.equal(e, O.counter_noise(6, 3, 8, 151936).double())
+    # a shard sees the noise of its global indices
+    part = O.counter_noise(5, 3, 8, 1000, index_offset=4000).double()
+    assert torch.equal(part, e[:, 4000:5000])
