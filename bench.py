@@ -711,6 +711,24 @@ def run_own_arm(args):
         e2e_runs = [max_over_ranks(torch, e2e_loop(W, K)) for _ in range(max(3, args.repeats // 2))]
         e2e_ms = statistics.median(e2e_runs)
 
+        # (2b) the same steps as ONE call: a burst of K steps from host inputs (one H2D, tokens fed back on the
+        # device and published in pinned host memory by the device, one synchronisation per call)
+        def burst_loop(n_warm, n_timed):
+            cur = [int(t) for t in torch.randint(0, g.vocab, (B,)).tolist()]
+            nblk = -(-(P + n_warm + n_timed + 1) // g.block_size)
+            bt = [t[:nblk] for t in tables]
+            if n_warm:
+                cur = dec.decode_burst(cur, [P] * B, bt, n_warm)[-1]
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); barrier(); start.record(); t0 = time.perf_counter()
+            dec.decode_burst(cur, [P + n_warm] * B, bt, n_timed)
+            stop.record(); torch.cuda.synchronize(); wall = time.perf_counter() - t0; barrier()
+            return max(start.elapsed_time(stop), 1e3 * wall)
+        burst_ms = None
+        if K <= native.DFB_MAX_BURST and P + W + K < g.max_model_len:
+            burst_runs = [max_over_ranks(torch, burst_loop(W, K)) for _ in range(max(3, args.repeats // 2))]
+            burst_ms = statistics.median(burst_runs)
+
         # (3) where the step's time goes: the library's own timeline of one live step, and every kernel alone
         shares, span_us = ({}, 0.0)
         kernels = []
@@ -746,9 +764,13 @@ def run_own_arm(args):
         "step_floor": {"bytes_per_step": step_bytes, "floor_us": step_bytes / (peak * 1e3),
                        "frac_of_floor": step_bytes / (peak * 1e3) / us_per_step, "peak_gbs": peak, "peak": peak_kind},
         "e2e": {"value": world * B * K / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms / K,
-                "h2d_bytes_per_step": 4 * (24 + 8 * g.max_pages) if B == 1 else 8 * B * 2 + 4 * B * g.max_pages,
+                "h2d_bytes_per_step": 4 * (32 + 8 * g.max_pages) if B == 1 else 8 * B * 2 + 4 * B * g.max_pages,
                 "d2h_bytes_per_step": 48, "api": "MegakernelBackend.decode" if B == 1 else "MegakernelBackend.decode_batch",
                 "runs": len(e2e_runs)},
+        "e2e_burst": None if burst_ms is None else {
+            "value": world * B * K / (burst_ms / 1e3), "unit": UNIT, "ms_per_step": burst_ms / K, "steps_per_call": K,
+            "h2d_bytes_per_call": 4 * (32 + 8 * g.max_pages), "api": "StreamDecoder.decode_burst "
+            "(dfb_decode_burst_host: K steps per call, tokens fed back on the device, one synchronisation)"},
         "gpu_launches": kernels_per_step * K,
         "step_kernels": step_kernel,
         "clocks": clocks,

@@ -176,6 +176,8 @@ struct Launcher {
 
 }  // namespace
 
+constexpr int kMaxBurst = 1024;   // steps of one burst (capacity of the pinned token ring)
+
 struct DfbHandle {
   DfbModelDesc m;
   std::vector<DfbLayerWeights> layers;
@@ -216,6 +218,13 @@ struct DfbHandle {
   unsigned long long sample_seed = 0;   // dfb_set_seed
   unsigned int* sample_ctr = nullptr;   // device: sampled LM-head launches so far (position in the noise stream)
   const float* lm_temps = nullptr;      // temperatures the LM head being enqueued samples with (null = greedy)
+  // burst: several steps enqueued at once, tokens published in a pinned ring written by the device
+  int* burst_ring = nullptr;            // pinned: [kMaxBurst][8] tokens | [4] status | [1] steps done
+  unsigned int* burst_slot = nullptr;   // device
+  cudaEvent_t burst_event = nullptr;
+  int burst_rows = 0, burst_steps = 0;  // of the burst in flight (0 = none)
+  int* burst_status() const { return burst_ring + kMaxBurst * kMaxRows; }
+  volatile int* burst_done() const { return burst_ring + kMaxBurst * kMaxRows + 4; }
   cudaStream_t capture_stream = nullptr;
   // One captured step: the input staging (a kernel for device inputs, a host-to-device copy for host inputs),
   // the kernel chain and the copy-out of tokens + status, so that a step is ONE graph launch with no
@@ -755,11 +764,14 @@ struct StepIo {
   bool host = false;                  // host inputs: h->host_stage -> h->stage before, h->tokens -> h->host_tokens after
   int* out_tokens = nullptr;          // device inputs: optional copy of tokens + status
   bool sampling = false;              // the staged temperatures are live: the LM head samples rows with T > 1e-10
+  bool burst = false;                 // inputs are already staged on the device; publish_tokens_kernel follows the chain
 };
 
 int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream,
                        float* logits_out) {
-  if (io.host) {
+  if (io.burst) {
+    // staged by the burst's one host-to-device copy, advanced on the device from step to step
+  } else if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->stage, h->host_stage, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
   } else if (io.stage) {
     stage_inputs_kernel<<<1, 128, 0, stream>>>(*io.stage);
@@ -771,7 +783,14 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
                              : enqueue_step(h, rows, nsplit, bt_cols, stream, logits_out);
   h->lm_temps = nullptr;
   if (rc) return rc;
-  if (io.host) {
+  if (io.burst) {
+    PublishArgs p = {};
+    p.tokens = h->tokens; p.status = h->status; p.ids_out = h->st_ids(); p.positions_out = h->st_pos();
+    p.rows = rows; p.embed_rows = h->embed_rows(); p.slot = h->burst_slot;
+    p.ring = h->burst_ring; p.ring_status = h->burst_status(); p.ring_done = h->burst_done();
+    publish_tokens_kernel<<<1, 32, 0, stream>>>(p);
+    DFB_CUDA(cudaGetLastError());
+  } else if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   } else if (io.out_tokens) {
     DFB_CUDA(cudaMemcpyAsync(io.out_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToDevice, stream));
@@ -783,7 +802,7 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
   const bool persistent = h->step_mode == 1;
   if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
   // one graph per (rows, split bucket, filled block-table columns, kind of inputs / outputs)
-  const int io_kind = (io.host ? 3 : (io.out_tokens ? 2 : 1)) + (io.sampling ? 4 : 0);
+  const int io_kind = (io.burst ? 0 : io.host ? 3 : (io.out_tokens ? 2 : 1)) + (io.sampling ? 4 : 0);
   const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 1024 + nsplit) * 2 +
                          (h->use_pdl ? 1 : 0)) * 8 + io_kind;
   auto it = h->graphs.find(key);
@@ -795,7 +814,7 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) return (int)e;
     DfbHandle::StepGraph g;
-    if (!io.host) {
+    if (!io.host && !io.burst) {
       // find the two nodes whose parameters follow the caller's pointers
       size_t n = 0;
       e = cudaGraphGetNodes(graph, nullptr, &n);
@@ -824,7 +843,7 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
     it = h->graphs.emplace(key, g).first;
   }
   DfbHandle::StepGraph& g = it->second;
-  if (!io.host) {
+  if (!io.host && !io.burst) {
     if (memcmp(&g.stage_args, io.stage, sizeof(StageArgs)) != 0) {
       StageArgs args = *io.stage;
       void* params[1] = {&args};
@@ -919,10 +938,13 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_best = carve(sizeof(ArgmaxPart) * kMaxRows * 9);  // this rank's winners | all ranks' (up to 8)
   const size_t o_tpstep = carve(sizeof(unsigned) * 4);
   const size_t o_sctr = carve(sizeof(unsigned) * 4);
+  const size_t o_bslot = carve(sizeof(unsigned) * 4);
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_tokens, sizeof(int) * (kMaxRows + 4));
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->burst_ring, sizeof(int) * (kMaxBurst * kMaxRows + 8));
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->burst_event, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) { dfb_destroy(h); return (int)e; }
   char* s = (char*)h->slab;
@@ -947,6 +969,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   h->best_local = (ArgmaxPart*)(s + o_best); h->best_all = h->best_local + kMaxRows;
   h->tp_step = (unsigned int*)(s + o_tpstep);
   h->sample_ctr = (unsigned int*)(s + o_sctr);
+  h->burst_slot = (unsigned int*)(s + o_bslot);
   *out = h;
   return 0;
 }
@@ -962,6 +985,8 @@ void dfb_destroy(DfbHandle* h) {
   if (h->window_local) cudaFree(h->window_local);
   if (h->host_stage) cudaFreeHost(h->host_stage);
   if (h->host_tokens) cudaFreeHost(h->host_tokens);
+  if (h->burst_ring) cudaFreeHost(h->burst_ring);
+  if (h->burst_event) cudaEventDestroy(h->burst_event);
   if (h->slab) cudaFree(h->slab);
   delete h;
 }
@@ -1167,18 +1192,21 @@ int dfb_decode_step_host(DfbHandle* h, int32_t rows, const int64_t* input_ids, c
                                       out_tokens, stream_);
 }
 
-int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
-                                 const int32_t* block_tables, int32_t cols, const int32_t* row_active,
-                                 const float* temperatures, int32_t* out_tokens, dfb_stream_t stream_) {
-  if (!h || !input_ids || !positions || !block_tables || !out_tokens) return DFB_E_BAD_ARG;
-  if (rows < 1 || rows > kMaxRows || cols < 1) return DFB_E_BAD_ARG;
+// Validates one step's host inputs (for a burst: of all its steps) and packs them into the pinned staging
+// buffer: ids | positions | row_active | block tables | temperatures.  Returns 0 and the largest context.
+static int pack_host_inputs(DfbHandle* h, int rows, const int64_t* input_ids, const int64_t* positions,
+                            const int32_t* block_tables, int cols, const int32_t* row_active,
+                            const float* temperatures, int steps, int* max_ctx_out) {
+  if (!h || !input_ids || !positions || !block_tables) return DFB_E_BAD_ARG;
+  if (rows < 1 || rows > kMaxRows || cols < 1 || steps < 1) return DFB_E_BAD_ARG;
   if (cols > h->max_pages) return DFB_E_TOO_LARGE;
-  cudaStream_t stream = (cudaStream_t)stream_;
+  if (h->burst_steps) return DFB_E_BAD_ARG;   // a burst is in flight: collect it first (it owns the staging buffers)
   int* hs = h->host_stage;
   int max_ctx = 1;
   for (int r = 0; r < rows; ++r) {
-    if (positions[r] < 0 || positions[r] >= h->m.max_model_len) return DFB_E_BAD_ARG;
-    if (positions[r] >= (int64_t)cols * h->m.block_size) return DFB_E_BAD_ARG;   // beyond the block table given
+    const int64_t last = positions[r] + steps - 1;                              // position of the row's last step
+    if (positions[r] < 0 || last >= h->m.max_model_len) return DFB_E_BAD_ARG;
+    if (last >= (int64_t)cols * h->m.block_size) return DFB_E_BAD_ARG;         // beyond the block table given
     // ids index the whole (replicated) embedding table, also on a tensor-parallel shard
     if (input_ids[r] < 0 || input_ids[r] >= h->embed_rows()) return DFB_E_BAD_ARG;
     hs[r] = (int)input_ids[r];
@@ -1191,10 +1219,22 @@ int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* inpu
       memcpy(&hs[24 + 8 * h->max_pages + r], &temperatures[r], sizeof(float));
     }
   }
+  *max_ctx_out = max_ctx;
+  return 0;
+}
+
+int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* input_ids, const int64_t* positions,
+                                 const int32_t* block_tables, int32_t cols, const int32_t* row_active,
+                                 const float* temperatures, int32_t* out_tokens, dfb_stream_t stream_) {
+  if (!out_tokens) return DFB_E_BAD_ARG;
+  int max_ctx = 1;
+  int rc = pack_host_inputs(h, rows, input_ids, positions, block_tables, cols, row_active, temperatures, 1, &max_ctx);
+  if (rc) return rc;
+  cudaStream_t stream = (cudaStream_t)stream_;
   StepIo io;
   io.sampling = temperatures != nullptr;
   io.host = true;      // the two copies between the pinned staging buffers and the device are part of the step's graph
-  int rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, io, stream, nullptr);
+  rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, io, stream, nullptr);
   if (rc) return rc;
   DFB_CUDA(cudaStreamSynchronize(stream));
   for (int r = 0; r < rows; ++r) out_tokens[r] = h->host_tokens[r];
@@ -1206,6 +1246,66 @@ int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* inpu
     return DFB_E_DEVICE_STATUS;
   }
   return 0;
+}
+
+int dfb_decode_burst_enqueue(DfbHandle* h, int32_t rows, int32_t steps, const int64_t* input_ids,
+                             const int64_t* positions, const int32_t* block_tables, int32_t cols,
+                             const int32_t* row_active, const float* temperatures, dfb_stream_t stream_) {
+  if (steps > kMaxBurst) return DFB_E_TOO_LARGE;
+  int max_ctx = 1;
+  int rc = pack_host_inputs(h, rows, input_ids, positions, block_tables, cols, row_active, temperatures, steps, &max_ctx);
+  if (rc) return rc;
+  if (h->step_mode == 1) return DFB_E_BAD_ARG;   // the persistent kernel takes its inputs per launch
+  cudaStream_t stream = (cudaStream_t)stream_;
+  *h->burst_done() = 0;
+  DFB_CUDA(cudaMemsetAsync(h->burst_slot, 0, sizeof(unsigned), stream));
+  DFB_CUDA(cudaMemcpyAsync(h->stage, h->host_stage, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
+  StepIo io;
+  io.sampling = temperatures != nullptr;
+  io.burst = true;
+  for (int s = 0; s < steps; ++s) {
+    // the attention grid follows the growing context; everything else of the step is the same graph
+    rc = run_step(h, rows, split_bucket(h, max_ctx + s, rows), cols, io, stream, nullptr);
+    if (rc) return rc;
+    ++h->steps;
+  }
+  DFB_CUDA(cudaEventRecord(h->burst_event, stream));
+  h->burst_rows = rows;
+  h->burst_steps = steps;
+  return 0;
+}
+
+int dfb_decode_burst_collect(DfbHandle* h, int32_t wait, int32_t* out_tokens, int32_t* steps_done) {
+  if (!h || !out_tokens || !steps_done) return DFB_E_BAD_ARG;
+  *steps_done = 0;
+  if (!h->burst_steps) return DFB_E_BAD_ARG;
+  if (wait) DFB_CUDA(cudaEventSynchronize(h->burst_event));
+  int done = *h->burst_done();   // written by the device after the tokens of that step (system-wide fence between)
+  if (done > h->burst_steps) done = h->burst_steps;
+  for (int s = 0; s < done; ++s)
+    for (int r = 0; r < h->burst_rows; ++r) out_tokens[s * h->burst_rows + r] = h->burst_ring[s * kMaxRows + r];
+  *steps_done = done;
+  if (done < h->burst_steps) return 0;     // still running (wait == 0): call again
+  h->burst_steps = 0;
+  const int* st = h->burst_status();
+  if (st[0]) {
+    h->last_status[0] = st[0]; h->last_status[1] = st[1]; h->last_status[2] = st[2]; h->last_status[3] = st[3];
+    DFB_CUDA(cudaMemset(h->status, 0, sizeof(int) * 4));
+    return DFB_E_DEVICE_STATUS;
+  }
+  return 0;
+}
+
+int dfb_decode_burst_host(DfbHandle* h, int32_t rows, int32_t steps, const int64_t* input_ids,
+                          const int64_t* positions, const int32_t* block_tables, int32_t cols,
+                          const int32_t* row_active, const float* temperatures, int32_t* out_tokens,
+                          dfb_stream_t stream) {
+  if (!out_tokens) return DFB_E_BAD_ARG;
+  int rc = dfb_decode_burst_enqueue(h, rows, steps, input_ids, positions, block_tables, cols, row_active,
+                                    temperatures, stream);
+  if (rc) return rc;
+  int done = 0;
+  return dfb_decode_burst_collect(h, 1, out_tokens, &done);
 }
 
 int dfb_read_status(DfbHandle* h, DfbStatus* out) {

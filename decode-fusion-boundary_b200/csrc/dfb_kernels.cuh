@@ -936,4 +936,44 @@ __global__ void stage_inputs_kernel(const StageArgs a) {
   }
 }
 
+
+// Between the steps of a burst (several decode steps enqueued at once, dfb_decode_burst_enqueue): publishes
+// the step's tokens in a ring in pinned host memory that the kernel writes directly (no copy node, the host
+// can read finished steps while later ones run), then turns them into the next step's inputs on the device:
+// ids = tokens (clamped as in stage_inputs_kernel), positions + 1.
+struct PublishArgs {
+  const int* tokens;        // [rows] this step's result
+  int* status;              // [4] device status word
+  int* ids_out;             // staged inputs of the next step
+  int* positions_out;
+  int rows, embed_rows;
+  unsigned int* slot;       // device: steps published so far in this burst
+  int* ring;                // pinned host memory, mapped: [capacity][8] tokens
+  int* ring_status;         // pinned: [4] copy of the status word
+  volatile int* ring_done;  // pinned: steps whose tokens are visible to the host
+};
+__global__ void publish_tokens_kernel(const PublishArgs a) {
+  const int tid = threadIdx.x;
+  const unsigned slot = *a.slot;
+  if (tid < a.rows) {
+    const int tok = a.tokens[tid];
+    a.ring[slot * kMaxRows + tid] = tok;
+    long long id = tok;
+    if (id < 0 || id >= a.embed_rows) {
+      report_status(a.status, kStatusBadToken, kKernelStage, tid, tok);
+      id = 0;
+    }
+    a.ids_out[tid] = (int)id;
+    a.positions_out[tid] += 1;
+  }
+  __syncwarp();
+  if (tid < 4) a.ring_status[tid] = a.status[tid];
+  __threadfence_system();
+  __syncwarp();
+  if (tid == 0) {
+    *a.ring_done = (int)slot + 1;
+    *a.slot = slot + 1;
+  }
+}
+
 }  // namespace dfb

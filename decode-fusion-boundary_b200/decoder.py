@@ -282,11 +282,20 @@ class StreamDecoder:
         row): one packed host-to-device copy, the step, one device-to-host
         copy, one synchronisation -- all inside the native call.
         ``temperatures``: ``None`` (greedy) or one float per row."""
-        rows = len(token_ids)
-        if rows == 0:
+        if len(token_ids) == 0:
             return []
+        rows, cols, active, temps = self._pack_host(token_ids, positions, block_tables, active_rows, temperatures)
+        code = self._lib.dfb_decode_step_host_sampled(self._handle, rows, self._h_ids, self._h_pos, self._h_bt, cols,
+                                                      active, temps, self._h_out, self._stream())
+        if code == -4:
+            self._raise_device_status()
+        self._native.check(code, "dfb_decode_step_host_sampled")
+        return [int(self._h_out[r]) for r in range(rows)]
+
+    def _pack_host(self, token_ids, positions, block_tables, active_rows, temperatures):
+        rows = len(token_ids)
         if rows > self._max_rows:
-            raise RuntimeError(f"decode_host got {rows} rows; the decoder is sized for {self._max_rows}")
+            raise RuntimeError(f"got {rows} rows; the decoder is sized for {self._max_rows}")
         cols = max(len(t) for t in block_tables)
         if cols > self._max_pages:
             raise ValueError(
@@ -299,20 +308,43 @@ class StreamDecoder:
             base = r * cols
             for c in range(cols):
                 self._h_bt[base + c] = int(table[c]) if c < len(table) else 0
-        active = None
-        if active_rows is not None:
-            active = (C.c_int32 * rows)(*row_active_mask(active_rows, rows))
+        active = (C.c_int32 * rows)(*row_active_mask(active_rows, rows)) if active_rows is not None else None
         temps = None
         if temperatures is not None:
             if len(temperatures) != rows:
                 raise ValueError("one temperature per row")
             temps = (C.c_float * rows)(*[float(t) for t in temperatures])
-        code = self._lib.dfb_decode_step_host_sampled(self._handle, rows, self._h_ids, self._h_pos, self._h_bt, cols,
-                                                      active, temps, self._h_out, self._stream())
+        return rows, cols, active, temps
+
+    def burst_enqueue(self, token_ids, positions, block_tables, steps: int, active_rows=None,
+                      temperatures=None) -> None:
+        """Enqueue ``steps`` consecutive decode steps of the same rows (host lists as in
+        ``decode_host``; row r's step s runs at ``positions[r] + s`` and the block tables must already hold
+        the blocks up to ``positions[r] + steps - 1``).  Returns at once; the tokens feed back on the
+        device and are published step by step in pinned host memory (``burst_collect``)."""
+        rows, cols, active, temps = self._pack_host(token_ids, positions, block_tables, active_rows, temperatures)
+        self._burst = (rows, int(steps), (C.c_int32 * (rows * int(steps)))())
+        code = self._lib.dfb_decode_burst_enqueue(self._handle, rows, int(steps), self._h_ids, self._h_pos,
+                                                  self._h_bt, cols, active, temps, self._stream())
+        self._native.check(code, "dfb_decode_burst_enqueue")
+
+    def burst_collect(self, wait: bool = True) -> list[list[int]]:
+        """Tokens of the burst's finished steps, one list per step; ``wait=False`` returns what is there."""
+        rows, steps, buf = self._burst
+        done = C.c_int32(0)
+        code = self._lib.dfb_decode_burst_collect(self._handle, int(wait), buf, C.byref(done))
         if code == -4:
             self._raise_device_status()
-        self._native.check(code, "dfb_decode_step_host_sampled")
-        return [int(self._h_out[r]) for r in range(rows)]
+        self._native.check(code, "dfb_decode_burst_collect")
+        return [[int(buf[s * rows + r]) for r in range(rows)] for s in range(done.value)]
+
+    def decode_burst(self, token_ids, positions, block_tables, steps: int, active_rows=None,
+                     temperatures=None) -> list[list[int]]:
+        """``steps`` decode steps with one host-to-device copy and one synchronisation."""
+        if not token_ids:
+            return []
+        self.burst_enqueue(token_ids, positions, block_tables, steps, active_rows, temperatures)
+        return self.burst_collect(wait=True)
 
     def decode_row(self, token_id: int, position: int, block_table, temperature: float = 0.0) -> int:
         """Single-row path of ``ModelRunner`` (batch 1): takes the scheduler's

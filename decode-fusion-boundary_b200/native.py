@@ -20,6 +20,7 @@ HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persist
 
 DFB_ABI_VERSION = 2
 DFB_MAX_ROWS = 8
+DFB_MAX_BURST = 1024
 DFB_ATTN_CHUNK = 64
 DFB_TP_HANDLE_BYTES = 64
 DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
@@ -42,6 +43,7 @@ EXPORTS = (
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
     "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
+    "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host",
 )
 
 
@@ -132,6 +134,9 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
+    L.dfb_decode_burst_enqueue.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp]
+    L.dfb_decode_burst_collect.argtypes = [vp, i32, vp, vp]
+    L.dfb_decode_burst_host.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_launch_lmhead_sample.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp]
     L.dfb_read_status.argtypes = [vp, C.POINTER(DfbStatus)]
     L.dfb_read_trace.argtypes = [vp, vp, i32]

@@ -243,6 +243,32 @@ int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* inpu
                                  const int32_t* block_tables, int32_t cols, const int32_t* row_active,
                                  const float* temperatures, int32_t* out_tokens, dfb_stream_t stream);
 
+/* A burst: `steps` consecutive decode steps of the same rows enqueued at once, the whole loop resident on the
+ * device.  One host-to-device copy stages the inputs; after every step a one-warp kernel writes the step's
+ * tokens into a ring in pinned host memory (no copy node; the host may read finished steps while later ones
+ * run) and turns them into the next step's inputs on the device (ids = tokens, positions + 1).  Step s of row
+ * r runs at position positions[r] + s, so the block tables must already hold the blocks of positions[r] +
+ * steps - 1 (DFB_E_BAD_ARG otherwise); steps <= DFB_MAX_BURST.  Rows run on past an end-of-sequence token:
+ * the caller cuts the stream.  This is the step loop of LLMEngine.generate / ModelRunner.run
+ * (engine/llm_engine.py, engine/model_runner.py:264-284,315-376) without its per-step pinned tensor builds,
+ * small host-to-device copies and .tolist() synchronisation.
+ *   dfb_decode_burst_enqueue  returns once everything is enqueued on `stream` (no synchronisation);
+ *   dfb_decode_burst_collect  copies the tokens of the finished steps into out_tokens[steps_done][rows];
+ *                             wait = 1 blocks until the burst is complete, wait = 0 returns at once
+ *                             (steps_done < steps: call again).  The call that sees the last step ends the
+ *                             burst and returns DFB_E_DEVICE_STATUS if a kernel recorded an error;
+ *   dfb_decode_burst_host     = enqueue + collect(wait = 1).
+ * While a burst is in flight the decoder accepts no other step from host buffers. */
+#define DFB_MAX_BURST 1024
+int dfb_decode_burst_enqueue(DfbHandle* h, int32_t rows, int32_t steps, const int64_t* input_ids,
+                             const int64_t* positions, const int32_t* block_tables, int32_t cols,
+                             const int32_t* row_active, const float* temperatures, dfb_stream_t stream);
+int dfb_decode_burst_collect(DfbHandle* h, int32_t wait, int32_t* out_tokens, int32_t* steps_done);
+int dfb_decode_burst_host(DfbHandle* h, int32_t rows, int32_t steps, const int64_t* input_ids,
+                          const int64_t* positions, const int32_t* block_tables, int32_t cols,
+                          const int32_t* row_active, const float* temperatures, int32_t* out_tokens,
+                          dfb_stream_t stream);
+
 /* Seed of the sampling noise (default 0) and restart of its stream.  A sampled row takes
  * argmax_i(logit_i / T - log E_i), E_i ~ Exp(1) clamped at 1e-10, which is the reference's
  * argmax(softmax(logits / T) / E) without the softmax pass.  E_i = -log(u_i), u_i = (top 23 bits of
