@@ -311,9 +311,12 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
     __syncwarp();
     int last = 0;
     if (lane == 0) {
-      __threadfence();
-      last = (atomicAdd(a.tickets + row * a.kv_heads + warp, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
-      __threadfence();
+      // acquire-release at GPU scope: publishes this warp's partial (ordered before it by the warp barrier
+      // above) and makes the other chunks' partials visible to the last arrival
+      unsigned int prev;
+      asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                   : "=r"(prev) : "l"(a.tickets + row * a.kv_heads + warp) : "memory");
+      last = prev == (unsigned)(nsplits - 1) ? 1 : 0;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {

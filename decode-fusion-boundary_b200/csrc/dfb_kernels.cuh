@@ -815,9 +815,13 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
   }
   __syncthreads();
   if (tid == 0) {
-    __threadfence();  // after the barrier: orders every thread's partial before the ticket
-    last_flag = (atomicAdd(a.tickets + row * a.kv_heads + kvh, 1u) == (unsigned)(nsplits - 1)) ? 1 : 0;
-    __threadfence();
+    // One acquire-release atomic at GPU scope instead of fence + atomic + fence: the release covers the whole
+    // CTA's partials (they happen before it through the barrier above), the acquire the other CTAs' partials
+    // that the last arrival reads below (through the barrier that follows).
+    unsigned int prev;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                 : "=r"(prev) : "l"(a.tickets + row * a.kv_heads + kvh) : "memory");
+    last_flag = prev == (unsigned)(nsplits - 1) ? 1 : 0;
     trace_max(a.trace, 6);
   }
   __syncthreads();

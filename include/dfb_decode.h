@@ -161,7 +161,8 @@ typedef struct DfbStatus {
 #define DFB_OPT_PERSIST_CTAS 6/* grid of the persistent kernel, 1..SM count (0 = SM count, the default) */
 /* Options 7-17 belong to the decoder they are set on (no process-wide state). */
 #define DFB_OPT_ROW_GEMV 7    /* largest batch (0..8) that runs the projections on the FP32 GEMV kernels in the
-                                 kernel chain; larger batches use the tensor-core kernels */
+                                 kernel chain; larger batches use the tensor-core kernels (default 1; 2 on a
+                                 tensor-parallel shard) */
 #define DFB_OPT_ATTN_WIDE 8   /* attention grids of at most this many CTAs run 256-thread CTAs
                                  instead of 128-thread ones (default 296 = two per SM) */
 #define DFB_OPT_SMEM_CARVEOUT 9      /* share (percent, -1 = driver's choice) of an SM's L1/shared memory that the
