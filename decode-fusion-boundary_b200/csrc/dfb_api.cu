@@ -82,6 +82,15 @@ struct ChainOptions {
   // counterparts (their longer post-dependency path: bulk copies of x, two issue loops, accumulator read).
   int tcgen05 = env_int("DFB_TCGEN05", 4);
   int carve_tc = 100;          // ... whose chain asks for all of an SM's L1/shared memory as shared memory
+  int attn_cluster = env_int("DFB_ATTN_CLUSTER", 148);  // attention grids of at most this many CTAs (and 2..16 chunks
+                               // per row) launch the chunks of one (row, KV head) as a thread-block cluster that
+                               // merges its partial results through distributed shared memory instead of global
+                               // memory and a ticket; 0 = never.  Larger grids lose more to the co-scheduling of
+                               // 16-CTA clusters than the merge saves (batch 8 / context 512: 1,009 against 709 us)
+  int attn_chunk128 = env_int("DFB_ATTN_CHUNK128", 0);    // attention grids that 128-position chunks bring to at most
+                               // this many CTAs use them (256 threads, twice the K/V per thread): one row needs no
+                               // split up to 128 tokens; 0 = always 64-position chunks.  Off: measured 2.5 % faster
+                               // only for contexts of 65..128 tokens, 2-5 % slower below and above
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -117,6 +126,20 @@ cudaError_t ensure_dynamic_smem(const void* fn, int bytes) {
   return e;
 }
 
+// Clusters of more than 8 CTAs need a one-time opt-in per device and function.
+cudaError_t ensure_large_clusters(const void* fn) {
+  static std::map<std::pair<int, const void*>, int> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(g_attr_mu);
+  auto key = std::make_pair(dev, fn);
+  if (done.count(key)) return cudaSuccess;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e == cudaSuccess) done[key] = 1;
+  return e;
+}
+
 struct Launcher {
   cudaStream_t stream;
   bool pdl;
@@ -143,7 +166,7 @@ struct Launcher {
   }
   template <typename Args>
   void launch(void (*kernel)(Args), dim3 grid, dim3 block, const Args& args, bool allow_pdl = true,
-              size_t smem = 0) {
+              size_t smem = 0, int cluster_x = 0) {
     if (err) return;
     prefer_carveout((const void*)kernel, carve);
     cudaLaunchConfig_t cfg = {};
@@ -151,11 +174,22 @@ struct Launcher {
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl && allow_pdl && !plain_next) {
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      ++n_attr;
+    }
+    if (cluster_x > 1) {   // the grid's x dimension is made of thread-block clusters of this many CTAs
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = (unsigned)cluster_x;
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = (pdl && allow_pdl && !plain_next) ? 1 : 0;
+    cfg.numAttrs = n_attr;
     plain_next = false;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) {
@@ -302,6 +336,7 @@ int sm_count_cached() {
 int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
 
 constexpr int kRingFlag = 256;   // bit of the split-bucket value that selects the streaming attention kernel
+constexpr int kChunk128Flag = 512;   // ... that selects 128-position chunks in the register-resident kernel
 
 // ---- kernel launch wrappers -------------------------------------------------
 // Launch one instantiation of the GEMV kernel; its dynamic shared memory (the
@@ -603,6 +638,7 @@ int tp_sum(Launcher& L, DfbHandle* h, bf16* buf, int rows) {
 int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, const int* positions, const int* bt,
                      int bt_stride, int bt_cols, const int* row_active, bf16* out, int rows, int nsplit_arg) {
   const bool ring = (nsplit_arg & kRingFlag) != 0;   // set by split_bucket for long contexts
+  const bool chunk128 = (nsplit_arg & kChunk128Flag) != 0;   // ... and for small grids
   const int nsplit = nsplit_arg & (kRingFlag - 1);
   const DfbModelDesc& m = h->m;
   AttnArgs a = {};
@@ -633,13 +669,33 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
     L.carve = chain_carve;
     return L.err;
   }
-  if (rows <= L.opt->row_max_rows) {
-    if (ctas <= L.opt->attn_wide_ctas) L.launch(paged_attention_kernel<256, 0>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
-    else L.launch(paged_attention_kernel<128, 0>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
-  } else if (ctas <= L.opt->attn_wide_ctas) {
-    L.launch(paged_attention_kernel<256, 1>, dim3(nsplit, m.kv_heads, rows), dim3(256), a);
+  // 2..16 chunks: the chunks of one (row, KV head) form a thread-block cluster and merge in shared memory
+  const int cluster = (nsplit >= 2 && nsplit <= kAttnClusterMax && ctas <= L.opt->attn_cluster) ? nsplit : 0;
+  const bool wide = ctas <= L.opt->attn_wide_ctas;
+  const dim3 grid(nsplit, m.kv_heads, rows);
+  auto go = [&](auto kernel, int threads) {
+    if (cluster > 8) {
+      cudaError_t e = ensure_large_clusters((const void*)kernel);
+      if (e != cudaSuccess) { L.err = (int)e; return; }
+    }
+    L.launch(kernel, grid, dim3(threads), a, true, 0, cluster);
+  };
+  if (chunk128) {
+    if (rows <= L.opt->row_max_rows) {
+      if (cluster) go(paged_attention_kernel<256, 0, true, 2 * kAttnChunk>, 256);
+      else go(paged_attention_kernel<256, 0, false, 2 * kAttnChunk>, 256);
+    } else {
+      if (cluster) go(paged_attention_kernel<256, 1, true, 2 * kAttnChunk>, 256);
+      else go(paged_attention_kernel<256, 1, false, 2 * kAttnChunk>, 256);
+    }
+  } else if (rows <= L.opt->row_max_rows) {
+    if (cluster) { if (wide) go(paged_attention_kernel<256, 0, true>, 256); else go(paged_attention_kernel<128, 0, true>, 128); }
+    else if (wide) go(paged_attention_kernel<256, 0, false>, 256);
+    else go(paged_attention_kernel<128, 0, false>, 128);
   } else {
-    L.launch(paged_attention_kernel<128, 1>, dim3(nsplit, m.kv_heads, rows), dim3(128), a);
+    if (cluster) { if (wide) go(paged_attention_kernel<256, 1, true>, 256); else go(paged_attention_kernel<128, 1, true>, 128); }
+    else if (wide) go(paged_attention_kernel<256, 1, false>, 256);
+    else go(paged_attention_kernel<128, 1, false>, 128);
   }
   return L.err;
 }
@@ -650,12 +706,17 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
 int split_bucket(const DfbHandle* h, int max_context, int rows) {
   if (max_context < 1) max_context = 1;
   if (max_context > h->m.max_model_len) max_context = h->m.max_model_len;
-  const int need = (max_context + kAttnChunk - 1) / kAttnChunk;
+  int need = (max_context + kAttnChunk - 1) / kAttnChunk;
+  const bool ring = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
+  // small grids: 128 positions per CTA halve the number of partial results (none up to 128 tokens)
+  const int need128 = (max_context + 2 * kAttnChunk - 1) / (2 * kAttnChunk);
+  const bool chunk128 = !ring && h->m.block_size % (2 * kAttnChunk) == 0 &&
+                        rows * h->m.kv_heads * need128 <= h->opt.attn_chunk128;
+  if (chunk128) need = need128;
   int b = 1;
   while (b < need) b <<= 1;
   if (b > kMaxSplits) b = kMaxSplits;
-  const bool ring = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
-  return b | (ring ? kRingFlag : 0);
+  return b | (ring ? kRingFlag : 0) | (chunk128 ? kChunk128Flag : 0);
 }
 
 // The whole step as one chain of 5 kernels per layer + the LM head.
@@ -1113,6 +1174,14 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_ATTN_RING:
       if (value < 0) return DFB_E_BAD_ARG;
       h->opt.attn_ring_min = value;
+      break;
+    case DFB_OPT_ATTN_CHUNK128:
+      if (value < 0) return DFB_E_BAD_ARG;
+      h->opt.attn_chunk128 = value;
+      break;
+    case DFB_OPT_ATTN_CLUSTER:
+      if (value < 0) return DFB_E_BAD_ARG;
+      h->opt.attn_cluster = value;
       break;
     case DFB_OPT_TCGEN05:
       if (value < 0 || value > 7) return DFB_E_BAD_ARG;

@@ -566,12 +566,42 @@ struct AttnArgs {
 
 // CHAIN only separates instantiations: a function's preferred shared-memory split is
 // a property of the function, and the two kernel chains prefer different ones.
-template <int THREADS, int CHAIN>
+// Thread-block cluster helpers for the cluster variant of the attention kernel: the CTAs of one (row, KV head)
+// form a cluster along x and merge their partial results through distributed shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(const float* local, unsigned cta_rank) {
+  unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_dsmem_f32x2(const float2* local, unsigned cta_rank) {
+  unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
+  float2 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(ra) : "memory");
+  return v;
+}
+constexpr int kAttnClusterMax = 16;   // chunks of one (row, KV head) that one cluster can merge
+
+// CLUSTER: the grid's x dimension is one thread-block cluster (2..16 CTAs, launched with that cluster
+// dimension).  The chunks' partial results then stay in shared memory: one cluster barrier, CTA 0 reads its
+// peers' partials through distributed shared memory and writes the row, a second barrier keeps the peers'
+// shared memory alive until it has.  No global partials, no fence, no ticket.  Every CTA of a cluster whose
+// row has more than one chunk passes both barriers, also those without a chunk; a row with a single chunk
+// uses neither (all CTAs of a cluster see the same row, hence the same count).
+// CHUNK: positions per CTA, 64 or (256 threads only) 128: short contexts of small batches then need no split at
+// all up to 128 tokens, and half as many partial results beyond.
+template <int THREADS, int CHAIN, bool CLUSTER = false, int CHUNK = kAttnChunk>
 __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs a) {
   constexpr int PG = THREADS / 16;           // position groups: 16 threads share one position
-  constexpr int ITER = kAttnChunk / PG;      // positions per thread
+  constexpr int ITER = CHUNK / PG;      // positions per thread
   constexpr int J = 2 * kHeadDim / THREADS;  // output elements per thread in the reduction and the merge
   static_assert(THREADS == 128 || THREADS == 256, "128 or 256 threads");
+  static_assert(CHUNK == kAttnChunk || (CHUNK == 2 * kAttnChunk && THREADS == 256), "64 positions, or 128 with 256 threads");
   if (!a.late_trigger) pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x;
@@ -589,20 +619,28 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x),
                       (int)(gridDim.x * gridDim.y * gridDim.z));
   int ctx = pos + 1;
-  int nsplits = (ctx + kAttnChunk - 1) / kAttnChunk;
+  int nsplits = (ctx + CHUNK - 1) / CHUNK;
   if (nsplits > (int)gridDim.x) {
     // The host sized the grid from a context bound smaller than this row's position: the chunk holding
     // the new token has no CTA.  Record it and attend to what the grid covers, so that the tickets
     // still balance and nothing is written outside the covered range.
     if (split == 0) report_status(a.status, kStatusBadGrid, kKernelAttention, row, pos);
     nsplits = (int)gridDim.x;
-    ctx = nsplits * kAttnChunk;
+    ctx = nsplits * CHUNK;
     pos = ctx - 1;
     write_ok = false;
   }
-  if (split >= nsplits) return;  // split 0 always stays and orders the grid after its predecessor
+  if (split >= nsplits) {  // split 0 always stays and orders the grid after its predecessor
+    if (CLUSTER && nsplits > 1) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
+    return;
+  }
 
   __shared__ float qs[2][kHeadDim];
+  __shared__ __align__(16) float cpo[CLUSTER ? 2 * kHeadDim : 4];   // cluster variant: this chunk's partial output
+  __shared__ float2 cml[2];                                         // ... and its (max, sum) per head
   __shared__ __align__(16) __nv_bfloat16 ks[kHeadDim];
   __shared__ __align__(16) __nv_bfloat16 vs[kHeadDim];
   __shared__ float mred[PG][2];
@@ -610,8 +648,8 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
   __shared__ __align__(16) float ored[PG / 2][2][kHeadDim];
   __shared__ int last_flag;
 
-  const int start = split * kAttnChunk;
-  const int end = min(ctx, start + kAttnChunk);
+  const int start = split * CHUNK;
+  const int end = min(ctx, start + CHUNK);
   const bool owner = split == nsplits - 1;  // the chunk holding the new token
   const int pg = tid >> 4, l16 = tid & 15;  // position group, 16-byte slice of the head
   int bt_col = start / a.block_size;
@@ -803,47 +841,66 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     return;
   }
 
-  // ---- several splits: publish the partial, the last CTA to arrive merges ----
+  // ---- several splits: publish the partial, one CTA merges ----
+  constexpr int MS = CLUSTER ? kAttnClusterMax : kMaxSplits;
   const size_t pidx = ((size_t)row * a.kv_heads + kvh) * kMaxSplits;
-  float* po = a.part_o + (pidx + split) * 2 * kHeadDim;
+  if (CLUSTER) {
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int idx = tid + j * THREADS;
-    po[idx] = O[j];
-    if ((idx & (kHeadDim - 1)) == 0)  // one thread per head publishes (max, sum)
-      a.part_ml[(pidx + split) * 2 + (idx >> 7)] = make_float2((idx >> 7) ? m1 : m0, L[j]);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    // One acquire-release atomic at GPU scope instead of fence + atomic + fence: the release covers the whole
-    // CTA's partials (they happen before it through the barrier above), the acquire the other CTAs' partials
-    // that the last arrival reads below (through the barrier that follows).
-    unsigned int prev;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
-                 : "=r"(prev) : "l"(a.tickets + row * a.kv_heads + kvh) : "memory");
-    last_flag = prev == (unsigned)(nsplits - 1) ? 1 : 0;
-    trace_max(a.trace, 6);
-  }
-  __syncthreads();
-  if (!last_flag) {
-    if (tid == 0) trace_max(a.trace, 2);
-    return;
+    for (int j = 0; j < J; ++j) {
+      const int idx = tid + j * THREADS;
+      cpo[idx] = O[j];
+      if ((idx & (kHeadDim - 1)) == 0) cml[idx >> 7] = make_float2((idx >> 7) ? m1 : m0, L[j]);
+    }
+    cluster_sync_all();   // every chunk's partial is in its CTA's shared memory
+    if (tid == 0) trace_max(a.trace, 6);
+    if (split != 0) {
+      cluster_sync_all(); // CTA 0 has read this CTA's partial
+      if (tid == 0) trace_max(a.trace, 2);
+      return;
+    }
+  } else {
+    float* po = a.part_o + (pidx + split) * 2 * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int idx = tid + j * THREADS;
+      po[idx] = O[j];
+      if ((idx & (kHeadDim - 1)) == 0)  // one thread per head publishes (max, sum)
+        a.part_ml[(pidx + split) * 2 + (idx >> 7)] = make_float2((idx >> 7) ? m1 : m0, L[j]);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      // One acquire-release atomic at GPU scope instead of fence + atomic + fence: the release covers the whole
+      // CTA's partials (they happen before it through the barrier above), the acquire the other CTAs' partials
+      // that the last arrival reads below (through the barrier that follows).
+      unsigned int prev;
+      asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                   : "=r"(prev) : "l"(a.tickets + row * a.kv_heads + kvh) : "memory");
+      last_flag = prev == (unsigned)(nsplits - 1) ? 1 : 0;
+      trace_max(a.trace, 6);
+    }
+    __syncthreads();
+    if (!last_flag) {
+      if (tid == 0) trace_max(a.trace, 2);
+      return;
+    }
   }
   // Every load of the merge is issued before anything is computed, so that the
-  // merge costs one trip to L2 whatever the number of splits.
-  float pv[J][kMaxSplits];
+  // merge costs one trip (to L2, or to the peers' shared memory) whatever the number of splits.
+  float pv[J][MS];
   const float* ps = a.part_o + pidx * 2 * kHeadDim;
 #pragma unroll
   for (int j = 0; j < J; ++j)
 #pragma unroll
-    for (int s = 0; s < kMaxSplits; ++s)
-      pv[j][s] = s < nsplits ? __ldcg(ps + (size_t)s * 2 * kHeadDim + tid + j * THREADS) : 0.f;
+    for (int s = 0; s < MS; ++s) {
+      if (CLUSTER) pv[j][s] = s < nsplits ? ld_dsmem_f32(&cpo[tid + j * THREADS], (unsigned)s) : 0.f;
+      else pv[j][s] = s < nsplits ? __ldcg(ps + (size_t)s * 2 * kHeadDim + tid + j * THREADS) : 0.f;
+    }
   // `ored` is free again (every thread passed two barriers after reading it).
-  float* msm = &ored[0][0][0];        // [2 * kMaxSplits] partial maxima, index 2 s + head
-  float* lsm = msm + 2 * kMaxSplits;  // [2 * kMaxSplits] weighted partial sums
-  float* wsm = lsm + 2 * kMaxSplits;  // [2 * kMaxSplits] weights
+  float* msm = &ored[0][0][0];        // [2 * MS] partial maxima, index 2 s + head
+  float* lsm = msm + 2 * kMaxSplits;  // [2 * MS] weighted partial sums
+  float* wsm = lsm + 2 * kMaxSplits;  // [2 * MS] weights
   if (tid < 2 * nsplits) {
-    const float2 ml = __ldcg(&a.part_ml[pidx * 2 + tid]);
+    const float2 ml = CLUSTER ? ld_dsmem_f32x2(&cml[tid & 1], (unsigned)(tid >> 1)) : __ldcg(&a.part_ml[pidx * 2 + tid]);
     msm[tid] = ml.x;
     lsm[tid] = ml.y;
   }
@@ -862,7 +919,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     const int idx = tid + j * THREADS, h = idx >> 7;
     float A = 0.f, S = 0.f;
 #pragma unroll
-    for (int s = 0; s < kMaxSplits; ++s) {
+    for (int s = 0; s < MS; ++s) {
       if (s < nsplits) {
         A += wsm[2 * s + h] * pv[j][s];
         S += lsm[2 * s + h];
@@ -870,7 +927,10 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
     }
     out[idx] = __float2bfloat16_rn(A / S);
   }
-  if (tid == 0) {
+  if (CLUSTER) {
+    cluster_sync_all();   // the peers may leave: their partials have been read (pv, msm, lsm are local copies)
+    if (tid == 0) trace_max(a.trace, 2);
+  } else if (tid == 0) {
     a.tickets[row * a.kv_heads + kvh] = 0u;
     trace_max(a.trace, 2);
   }

@@ -29,6 +29,8 @@ DFB_OPT_SMEM_CARVEOUT, DFB_OPT_SMEM_CARVEOUT_MMA, DFB_OPT_LATE_TRIGGER, DFB_OPT_
 DFB_OPT_BULK_X, DFB_OPT_TP_FUSED = 13, 14
 DFB_OPT_LOOK_AHEAD, DFB_OPT_LMHEAD_AHEAD_MB, DFB_OPT_PEER_WAIT_US, DFB_OPT_TCGEN05 = 15, 16, 17, 18
 DFB_OPT_ATTN_RING = 19
+DFB_OPT_ATTN_CLUSTER = 20
+DFB_OPT_ATTN_CHUNK128 = 21
 DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
 DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
 

@@ -193,6 +193,14 @@ typedef struct DfbStatus {
                                   kernel (one CTA per row and 64-position chunk for all KV heads, K/V through a
                                   shared-memory ring fed by bulk copies) instead of the register-resident one;
                                   0 = never (default 200) */
+#define DFB_OPT_ATTN_CLUSTER 20 /* register-resident attention kernel: grids of at most this many CTAs with 2..16
+                                  chunks per row launch the chunks of one (row, KV head) as a thread-block cluster
+                                  that merges its partial results through distributed shared memory (no global
+                                  partials, no ticket); 0 = never (default 148: one row up to context 1024) */
+#define DFB_OPT_ATTN_CHUNK128 21 /* register-resident attention kernel: when 128-position chunks bring the grid to at
+                                  most this many CTAs they replace the 64-position ones (no split up to 128
+                                  tokens, half as many partial results beyond); 0 = never (the default: it pays only
+                                  for contexts of 65..128 tokens) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

@@ -122,9 +122,10 @@ def test_rmsnorm_gateup_swiglu(small, rows):
     assert ok, d
 
 
-def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None, ring=None):
+def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None, ring=None, options=None):
     """Random KV history in a paged cache; one new token per row.  ``ring``: True forces the streaming
-    kernel (dfb_attnring.cuh) for every grid size, False the register-resident one, None the default rule."""
+    kernel (dfb_attnring.cuh) for every grid size, False the register-resident one, None the default rule.
+    ``options``: further ``{option name: value}`` of the decoder."""
     from dfb_b200 import native
     lw = w.layers[0]
     tables, nblocks = O.allocate_blocks(ctx_lens, g.block_size, perm)
@@ -140,6 +141,8 @@ def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None, ring
     dec = H.make_decoder(w, kv_gpu)
     if ring is not None:
         dec.set_option(native.DFB_OPT_ATTN_RING, 1 if ring else 0)
+    for name, value in (options or {}).items():
+        dec.set_option(getattr(native, name), value)
     out = torch.zeros(rows, g.q_size, dtype=BF, device="cuda")
     bt = H.padded_tables(tables, ctx_lens, g.block_size)
     pos32 = positions.to(torch.int32).cuda()
@@ -163,6 +166,30 @@ def test_paged_attention(small, ctx_lens, ring):
     d = (out.float() - want.float()).abs().max()
     assert float(d) <= 2.0 ** -6, float(d)          # |out| < 4
     assert torch.equal(kv_got, kv_want)            # new K/V rows written bit-exactly, nothing else touched
+
+
+# How the register-resident kernel splits a row and merges the chunks: 64-position chunks merged through global
+# partials and a ticket, the same merged inside a thread-block cluster (distributed shared memory), and both
+# with 128-position chunks.  The limits are raised so that every grid of the list takes the variant.
+ATTENTION_VARIANTS = {
+    "ticket": {"DFB_OPT_ATTN_CLUSTER": 0, "DFB_OPT_ATTN_CHUNK128": 0},
+    "cluster": {"DFB_OPT_ATTN_CLUSTER": 1 << 20, "DFB_OPT_ATTN_CHUNK128": 0},
+    "chunk128_ticket": {"DFB_OPT_ATTN_CLUSTER": 0, "DFB_OPT_ATTN_CHUNK128": 1 << 20},
+    "chunk128_cluster": {"DFB_OPT_ATTN_CLUSTER": 1 << 20, "DFB_OPT_ATTN_CHUNK128": 1 << 20},
+}
+
+
+@pytest.mark.parametrize("variant", sorted(ATTENTION_VARIANTS))
+@pytest.mark.parametrize("ctx_lens", [(65,), (128,), (129,), (1, 100), (64, 65, 300), (1000, 3, 513, 1024),
+                                      (255, 256, 257, 1, 2, 130, 700, 1024), (2048, 5)])
+def test_paged_attention_split_variants(small, ctx_lens, variant):
+    """Rows of one launch with different chunk counts (a cluster whose row has a single chunk passes no cluster
+    barrier; CTAs beyond a row's last chunk pass both), up to the largest cluster (16 chunks) and beyond it."""
+    g, w = small
+    out, want, kv_got, kv_want, _ = _attention_case(g, w, len(ctx_lens), list(ctx_lens), seed=61, ring=False,
+                                                    options=ATTENTION_VARIANTS[variant])
+    assert float((out.float() - want.float()).abs().max()) <= 2.0 ** -6
+    assert torch.equal(kv_got, kv_want)
 
 
 @pytest.mark.parametrize("ring", [False, True])
