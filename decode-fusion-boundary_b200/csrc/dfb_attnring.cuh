@@ -184,8 +184,8 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
       float y[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) y[e] = round_bf16(round_bf16(x[i][e] * rstd) * w[e]);
-      const uint32_t r_lo = pack_bf16(round_bf16(y[0] * rc.x - y[2] * rs.x), round_bf16(y[1] * rc.y - y[3] * rs.y));
-      const uint32_t r_hi = pack_bf16(round_bf16(y[2] * rc.x + y[0] * rs.x), round_bf16(y[3] * rc.y + y[1] * rs.y));
+      const uint32_t r_lo = pack_bf16(round_bf16(mul_sub_unfused(y[0], rc.x, y[2], rs.x)), round_bf16(mul_sub_unfused(y[1], rc.y, y[3], rs.y)));
+      const uint32_t r_hi = pack_bf16(round_bf16(mul_add_unfused(y[2], rc.x, y[0], rs.x)), round_bf16(mul_add_unfused(y[3], rc.y, y[1], rs.y)));
       __nv_bfloat16* dst = i < 2 ? qsm[warp][i] : knew[warp];
       *reinterpret_cast<uint32_t*>(dst + d) = r_lo;
       *reinterpret_cast<uint32_t*>(dst + d + 64) = r_hi;

@@ -114,6 +114,15 @@ __device__ __forceinline__ uint4 ldg_cg(const void* p) {
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+// a * b - c * d and a * b + c * d with every product and the sum rounded to fp32 on its own, as the elementwise
+// torch expressions of the reference's rotary embedding do (layers/rotary_embedding.py:6-16); a fused
+// multiply-add here moves results near zero by one bf16 step
+__device__ __forceinline__ float mul_sub_unfused(float a, float b, float c, float d) {
+  return __fsub_rn(__fmul_rn(a, b), __fmul_rn(c, d));
+}
+__device__ __forceinline__ float mul_add_unfused(float a, float b, float c, float d) {
+  return __fadd_rn(__fmul_rn(a, b), __fmul_rn(c, d));
+}
 
 // ---------------------------------------------------------------------------
 // Sampling fused after the LM head (layers/sampler.py:7-16 of the reference:
@@ -717,8 +726,8 @@ __global__ void __launch_bounds__(THREADS) paged_attention_kernel(const AttnArgs
 #pragma unroll
       for (int e = 0; e < 4; ++e) x[e] = round_bf16(round_bf16(x[e] * rstd) * w[e]);
       const float2 c = rc, s = rs;
-      const float y0 = round_bf16(x[0] * c.x - x[2] * s.x), y1 = round_bf16(x[1] * c.y - x[3] * s.y);
-      const float y2 = round_bf16(x[2] * c.x + x[0] * s.x), y3 = round_bf16(x[3] * c.y + x[1] * s.y);
+      const float y0 = round_bf16(mul_sub_unfused(x[0], c.x, x[2], s.x)), y1 = round_bf16(mul_sub_unfused(x[1], c.y, x[3], s.y));
+      const float y2 = round_bf16(mul_add_unfused(x[2], c.x, x[0], s.x)), y3 = round_bf16(mul_add_unfused(x[3], c.y, x[1], s.y));
       if (warp < 2) {
         qs[warp][d] = y0; qs[warp][d + 1] = y1; qs[warp][d + 64] = y2; qs[warp][d + 65] = y3;
       } else {

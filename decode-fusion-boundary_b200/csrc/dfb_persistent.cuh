@@ -233,8 +233,8 @@ __device__ __forceinline__ void p_attention_item(const PersistArgs& a, PAttnSmem
     const float w[4] = {bf_lo(wlo), bf_hi(wlo), bf_lo(whi), bf_hi(whi)};
 #pragma unroll
     for (int e = 0; e < 4; ++e) x[e] = round_bf16(round_bf16(x[e] * rstd) * w[e]);
-    const float y0 = round_bf16(x[0] * c.x - x[2] * s.x), y1 = round_bf16(x[1] * c.y - x[3] * s.y);
-    const float y2 = round_bf16(x[2] * c.x + x[0] * s.x), y3 = round_bf16(x[3] * c.y + x[1] * s.y);
+    const float y0 = round_bf16(mul_sub_unfused(x[0], c.x, x[2], s.x)), y1 = round_bf16(mul_sub_unfused(x[1], c.y, x[3], s.y));
+    const float y2 = round_bf16(mul_add_unfused(x[2], c.x, x[0], s.x)), y3 = round_bf16(mul_add_unfused(x[3], c.y, x[1], s.y));
     if (warp < 2) {
       sm.qs[warp][d] = y0; sm.qs[warp][d + 1] = y1; sm.qs[warp][d + 64] = y2; sm.qs[warp][d + 65] = y3;
     } else {
