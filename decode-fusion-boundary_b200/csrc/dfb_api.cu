@@ -87,10 +87,11 @@ struct ChainOptions {
                                // merges its partial results through distributed shared memory instead of global
                                // memory and a ticket; 0 = never.  Larger grids lose more to the co-scheduling of
                                // 16-CTA clusters than the merge saves (batch 8 / context 512: 1,009 against 709 us)
-  int attn_chunk128 = env_int("DFB_ATTN_CHUNK128", 0);    // attention grids that 128-position chunks bring to at most
-                               // this many CTAs use them (256 threads, twice the K/V per thread): one row needs no
-                               // split up to 128 tokens; 0 = always 64-position chunks.  Off: measured 2.5 % faster
-                               // only for contexts of 65..128 tokens, 2-5 % slower below and above
+  int attn_chunk128 = env_int("DFB_ATTN_CHUNK128", 1);    // 1: context bounds of 65..128 tokens run ONE 128-position chunk
+                               // per row and KV head (256 threads, twice the K/V per thread) instead of two merged
+                               // 64-position chunks (batch 1: 461 against 474 us per step); N > 1: also every grid
+                               // that 128-position chunks bring to at most N CTAs (measured 2-5 % slower than
+                               // 64-position chunks with a cluster merge); 0: never
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -710,8 +711,8 @@ int split_bucket(const DfbHandle* h, int max_context, int rows) {
   const bool ring = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
   // small grids: 128 positions per CTA halve the number of partial results (none up to 128 tokens)
   const int need128 = (max_context + 2 * kAttnChunk - 1) / (2 * kAttnChunk);
-  const bool chunk128 = !ring && h->m.block_size % (2 * kAttnChunk) == 0 &&
-                        rows * h->m.kv_heads * need128 <= h->opt.attn_chunk128;
+  const bool chunk128 = !ring && h->m.block_size % (2 * kAttnChunk) == 0 && h->opt.attn_chunk128 > 0 &&
+                        ((need128 == 1 && need == 2) || rows * h->m.kv_heads * need128 <= h->opt.attn_chunk128);
   if (chunk128) need = need128;
   int b = 1;
   while (b < need) b <<= 1;

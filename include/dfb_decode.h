@@ -197,10 +197,11 @@ typedef struct DfbStatus {
                                   chunks per row launch the chunks of one (row, KV head) as a thread-block cluster
                                   that merges its partial results through distributed shared memory (no global
                                   partials, no ticket); 0 = never (default 148: one row up to context 1024) */
-#define DFB_OPT_ATTN_CHUNK128 21 /* register-resident attention kernel: when 128-position chunks bring the grid to at
-                                  most this many CTAs they replace the 64-position ones (no split up to 128
-                                  tokens, half as many partial results beyond); 0 = never (the default: it pays only
-                                  for contexts of 65..128 tokens) */
+#define DFB_OPT_ATTN_CHUNK128 21 /* register-resident attention kernel: 1 (default) = a step whose context bound is
+                                  65..128 tokens runs one 128-position chunk per row and KV head instead of two
+                                  merged 64-position chunks; N > 1 = also every grid that 128-position chunks
+                                  bring to at most N CTAs; 0 = never.  Rows of launches with different bounds may
+                                  then differ in the last bit of the attention output (another summation order) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

@@ -143,7 +143,8 @@ def test_batch_equals_independent_rows(cuda_device, persistent):
     tests/test_taskgraph_bs2.py:235-248).  One- and two-row batches are
     multiplied on the FP32 pipe and larger ones on the tensor cores (another
     summation order), so a 3-row launch agrees with single-row launches to bf16
-    rounding; with the FP32 kernels switched off the arithmetic is the same for
+    rounding; with the FP32 kernels and the 128-position attention chunks (chosen
+    by the launch's longest row) switched off the arithmetic is the same for
     every batch size and the agreement is bit for bit."""
     from dfb_b200 import native
     lens = [40, 300, 7]
@@ -154,6 +155,7 @@ def test_batch_equals_independent_rows(cuda_device, persistent):
     if exact:
         for dec in (dec_a, dec_b):                      # options belong to the decoder they are set on
             dec.set_option(native.DFB_OPT_ROW_GEMV, 0)
+            dec.set_option(native.DFB_OPT_ATTN_CHUNK128, 0)
     la = torch.zeros(3, g.vocab, device="cuda")
     lb = torch.zeros(1, g.vocab, device="cuda")
     cur = list(first)
@@ -221,8 +223,9 @@ def test_bad_block_id_is_reported_not_followed(cuda_device):
 
 
 def test_options_are_per_decoder(cuda_device):
-    """An option set on one decoder leaves another decoder of the same process alone: with the FP32 kernels
-    switched off on A only, a two-row step of B still equals a fresh decoder's."""
+    """An option set on one decoder leaves another decoder of the same process alone: with other kernels
+    chosen on A only (8 instead of 16 weight rows per MMA, no tcgen05, no FP32 kernels), a two-row step of B
+    still equals a fresh decoder's."""
     from dfb_b200 import native
     lens = [40, 300]
     g, w, kv, tables, first = _setup(lens, seed=24)
@@ -231,6 +234,8 @@ def test_options_are_per_decoder(cuda_device):
         other = H.make_decoder(w, kv.cuda())
         if touch_other:
             other.set_option(native.DFB_OPT_ROW_GEMV, 0)
+            other.set_option(native.DFB_OPT_PAIR_GEMV, 0)
+            other.set_option(native.DFB_OPT_TCGEN05, 0)
             other.set_option(native.DFB_OPT_LOOK_AHEAD, 0)
         dec = H.make_decoder(w, kv.cuda())
         logits = torch.zeros(2, g.vocab, device="cuda")
