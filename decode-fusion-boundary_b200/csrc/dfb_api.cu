@@ -1039,6 +1039,8 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
 
 void dfb_destroy(DfbHandle* h) {
   if (!h) return;
+  // a burst in flight still writes the pinned token ring: let it finish before anything is freed
+  if (h->burst_steps && h->burst_event) cudaEventSynchronize(h->burst_event);
   for (auto& kv : h->graphs) { cudaGraphExecDestroy(kv.second.exec); cudaGraphDestroy(kv.second.graph); }
   if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   for (int r = 0; r < kMaxRanks; ++r) {

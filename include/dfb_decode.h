@@ -286,7 +286,8 @@ int dfb_decode_burst_host(DfbHandle* h, int32_t rows, int32_t steps, const int64
  * c = ((n * 8 + row) << 32) | i, n = the number of sampled LM-head launches of this decoder since the seed was
  * set (greedy steps do not advance it), i = the token's index in the whole vocabulary: the draw is a
  * function of (seed, n, row, i) alone, identical on every tensor-parallel rank and reproducible on the host.
- * torch's own generator stream is not reproduced: parity with the reference's sampler is in distribution. */
+ * torch's own generator stream is not reproduced: parity with the reference's sampler is in distribution.
+ * Call it between steps (it synchronises nothing): a step in flight may see either stream position. */
 int dfb_set_seed(DfbHandle* h, uint64_t seed);
 
 /* Read (and clear) the device status word; synchronises nothing by itself, so
