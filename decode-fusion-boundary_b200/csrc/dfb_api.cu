@@ -92,6 +92,12 @@ struct ChainOptions {
                                // 64-position chunks (batch 1: 461 against 474 us per step); N > 1: also every grid
                                // that 128-position chunks bring to at most N CTAs (measured 2-5 % slower than
                                // 64-position chunks with a cluster merge); 0: never
+  int attn_ring32_min = env_int("DFB_ATTN_RING32", 0);   // steps with context bound <= 1024 whose rows x 32-position
+                               // chunks reach this value (and that the rule below does not take) run the streaming
+                               // kernel with 32 positions per CTA; 0 = never.  Off: the streaming kernel's fixed
+                               // cost per CTA (q/k norm and rotation for all eight heads, ring start-up) loses to
+                               // the register-resident kernel at these sizes (batch 8 / context 512: 811 against
+                               // 709 us per step, batch 4: 769 against 636)
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -337,6 +343,7 @@ int sm_count_cached() {
 int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
 
 constexpr int kRingFlag = 256;   // bit of the split-bucket value that selects the streaming attention kernel
+constexpr int kRing32Flag = 1024;    // ... with kRingFlag: the streaming kernel with 32 positions per CTA
 constexpr int kChunk128Flag = 512;   // ... that selects 128-position chunks in the register-resident kernel
 
 // ---- kernel launch wrappers -------------------------------------------------
@@ -662,11 +669,13 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
   a.late_trigger = L.opt->late_trigger;
   if (ring && m.kv_heads == kRingHeads) {
     // long contexts / full batches: one CTA per (row, chunk) for all KV heads, K/V streamed through shared memory
-    cudaError_t e = ensure_dynamic_smem((const void*)paged_attention_ring_kernel, kRingSmemBytes);
+    const bool ring32 = (nsplit_arg & kRing32Flag) != 0;
+    auto kernel = ring32 ? paged_attention_ring_kernel<kAttnChunk / 2> : paged_attention_ring_kernel<kAttnChunk>;
+    cudaError_t e = ensure_dynamic_smem((const void*)kernel, kRingSmemBytes);
     if (e != cudaSuccess) { L.err = (int)e; return L.err; }
     const int chain_carve = L.carve;
     L.carve = 100;   // two CTAs of about 104 KB per SM
-    L.launch(paged_attention_ring_kernel, dim3(nsplit, rows), dim3(kRingThreads), a, true, kRingSmemBytes);
+    L.launch(kernel, dim3(nsplit, rows), dim3(kRingThreads), a, true, kRingSmemBytes);
     L.carve = chain_carve;
     return L.err;
   }
@@ -708,7 +717,13 @@ int split_bucket(const DfbHandle* h, int max_context, int rows) {
   if (max_context < 1) max_context = 1;
   if (max_context > h->m.max_model_len) max_context = h->m.max_model_len;
   int need = (max_context + kAttnChunk - 1) / kAttnChunk;
-  const bool ring = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
+  const bool ring64 = h->m.kv_heads == kRingHeads && h->opt.attn_ring_min > 0 && rows * need >= h->opt.attn_ring_min;
+  // mid-size steps: the streaming kernel with 32 positions per CTA (its partial results fit the 32 slots up to 1024 tokens)
+  const int need32 = (max_context + kAttnChunk / 2 - 1) / (kAttnChunk / 2);
+  const bool ring32 = !ring64 && h->m.kv_heads == kRingHeads && h->opt.attn_ring32_min > 0 && need32 <= kMaxSplits &&
+                      h->m.block_size % (kAttnChunk / 2) == 0 && rows * need32 >= h->opt.attn_ring32_min;
+  const bool ring = ring64 || ring32;
+  if (ring32) need = need32;
   // small grids: 128 positions per CTA halve the number of partial results (none up to 128 tokens)
   const int need128 = (max_context + 2 * kAttnChunk - 1) / (2 * kAttnChunk);
   const bool chunk128 = !ring && h->m.block_size % (2 * kAttnChunk) == 0 && h->opt.attn_chunk128 > 0 &&
@@ -717,7 +732,7 @@ int split_bucket(const DfbHandle* h, int max_context, int rows) {
   int b = 1;
   while (b < need) b <<= 1;
   if (b > kMaxSplits) b = kMaxSplits;
-  return b | (ring ? kRingFlag : 0) | (chunk128 ? kChunk128Flag : 0);
+  return b | (ring ? kRingFlag : 0) | (ring32 ? kRing32Flag : 0) | (chunk128 ? kChunk128Flag : 0);
 }
 
 // The whole step as one chain of 5 kernels per layer + the LM head.
@@ -866,7 +881,7 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
   if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
   // one graph per (rows, split bucket, filled block-table columns, kind of inputs / outputs)
   const int io_kind = (io.burst ? 0 : io.host ? 3 : (io.out_tokens ? 2 : 1)) + (io.sampling ? 4 : 0);
-  const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 1024 + nsplit) * 2 +
+  const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 4096 + nsplit) * 2 +
                          (h->use_pdl ? 1 : 0)) * 8 + io_kind;
   auto it = h->graphs.find(key);
   if (it == h->graphs.end()) {
@@ -1177,6 +1192,10 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_ATTN_RING:
       if (value < 0) return DFB_E_BAD_ARG;
       h->opt.attn_ring_min = value;
+      break;
+    case DFB_OPT_ATTN_RING32:
+      if (value < 0) return DFB_E_BAD_ARG;
+      h->opt.attn_ring32_min = value;
       break;
     case DFB_OPT_ATTN_CHUNK128:
       if (value < 0) return DFB_E_BAD_ARG;

@@ -70,7 +70,11 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// CH: context positions per CTA, 64 or 32 (half as many stages per CTA and twice the CTAs: mid-size grids then
+// cover every SM, and three of a CTA's four stages are in flight before the dependency resolves).
+template <int CH>
 __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(const AttnArgs a) {
+  static_assert(CH == kAttnChunk || 2 * CH == kAttnChunk, "64 or 32 positions per CTA");
   if (!a.late_trigger) pdl_launch_dependents();
   const int split = blockIdx.x, row = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -83,11 +87,11 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
     write_ok = false;
   }
   int ctx = pos + 1;
-  int nsplits = (ctx + kAttnChunk - 1) / kAttnChunk;
+  int nsplits = (ctx + CH - 1) / CH;
   if (nsplits > (int)gridDim.x) {   // the host's context bound was too small (see paged_attention_kernel)
     if (split == 0) report_status(a.status, kStatusBadGrid, kKernelAttention, row, pos);
     nsplits = (int)gridDim.x;
-    ctx = nsplits * kAttnChunk;
+    ctx = nsplits * CH;
     pos = ctx - 1;
     write_ok = false;
   }
@@ -100,8 +104,8 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
   __shared__ __align__(16) __nv_bfloat16 knew[kRingHeads][kHeadDim];
   __shared__ __align__(16) __nv_bfloat16 vnew[kRingHeads][kHeadDim];
 
-  const int start = split * kAttnChunk;
-  const int end = min(ctx, start + kAttnChunk);
+  const int start = split * CH;
+  const int end = min(ctx, start + CH);
   const bool owner = split == nsplits - 1;
   const int nsub = (end - start + kRingPos - 1) / kRingPos;
   int bt_col = start / a.block_size;

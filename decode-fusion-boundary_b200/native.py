@@ -31,6 +31,7 @@ DFB_OPT_LOOK_AHEAD, DFB_OPT_LMHEAD_AHEAD_MB, DFB_OPT_PEER_WAIT_US, DFB_OPT_TCGEN
 DFB_OPT_ATTN_RING = 19
 DFB_OPT_ATTN_CLUSTER = 20
 DFB_OPT_ATTN_CHUNK128 = 21
+DFB_OPT_ATTN_RING32 = 22
 DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
 DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
 

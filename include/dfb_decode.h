@@ -202,6 +202,9 @@ typedef struct DfbStatus {
                                   merged 64-position chunks; N > 1 = also every grid that 128-position chunks
                                   bring to at most N CTAs; 0 = never.  Rows of launches with different bounds may
                                   then differ in the last bit of the attention output (another summation order) */
+#define DFB_OPT_ATTN_RING32 22  /* steps with a context bound of at most 1024 tokens whose rows x ceil(bound / 32) reach
+                                  this value, and that DFB_OPT_ATTN_RING does not take, run the streaming attention
+                                  kernel with 32 positions per CTA; 0 = never (the default: measured slower) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

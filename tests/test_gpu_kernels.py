@@ -141,6 +141,7 @@ def _attention_case(g, w, rows, ctx_lens, seed, perm=None, row_active=None, ring
     dec = H.make_decoder(w, kv_gpu)
     if ring is not None:
         dec.set_option(native.DFB_OPT_ATTN_RING, 1 if ring else 0)
+        dec.set_option(native.DFB_OPT_ATTN_RING32, 0)
     for name, value in (options or {}).items():
         dec.set_option(getattr(native, name), value)
     out = torch.zeros(rows, g.q_size, dtype=BF, device="cuda")
@@ -176,6 +177,8 @@ ATTENTION_VARIANTS = {
     "cluster": {"DFB_OPT_ATTN_CLUSTER": 1 << 20, "DFB_OPT_ATTN_CHUNK128": 0},
     "chunk128_ticket": {"DFB_OPT_ATTN_CLUSTER": 0, "DFB_OPT_ATTN_CHUNK128": 1 << 20},
     "chunk128_cluster": {"DFB_OPT_ATTN_CLUSTER": 1 << 20, "DFB_OPT_ATTN_CHUNK128": 1 << 20},
+    # the streaming kernel with 32 positions per CTA for every bound up to 1024 tokens
+    "ring32": {"DFB_OPT_ATTN_RING32": 1},
 }
 
 
