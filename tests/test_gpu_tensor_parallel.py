@@ -56,3 +56,19 @@ def test_tensor_parallel_matches_unsharded_oracle(world, use_graph, transport, t
         assert rep["max_abs_kv_diff"] <= 2.0 ** -4, rep
         if not use_graph:
             assert rep["max_abs_logit_diff"] <= 2 * H.LOGIT_ATOL, rep
+
+
+def test_tensor_parallel_burst_and_sampling(tmp_path):
+    """Two ranks: a sampled burst publishes the same tokens on every rank and equals the same steps one by one."""
+    if 2 not in _world_sizes():
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from tests.tp_worker import tp_burst_worker
+
+    mp.spawn(tp_burst_worker, args=(2, _free_port(), str(tmp_path), 2, 8192, 6), nprocs=2, join=True)
+    for r in range(2):
+        rep = json.loads((tmp_path / f"rank{r}.json").read_text())
+        assert rep["status"] == [0, 0], rep
+        assert rep["ranks_agree"], rep
+        assert rep["burst_equals_steps"], rep
+        assert rep["kv_equal"], rep

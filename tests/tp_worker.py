@@ -90,3 +90,65 @@ def tp_parity_worker(rank: int, world: int, port: int, out_dir: str, layers: int
     dist.barrier()
     group.close()
     dist.destroy_process_group()
+
+
+def tp_burst_worker(rank: int, world: int, port: int, out_dir: str, layers: int, vocab: int, steps: int):
+    """Bursts and the fused sampler on a sharded decoder: every rank must publish the same tokens (the sampling
+    noise is a function of the global vocabulary index, the shards' winners are merged by key), and a burst must
+    equal the same steps issued one by one."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from tests import harness as H
+    from tests.harness import O
+    from dfb_b200.decoder import StreamDecoder
+    from dfb_b200.tensor_parallel import TensorParallelGroup, shard_weights
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    group = TensorParallelGroup.create(dist, rank, transport="direct")
+    g = H.oracle_geometry(layers=layers, vocab=vocab)
+    w = O.make_weights(g, seed=8, norm="random").to(torch.bfloat16)
+    lens = [5, 70, 250]
+    rows = len(lens)
+    tables, nblocks = O.allocate_blocks([n + 2 * steps + 2 for n in lens], g.block_size)
+    history = torch.from_numpy(np.random.Generator(np.random.Philox(key=81)).standard_normal(
+        tuple(O.new_kv_cache(g, nblocks, torch.bfloat16).shape), dtype=np.float32) * 0.5).to(torch.bfloat16)
+    local = shard_weights(H.to_decoder_weights(w), rank, world)
+    lg = local.geom
+    h0, h1 = rank * lg.kv_heads, (rank + 1) * lg.kv_heads
+    temps = [0.0, 0.8, 1.3]
+    first = [11, 22, 33]
+    results = {}
+    for mode in ("steps", "burst"):
+        kv_gpu = history[:, :, :, :, h0:h1, :].contiguous().cuda()
+        dec = StreamDecoder(local, kv_gpu[0], kv_gpu[1], block_size=g.block_size, num_cache_blocks=nblocks,
+                            max_model_len=g.max_pos, tensor_parallel=group)
+        dec.set_seed(4242)
+        dist.barrier()
+        if mode == "steps":
+            out, ids = [], first
+            for s in range(steps):
+                ids = dec.decode_host(ids, [n + s for n in lens], tables, temperatures=temps)
+                out.append(list(ids))
+        else:
+            out = dec.decode_burst(first, lens, tables, steps, temperatures=temps)
+        code, st = dec.status()
+        results[mode] = dict(tokens=out, status=int(st.device_status), kv=kv_gpu.cpu())
+        dec.close()
+        torch.cuda.synchronize()
+        dist.barrier()
+    toks = [None] * world
+    dist.all_gather_object(toks, results["burst"]["tokens"])
+    report = dict(rank=rank, ranks_agree=all(t == toks[0] for t in toks),
+                  burst_equals_steps=results["burst"]["tokens"] == results["steps"]["tokens"],
+                  kv_equal=bool(torch.equal(results["burst"]["kv"], results["steps"]["kv"])),
+                  status=[results["steps"]["status"], results["burst"]["status"]],
+                  sampled_rows_moved=any(a[1:] != b[1:] for a, b in zip(results["burst"]["tokens"][:-1],
+                                                                        results["burst"]["tokens"][1:])),
+                  tokens=results["burst"]["tokens"])
+    Path(out_dir, f"rank{rank}.json").write_text(json.dumps(report))
+    group.close()
+    dist.destroy_process_group()
