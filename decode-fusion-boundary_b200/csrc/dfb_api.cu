@@ -98,6 +98,14 @@ struct ChainOptions {
                                // cost per CTA (q/k norm and rotation for all eight heads, ring start-up) loses to
                                // the register-resident kernel at these sizes (batch 8 / context 512: 811 against
                                // 709 us per step, batch 4: 769 against 636)
+  int reg_weights = env_int("DFB_REG_WEIGHTS", 0);   // batches above row_max_rows, a bit mask: 1 = QKV and gate/up,
+                               // 2 = o_proj and down_proj, 4 = LM head keep their weights in registers (loaded straight
+                               // from global memory in MMA fragment order, pair_gemv_kernel<0, ...> and
+                               // reg_store_gemv_kernel) instead of shared-memory stages, so that a kernel's CTAs fit
+                               // beside its predecessor's; 8 = those kernels launch up to two CTAs per SM.  Off:
+                               // measured slower at every batch (batch 8 / context 512: 758 us with bit 1, 719 with
+                               // bit 2, 786 with both, against 709): at 2-8 rows a successor that streams its
+                               // weights beside the running kernel takes bandwidth from that kernel's own stream
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -341,6 +349,11 @@ int sm_count_cached() {
   return count[dev];
 }
 int grid_for(int n_tiles) { const int sms = sm_count_cached(); return n_tiles < sms ? n_tiles : sms; }
+// grid of the kernels that keep their weights in registers: one CTA per SM, or (option bit 8) up to two
+int reg_grid(const Launcher& L, int n_tiles) {
+  const int cap = ((L.opt->reg_weights & 8) ? 2 : 1) * sm_count_cached();
+  return n_tiles < cap ? n_tiles : cap;
+}
 
 constexpr int kRingFlag = 256;   // bit of the split-bucket value that selects the streaming attention kernel
 constexpr int kRing32Flag = 1024;    // ... with kRingFlag: the streaming kernel with 32 positions per CTA
@@ -491,7 +504,8 @@ int launch_norm_qkv(Launcher& L, const bf16* x, const int* ids, const bf16* res_
   if (L.opt->pair_gemv && n % 16 == 0) {
     a.n_tiles = n / 16;
     tp_fill(L, L.tp, a, false);
-    launch_pair<2, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
+    if (L.opt->reg_weights & 1) launch_pair<0, kModeNormStore>(L, a, reg_grid(L, a.n_tiles), allow_pdl);
+    else launch_pair<2, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
     return L.err;
   }
   launch_gemv<4, 8, 4, kModeNormStore>(L, a, grid_for(a.n_tiles), allow_pdl);
@@ -525,6 +539,14 @@ int launch_linear(Launcher& L, const bf16* x, const bf16* w, bf16* out, int rows
     }
     return L.err;
   }
+  if ((L.opt->reg_weights & 2) && (k == 2048 || k == 3072)) {
+    a.trace = L.next_trace();
+    L.fill_common(a);
+    const int grid = reg_grid(L, a.n_tiles);
+    if (k == 2048) L.launch(reg_store_gemv_kernel<2048>, dim3(grid), dim3(256), a);
+    else L.launch(reg_store_gemv_kernel<3072>, dim3(grid), dim3(384), a);
+    return L.err;
+  }
   const int grid = grid_for(a.n_tiles);
   switch (mma_loads) {
     case 4: launch_gemv<4, 8, 4, kModeStore>(L, a, grid); break;
@@ -556,7 +578,8 @@ int launch_gateup(Launcher& L, const bf16* h, const bf16* res_in, bf16* res_out,
   if (L.opt->pair_gemv && inter % 8 == 0) {
     a.n_tiles = inter / 8;
     tp_fill(L, L.tp, a, false);
-    launch_pair<3, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
+    if (L.opt->reg_weights & 1) launch_pair<0, kModeNormSwiglu>(L, a, reg_grid(L, a.n_tiles));
+    else launch_pair<3, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
     return L.err;
   }
   launch_gemv<4, 8, 6, kModeNormSwiglu>(L, a, grid_for(a.n_tiles));
@@ -594,7 +617,8 @@ int launch_lmhead(Launcher& L, DfbHandle* h, const bf16* hid, const bf16* res_in
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : 2 * h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
     tp_fill(L, L.tp, a, false);
-    launch_pair<2, kModeNormArgmax>(L, a, grid, true, 100);
+    if (L.opt->reg_weights & 4) launch_pair<0, kModeNormArgmax>(L, a, grid, true);
+    else launch_pair<2, kModeNormArgmax>(L, a, grid, true, 100);
   } else {
     int grid = h->lmhead_ctas > 0 ? h->lmhead_ctas : h->sm_count;
     if (grid > a.n_tiles) grid = a.n_tiles;
@@ -1192,6 +1216,10 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_ATTN_RING:
       if (value < 0) return DFB_E_BAD_ARG;
       h->opt.attn_ring_min = value;
+      break;
+    case DFB_OPT_REG_WEIGHTS:
+      if (value < 0 || value > 15) return DFB_E_BAD_ARG;
+      h->opt.reg_weights = value;
       break;
     case DFB_OPT_ATTN_RING32:
       if (value < 0) return DFB_E_BAD_ARG;

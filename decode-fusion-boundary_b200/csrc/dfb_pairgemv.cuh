@@ -23,7 +23,15 @@
 //     reduction and eight roots per thread made this prologue the longest part
 //     of the kernel after its dependency);
 //   * cross-warp reduction in shared memory, one thread per output for the
-//     epilogue (store / SwiGLU / logits + greedy argmax).
+//     epilogue (store / SwiGLU / logits + greedy argmax);
+//   * PSTAGES = 0 keeps the weights in REGISTERS instead of shared-memory
+//     stages: lane (g, t) loads the 16-byte pieces of rows g and g + 8 it would
+//     have read from the stage straight from global memory (eight 128-bit
+//     loads per tile, requested before the dependency wait; the next tile's
+//     once the MMAs have consumed them).  The CTA then holds 33 KB of shared
+//     memory instead of 101-135 KB, so that it fits on an SM beside its
+//     predecessor's CTAs and its weights stream while that kernel still runs,
+//     as in the FP32 chain.
 #pragma once
 
 #include "dfb_exchange.cuh"
@@ -43,6 +51,8 @@ struct PairSmem {
 template <int PSTAGES, int MODE>
 __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   constexpr bool kNorm = MODE != kModeStore;
+  constexpr bool kReg = PSTAGES == 0;     // weights in registers, no shared-memory stages
+  constexpr int kStagesOr1 = kReg ? 1 : PSTAGES;
   constexpr int K = PairSmem::kK, kWarps = 8;
   using SM = PairSmem;
   if (!a.late_trigger) pdl_launch_dependents();
@@ -79,6 +89,15 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   };
 
   // ---- weight prefetch, independent of the previous kernel ----
+  uint4 wu[4], wv[4];   // kReg: rows g and g + 8 of the current tile, this lane's piece of each 32-column block
+  if (kReg) {
+    if (blockIdx.x < a.n_tiles) {
+      const __nv_bfloat16* r0 = weight_row(blockIdx.x, g) + kbase;
+      const __nv_bfloat16* r1 = weight_row(blockIdx.x, g + 8) + kbase;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { wu[j] = ldg_stream(r0 + 32 * j); wv[j] = ldg_stream(r1 + 32 * j); }
+    }
+  }
   if (warp == 0) {
     if (lane == 0) {
 #pragma unroll
@@ -258,8 +277,8 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
   int it = 0;
   bool copy_ok = true;
   for (int tile = blockIdx.x; tile < a.n_tiles; tile += stride, ++it) {
-    const int s = it % PSTAGES;
-    if (!mbar_wait_bounded(&full[s], (it / PSTAGES) & 1)) { copy_ok = false; break; }
+    const int s = it % kStagesOr1;
+    if (!kReg && !mbar_wait_bounded(&full[s], (it / kStagesOr1) & 1)) { copy_ok = false; break; }
     const unsigned char* w0p = stage_base + s * SM::kStageBytes + g * SM::kRowStride + 2 * kbase;
     const unsigned char* w1p = w0p + 8 * SM::kRowStride;
     float c[4][4];
@@ -267,10 +286,19 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
     for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint4 u = *reinterpret_cast<const uint4*>(w0p + 64 * j);   // row g
-      const uint4 v = *reinterpret_cast<const uint4*>(w1p + 64 * j);   // row g + 8
+      const uint4 u = kReg ? wu[j] : *reinterpret_cast<const uint4*>(w0p + 64 * j);   // row g
+      const uint4 v = kReg ? wv[j] : *reinterpret_cast<const uint4*>(w1p + 64 * j);   // row g + 8
       mma_bf16_16816_full(c[(2 * j) & 3], u.x, v.x, u.y, v.y, xa[j].x, xa[j].y);
       mma_bf16_16816_full(c[(2 * j + 1) & 3], u.z, v.z, u.w, v.w, xa[j].z, xa[j].w);
+    }
+    if (kReg) {   // the weight registers are free: request the next tile's
+      const int nxt = tile + stride;
+      if (nxt < a.n_tiles) {
+        const __nv_bfloat16* r0 = weight_row(nxt, g) + kbase;
+        const __nv_bfloat16* r1 = weight_row(nxt, g + 8) + kbase;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { wu[j] = ldg_stream(r0 + 32 * j); wv[j] = ldg_stream(r1 + 32 * j); }
+      }
     }
     if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 5);
     // C: (row g, batch 2t, 2t+1) in [0],[1]; (row g+8, ...) in [2],[3]; red index = row * 8 + batch
@@ -280,7 +308,7 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
     *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) =
         make_float2((c[0][2] + c[1][2]) + (c[2][2] + c[3][2]), (c[0][3] + c[1][3]) + (c[2][3] + c[3][3]));
     __syncthreads();  // every warp is done with stage s
-    if (warp == 0) {
+    if (!kReg && warp == 0) {
       const int nxt = tile + PSTAGES * stride;
       if (nxt < a.n_tiles) request_tile(nxt, s);
     }
@@ -369,6 +397,74 @@ __global__ void __launch_bounds__(256, 2) pair_gemv_kernel(const GemvArgs a) {
       }
       if (tid == 0) { *a.ticket = 0u; sample_advance(a); }
     }
+  }
+  if (threadIdx.x == 0) trace_max(a.trace, 2);
+}
+
+// o_proj / down_proj (K = 2048 / 3072, plain store) for 2..8 batch rows with the weights in registers, the
+// companion of pair_gemv_kernel<0, ...>: a CTA owns tiles of 8 weight rows, its 8 or 12 warps split K (256
+// columns each), lane (g, t) holds the 16-byte pieces of row g for the warp's eight 32-column blocks (eight
+// 128-bit loads per tile, requested before the dependency wait) and, once the dependency has resolved, the
+// matching pieces of x[batch g] straight from global memory; rows 8..15 of each MMA are zero.  No shared-memory
+// staging at all (2-3 KB for the cross-warp reduction), so the CTA is resident beside its predecessor.
+template <int K>
+__global__ void __launch_bounds__(K / 256 * 32, 2) reg_store_gemv_kernel(const GemvArgs a) {
+  constexpr int W = K / 256;
+  static_assert(K == 2048 || K == 3072, "o_proj and down_proj widths");
+  if (!a.late_trigger) pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_min(a.trace, 0);
+  __shared__ float red[2][W][64];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int kbase = warp * 256 + 8 * t;
+  const int stride = gridDim.x;
+
+  uint4 wu[8];
+  int tile = blockIdx.x;
+  if (tile < a.n_tiles) {
+    const __nv_bfloat16* r0 = a.w + (size_t)(tile * 8 + g) * K + kbase;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wu[j] = ldg_stream(r0 + 32 * j);
+  }
+  if (warp == 1) l2_prefetch_slice(a.ahead_ptr, a.ahead_bytes, blockIdx.x, gridDim.x);
+
+  pdl_wait();
+  if (threadIdx.x == 0) { trace_max(a.trace, 1); trace_min(a.trace, 3); }
+  uint4 xa[8];   // B fragments: x[batch g], this lane's 8 columns of each 32-column block
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    xa[j] = g < a.rows ? ldg_cg(a.x + (size_t)g * K + kbase + 32 * j) : make_uint4(0, 0, 0, 0);
+  if (a.late_trigger) pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_max(a.trace, 4);
+
+  for (int it = 0; tile < a.n_tiles; tile += stride, ++it) {
+    float c[4][4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      mma_bf16_16816_full(c[(2 * j) & 3], wu[j].x, 0u, wu[j].y, 0u, xa[j].x, xa[j].y);
+      mma_bf16_16816_full(c[(2 * j + 1) & 3], wu[j].z, 0u, wu[j].w, 0u, xa[j].z, xa[j].w);
+    }
+    const int nxt = tile + stride;
+    if (nxt < a.n_tiles) {
+      const __nv_bfloat16* r0 = a.w + (size_t)(nxt * 8 + g) * K + kbase;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wu[j] = ldg_stream(r0 + 32 * j);
+    }
+    if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 5);
+    // C: (row g, batch 2t, 2t+1) in [0], [1]; red index = row * 8 + batch
+    *reinterpret_cast<float2*>(&red[it & 1][warp][g * 8 + 2 * t]) =
+        make_float2((c[0][0] + c[1][0]) + (c[2][0] + c[3][0]), (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]));
+    __syncthreads();
+    if (tid < 64) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[it & 1][w][tid];
+      const int er = tid >> 3, eb = tid & 7;
+      if (eb < a.rows) a.out[(size_t)eb * a.out_stride + tile * 8 + er] = __float2bfloat16_rn(v);
+    }
+    if (threadIdx.x == 0 && it == 0) trace_max(a.trace, 6);
   }
   if (threadIdx.x == 0) trace_max(a.trace, 2);
 }

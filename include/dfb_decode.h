@@ -205,6 +205,12 @@ typedef struct DfbStatus {
 #define DFB_OPT_ATTN_RING32 22  /* steps with a context bound of at most 1024 tokens whose rows x ceil(bound / 32) reach
                                   this value, and that DFB_OPT_ATTN_RING does not take, run the streaming attention
                                   kernel with 32 positions per CTA; 0 = never (the default: measured slower) */
+#define DFB_OPT_REG_WEIGHTS 23  /* batches above DFB_OPT_ROW_GEMV, a bit mask: 1 = QKV and gate/up, 2 = o_proj and
+                                  down_proj, 4 = LM head run the mma.sync kernels that keep their weights in
+                                  registers (loaded from global memory in MMA fragment order before the dependency
+                                  wait) instead of shared-memory stages: their CTAs need 3-33 KB of shared memory
+                                  and are resident beside their predecessor's; 8 = up to two CTAs per SM
+                                  (default 0: measured slower than the staged kernels at every batch) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,

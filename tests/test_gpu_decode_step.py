@@ -43,6 +43,19 @@ def test_tcgen05_projections_match_oracle(cuda_device, rows, mask):
     _check(r)
 
 
+@pytest.mark.parametrize("mask", [1, 2, 7, 15])
+@pytest.mark.parametrize("rows", [2, 5, 8])
+def test_register_resident_projections_match_oracle(cuda_device, rows, mask):
+    """The mma.sync kernels that keep their weights in registers instead of shared-memory stages (bit mask:
+    1 = QKV and gate/up, 2 = o_proj and down_proj, 4 = LM head, 8 = up to two CTAs per SM), with tcgen05 off
+    so that the LM head bit takes effect."""
+    from dfb_b200 import native
+    lens = [3, 70, 250, 129, 64, 1, 300, 17][:rows]
+    r = H.run_parity_case(layers=2, vocab=4096, prompt_lens=lens, steps=3, seed=40 + rows,
+                          options={native.DFB_OPT_TCGEN05: 0, native.DFB_OPT_REG_WEIGHTS: mask})
+    _check(r)
+
+
 @pytest.mark.parametrize("prompt", [254, 255, 256, 257])
 def test_block_boundary(cuda_device, prompt):
     """Decode across the 256-token block boundary (the reference's
