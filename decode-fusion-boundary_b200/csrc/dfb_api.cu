@@ -106,6 +106,9 @@ struct ChainOptions {
                                // measured slower at every batch (batch 8 / context 512: 758 us with bit 1, 719 with
                                // bit 2, 786 with both, against 709): at 2-8 rows a successor that streams its
                                // weights beside the running kernel takes bandwidth from that kernel's own stream
+  int host_io = env_int("DFB_HOST_IO", 2);   // steps from host buffers: 1 = the inputs reach the staging area by a one-warp
+                               // kernel that reads pinned host memory, 2 = tokens and status are written to pinned
+                               // host memory by a one-warp kernel, instead of copy nodes in the step's graph
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -873,6 +876,9 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
                        float* logits_out) {
   if (io.burst) {
     // staged by the burst's one host-to-device copy, advanced on the device from step to step
+  } else if (io.host && (h->opt.host_io & 1)) {
+    copy_ints_kernel<<<1, 128, 0, stream>>>(h->host_stage, h->stage, h->stage_ints());
+    DFB_CUDA(cudaGetLastError());
   } else if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->stage, h->host_stage, sizeof(int) * h->stage_ints(), cudaMemcpyHostToDevice, stream));
   } else if (io.stage) {
@@ -892,6 +898,15 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
     p.ring = h->burst_ring; p.ring_status = h->burst_status(); p.ring_done = h->burst_done();
     publish_tokens_kernel<<<1, 32, 0, stream>>>(p);
     DFB_CUDA(cudaGetLastError());
+  } else if (io.host && (h->opt.host_io & 2)) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (h->use_pdl && !h->sharded()) ? 1 : 0;   // after a collective: an ordinary dependency
+    DFB_CUDA(cudaLaunchKernelEx(&cfg, publish_result_kernel, (const int*)h->tokens, h->host_tokens, kMaxRows + 4));
   } else if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   } else if (io.out_tokens) {
@@ -1216,6 +1231,10 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     case DFB_OPT_ATTN_RING:
       if (value < 0) return DFB_E_BAD_ARG;
       h->opt.attn_ring_min = value;
+      break;
+    case DFB_OPT_HOST_IO:
+      if (value < 0 || value > 3) return DFB_E_BAD_ARG;
+      h->opt.host_io = value;
       break;
     case DFB_OPT_REG_WEIGHTS:
       if (value < 0 || value > 15) return DFB_E_BAD_ARG;

@@ -1010,6 +1010,18 @@ __global__ void stage_inputs_kernel(const StageArgs a) {
 }
 
 
+// Host-buffer steps without copy nodes: the packed inputs are read straight from pinned host memory into the
+// staging area, and the tokens plus the status word are written straight into pinned host memory (both
+// mappings are the host allocations themselves under unified addressing).  A copy node of a CUDA graph costs
+// more than a one-warp kernel for these few hundred bytes.
+__global__ void copy_ints_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+}
+__global__ void publish_result_kernel(const int* tokens_and_status, int* host_out, int n) {
+  pdl_wait();   // launched with a programmatic dependency on the LM head: everything before it has completed
+  if ((int)threadIdx.x < n) host_out[threadIdx.x] = tokens_and_status[threadIdx.x];
+}
+
 // Between the steps of a burst (several decode steps enqueued at once, dfb_decode_burst_enqueue): publishes
 // the step's tokens in a ring in pinned host memory that the kernel writes directly (no copy node, the host
 // can read finished steps while later ones run), then turns them into the next step's inputs on the device:

@@ -33,6 +33,7 @@ DFB_OPT_ATTN_CLUSTER = 20
 DFB_OPT_ATTN_CHUNK128 = 21
 DFB_OPT_ATTN_RING32 = 22
 DFB_OPT_REG_WEIGHTS = 23
+DFB_OPT_HOST_IO = 24
 DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
 DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
 

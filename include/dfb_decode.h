@@ -211,6 +211,10 @@ typedef struct DfbStatus {
                                   wait) instead of shared-memory stages: their CTAs need 3-33 KB of shared memory
                                   and are resident beside their predecessor's; 8 = up to two CTAs per SM
                                   (default 0: measured slower than the staged kernels at every batch) */
+#define DFB_OPT_HOST_IO 24      /* steps from host buffers, a bit mask: 1 = the packed inputs are read from pinned host
+                                  memory by a one-warp kernel, 2 = tokens and status are written to pinned host
+                                  memory by a one-warp kernel, instead of copy nodes in the step's graph (default 2: the
+                                  output side takes 6-7 us off a step, the input side is neutral) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
