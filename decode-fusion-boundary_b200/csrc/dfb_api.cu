@@ -915,10 +915,10 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
   return 0;
 }
 
-int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream, float* logits_out) {
+// The captured graph of a step geometry: one per (rows, split bucket, filled block-table columns, kind of
+// inputs / outputs); captured and instantiated on first use (or ahead of time by dfb_warm).
+int get_step_graph(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, DfbHandle::StepGraph** out) {
   const bool persistent = h->step_mode == 1;
-  if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
-  // one graph per (rows, split bucket, filled block-table columns, kind of inputs / outputs)
   const int io_kind = (io.burst ? 0 : io.host ? 3 : (io.out_tokens ? 2 : 1)) + (io.sampling ? 4 : 0);
   const long long key = ((persistent ? (1ll << 40) : 0ll) + (((long long)bt_cols * 16 + rows) * 4096 + nsplit) * 2 +
                          (h->use_pdl ? 1 : 0)) * 8 + io_kind;
@@ -959,7 +959,16 @@ int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, 
     g.graph = graph;
     it = h->graphs.emplace(key, g).first;
   }
-  DfbHandle::StepGraph& g = it->second;
+  *out = &it->second;
+  return 0;
+}
+
+int run_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const StepIo& io, cudaStream_t stream, float* logits_out) {
+  if (!h->use_graph || logits_out) return enqueue_whole_step(h, rows, nsplit, bt_cols, io, stream, logits_out);
+  DfbHandle::StepGraph* gp = nullptr;
+  int rc = get_step_graph(h, rows, nsplit, bt_cols, io, &gp);
+  if (rc) return rc;
+  DfbHandle::StepGraph& g = *gp;
   if (!io.host && !io.burst) {
     if (memcmp(&g.stage_args, io.stage, sizeof(StageArgs)) != 0) {
       StageArgs args = *io.stage;
@@ -1279,6 +1288,55 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
     default: return DFB_E_BAD_ARG;
   }
   drop_graphs();
+  return 0;
+}
+
+int dfb_warm(DfbHandle* h, int32_t max_rows, int32_t max_context, int32_t kinds, int32_t* graphs_out) {
+  if (graphs_out) *graphs_out = h ? (int32_t)h->graphs.size() : 0;
+  if (!h || max_rows < 1 || max_rows > kMaxRows || max_context < 1 || kinds < 1 || kinds > 31) return DFB_E_BAD_ARG;
+  if (max_context > h->m.max_model_len) max_context = h->m.max_model_len;
+  if (!h->use_graph) return 0;
+  // dummy arguments of the input staging kernel for the device-pointer kinds: a launch patches them anyway
+  StageArgs a = {};
+  a.prev_tokens = h->tokens; a.positions = reinterpret_cast<const int64_t*>(h->stage);
+  a.block_tables = h->st_bt(); a.bt_stride_in = h->max_pages; a.bt_stride_out = h->max_pages;
+  a.embed_rows = h->embed_rows(); a.status = h->status;
+  a.ids_out = h->st_ids(); a.positions_out = h->st_pos(); a.bt_out = h->st_bt(); a.row_active_out = h->st_active();
+  a.temps_out = h->st_temps();
+  const int bs = h->m.block_size;
+  for (int rows = 1; rows <= max_rows; ++rows) {
+    a.rows = rows;
+    for (int ctx = 1;; ctx += kAttnChunk) {
+      if (ctx > max_context) ctx = max_context;
+      const int cols = (ctx + bs - 1) / bs;
+      a.bt_cols = cols;
+      // context bounds a step of this many columns can come with: the exact one, and the full last column
+      // (what dfb_decode_step assumes without a max_context hint)
+      const int bounds[2] = {ctx, cols * bs};
+      for (int bi = 0; bi < 2; ++bi) {
+        const int nsplit = split_bucket(h, bounds[bi], rows);
+        for (int sampling = 0; sampling < 2; ++sampling) {
+          if (sampling && !(kinds & 16)) continue;
+          if (sampling && h->step_mode == 1) continue;
+          a.temps = sampling ? h->st_temps() : nullptr;
+          for (int kind = 0; kind < 4; ++kind) {
+            if (!(kinds & (1 << kind))) continue;
+            if (kind == 0 && h->step_mode == 1) continue;   // bursts run on the kernel chain only
+            StepIo io;
+            io.sampling = sampling != 0;
+            if (kind == 0) io.burst = true;
+            else if (kind == 3) io.host = true;
+            else { io.stage = &a; io.out_tokens = kind == 2 ? h->tokens : nullptr; }
+            DfbHandle::StepGraph* g = nullptr;
+            int rc = get_step_graph(h, rows, nsplit, cols, io, &g);
+            if (rc) return rc;
+          }
+        }
+      }
+      if (ctx >= max_context) break;
+    }
+  }
+  if (graphs_out) *graphs_out = (int32_t)h->graphs.size();
   return 0;
 }
 

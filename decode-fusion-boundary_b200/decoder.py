@@ -210,6 +210,20 @@ class StreamDecoder:
             f"(kernel {st.detail[0]}, index {st.detail[1]}, value {st.detail[2]})")
 
     # -- decode --------------------------------------------------------------
+    WARM_BURST, WARM_DEVICE, WARM_DEVICE_TOKENS, WARM_HOST, WARM_SAMPLING = 1, 2, 4, 8, 16
+
+    def warm(self, max_rows: int | None = None, max_context: int | None = None,
+             kinds: int = WARM_DEVICE_TOKENS | WARM_HOST) -> int:
+        """Capture the graphs of every step geometry ahead of time (``dfb_warm``; the counterpart of
+        ``ModelRunner.capture_cudagraph``).  The default prepares what ``MegakernelBackend`` calls: the
+        host-buffer step of ``decode`` and the device-pointer step of ``decode_batch``.  Returns the number of
+        graphs held."""
+        n = C.c_int32(0)
+        self._native.check(self._lib.dfb_warm(self._handle, int(max_rows or self._max_rows),
+                                              int(max_context or self._max_model_len), int(kinds), C.byref(n)),
+                           "dfb_warm")
+        return n.value
+
     def set_seed(self, seed: int) -> None:
         """Seed of the sampling noise; restarts the noise stream (``dfb_set_seed``)."""
         self._native.check(self._lib.dfb_set_seed(self._handle, int(seed) & (2 ** 64 - 1)), "dfb_set_seed")

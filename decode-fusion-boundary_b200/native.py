@@ -48,7 +48,7 @@ EXPORTS = (
     "dfb_launch_linear", "dfb_launch_rmsnorm_gateup_swiglu", "dfb_launch_lmhead_argmax",
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
     "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
-    "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host",
+    "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host", "dfb_warm",
 )
 
 
@@ -139,6 +139,7 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
+    L.dfb_warm.argtypes = [vp, i32, i32, i32, vp]
     L.dfb_decode_burst_enqueue.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_decode_burst_collect.argtypes = [vp, i32, vp, vp]
     L.dfb_decode_burst_host.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]

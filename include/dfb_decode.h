@@ -243,6 +243,16 @@ int dfb_tp_open_loopback(DfbHandle* h);
 void dfb_destroy(DfbHandle* h);
 int dfb_set_option(DfbHandle* h, int option, int value);
 
+/* Capture ahead of time the graphs of every step geometry up to `max_rows` rows and `max_context` tokens, so
+ * that no step of a serving run pays a capture (a few milliseconds) when the batch size changes or a row's
+ * context crosses a chunk or block boundary: the counterpart of ModelRunner.capture_cudagraph
+ * (engine/model_runner.py:379-416), which captures the torch path's graphs for its batch sizes at start-up.
+ * `kinds` is a bit mask of the entry points to prepare: 1 = bursts, 2 = dfb_decode_step without out_tokens,
+ * 4 = dfb_decode_step with out_tokens, 8 = the host-buffer steps, 16 = also the sampling variants of those.
+ * `graphs_out` (may be NULL) receives the number of graphs the decoder holds afterwards.  Options set later
+ * drop the graphs again. */
+int dfb_warm(DfbHandle* h, int32_t max_rows, int32_t max_context, int32_t kinds, int32_t* graphs_out);
+
 /* Enqueue one decode step on `stream` (no host synchronisation, no allocation
  * after the first call for a given (rows, bucket)).  Replaces tg_launch_decode +
  * tg_launch_zero_regions + the three staging copies of taskgraph.py:395-413. */

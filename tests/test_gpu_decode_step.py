@@ -379,3 +379,28 @@ def test_option_and_tensor_parallel_argument_errors(cuda_device):
     # the decoder still works after the refused calls
     assert len(dec.decode_host([first[0]], [10], [tables[0][:1]])) == 1
     dec.close()
+
+
+def test_warm_captures_every_geometry_ahead_of_time(cuda_device):
+    """After ``warm`` no step of the prepared kinds captures a graph any more: rows 1..3, contexts across the
+    chunk (64, 128) and block (256, 512) boundaries, through the host-buffer and the device-pointer entries."""
+    import time
+    g = H.oracle_geometry(layers=2, vocab=2048)
+    w = O.make_weights(g, seed=61, norm="random").to(torch.bfloat16)
+    kv = O.new_kv_cache(g, 12, torch.bfloat16).cuda()
+    dec = H.make_decoder(w, kv)
+    t0 = time.perf_counter()
+    held = dec.warm(max_rows=3, max_context=700)
+    warm_s = time.perf_counter() - t0
+    assert held > 0
+    for rows in (1, 2, 3):
+        tables = [[3 * r, 3 * r + 1, 3 * r + 2] for r in range(rows)]
+        for ctx in (1, 64, 65, 128, 129, 256, 257, 511, 512, 513, 699):
+            cols = -(-(ctx + 1) // g.block_size)
+            ids, pos = [5] * rows, [ctx] * rows
+            dec.decode_host(ids, pos, [t[:cols] for t in tables])
+            bt = torch.tensor([t[:cols] for t in tables], dtype=torch.int32, device="cuda")
+            dec.decode_rows(torch.tensor(ids, device="cuda"), torch.tensor(pos, device="cuda"), bt)
+    assert dec.warm(max_rows=3, max_context=700) == held, "a step captured a graph that warm() had not prepared"
+    assert warm_s < 30.0
+    dec.close()
