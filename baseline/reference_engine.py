@@ -15,8 +15,8 @@
   durations from ``torch.profiler`` (graph replay + the LM-head GEMM + the
   sampler that run outside the graph, engine/model_runner.py:292-313,374) --
   the last one is the number most favourable to the reference;
-* ``install_backend_switch``: the import switch of INTEGRATION.md, applied to
-  the loaded reference modules, after which ``decode_backend="megakernel"``
+* ``install_backend_switch``: the one-line import switch a maintainer would make
+  in ``engine/model_runner.py:10-13``, applied to the loaded reference modules, after which ``decode_backend="megakernel"``
   builds THIS repository's backend inside the reference's ``ModelRunner``.
 
 This file is benchmark / test infrastructure: nothing in the product package
@@ -127,7 +127,7 @@ def write_model_dir(path, seed: int = 0, layers: int = 28, vocab: int = 151936, 
 
 
 def install_backend_switch():
-    """The import switch of INTEGRATION.md applied at run time: the reference's
+    """The import switch of ``engine/model_runner.py:10-13`` applied at run time: the reference's
     ``ModelRunner`` (engine/model_runner.py:10-13,80-95,315-376) then builds this
     repository's ``MegakernelBackend`` for ``decode_backend="megakernel"``."""
     import_reference()

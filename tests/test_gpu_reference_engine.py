@@ -3,7 +3,7 @@
 The unmodified reference package (installed by ``baseline/install_reference.sh``
 into the git-ignored ``baseline/_ref``) is driven through its public API,
 ``LLM(dir, decode_backend=...)``, once with its torch decode path and once with
-``decode_backend="megakernel"`` after the import switch of INTEGRATION.md
+``decode_backend="megakernel"`` after the backend import switch
 (``baseline/reference_engine.install_backend_switch``), so that the reference's
 ``ModelRunner`` builds and calls THIS repository's ``MegakernelBackend``:
 scheduler, block manager, paged KV cache and prefill are the reference's.
