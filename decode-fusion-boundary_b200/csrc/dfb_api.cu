@@ -106,9 +106,11 @@ struct ChainOptions {
                                // measured slower at every batch (batch 8 / context 512: 758 us with bit 1, 719 with
                                // bit 2, 786 with both, against 709): at 2-8 rows a successor that streams its
                                // weights beside the running kernel takes bandwidth from that kernel's own stream
-  int host_io = env_int("DFB_HOST_IO", 2);   // steps from host buffers: 1 = the inputs reach the staging area by a one-warp
+  int host_io = env_int("DFB_HOST_IO", 6);   // steps from host buffers: 1 = the inputs reach the staging area by a one-warp
                                // kernel that reads pinned host memory, 2 = tokens and status are written to pinned
-                               // host memory by a one-warp kernel, instead of copy nodes in the step's graph
+                               // host memory by a one-warp kernel, instead of copy nodes in the step's graph; 4 = the
+                               // host then polls the sequence word that follows the tokens into pinned memory
+                               // instead of synchronising the stream
   int attn_ring_min = 200;     // steps whose rows x 64-position chunks of the context bound reach this many take the
                                // streaming attention kernel (dfb_attnring.cuh), which needs about two CTAs per SM
                                // to pay; smaller ones stay on the register-resident kernel; 0 = never
@@ -274,6 +276,8 @@ struct DfbHandle {
   // burst: several steps enqueued at once, tokens published in a pinned ring written by the device
   int* burst_ring = nullptr;            // pinned: [kMaxBurst][8] tokens | [4] status | [1] steps done
   unsigned int* burst_slot = nullptr;   // device
+  unsigned int* publish_seq = nullptr;  // device: host-buffer steps published so far (follows the tokens to the host)
+  unsigned int published = 0;           // host: the value the next published step will carry
   cudaEvent_t burst_event = nullptr;
   int burst_rows = 0, burst_steps = 0;  // of the burst in flight (0 = none)
   int* burst_status() const { return burst_ring + kMaxBurst * kMaxRows; }
@@ -906,7 +910,8 @@ int enqueue_whole_step(DfbHandle* h, int rows, int nsplit, int bt_cols, const St
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (h->use_pdl && !h->sharded()) ? 1 : 0;   // after a collective: an ordinary dependency
-    DFB_CUDA(cudaLaunchKernelEx(&cfg, publish_result_kernel, (const int*)h->tokens, h->host_tokens, kMaxRows + 4));
+    DFB_CUDA(cudaLaunchKernelEx(&cfg, publish_result_kernel, (const int*)h->tokens, h->host_tokens, kMaxRows + 4,
+                                h->publish_seq));
   } else if (io.host) {
     DFB_CUDA(cudaMemcpyAsync(h->host_tokens, h->tokens, sizeof(int) * (kMaxRows + 4), cudaMemcpyDeviceToHost, stream));
   } else if (io.out_tokens) {
@@ -1065,10 +1070,12 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   const size_t o_tpstep = carve(sizeof(unsigned) * 4);
   const size_t o_sctr = carve(sizeof(unsigned) * 4);
   const size_t o_bslot = carve(sizeof(unsigned) * 4);
+  const size_t o_pseq = carve(sizeof(unsigned) * 4);
   e = cudaMalloc(&h->slab, off);
   if (e == cudaSuccess) e = cudaMemset(h->slab, 0, off);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_stage, sizeof(int) * h->stage_ints());
-  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_tokens, sizeof(int) * (kMaxRows + 4));
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->host_tokens, sizeof(int) * (kMaxRows + 8));
+  if (e == cudaSuccess) h->host_tokens[kMaxRows + 4] = 0;
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->burst_ring, sizeof(int) * (kMaxBurst * kMaxRows + 8));
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->burst_event, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking);
@@ -1096,6 +1103,7 @@ int dfb_create(const DfbModelDesc* d, DfbHandle** out) {
   h->tp_step = (unsigned int*)(s + o_tpstep);
   h->sample_ctr = (unsigned int*)(s + o_sctr);
   h->burst_slot = (unsigned int*)(s + o_bslot);
+  h->publish_seq = (unsigned int*)(s + o_pseq);
   *out = h;
   return 0;
 }
@@ -1242,7 +1250,7 @@ int dfb_set_option(DfbHandle* h, int option, int value) {
       h->opt.attn_ring_min = value;
       break;
     case DFB_OPT_HOST_IO:
-      if (value < 0 || value > 3) return DFB_E_BAD_ARG;
+      if (value < 0 || value > 7) return DFB_E_BAD_ARG;
       h->opt.host_io = value;
       break;
     case DFB_OPT_REG_WEIGHTS:
@@ -1435,7 +1443,19 @@ int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* inpu
   io.host = true;      // the two copies between the pinned staging buffers and the device are part of the step's graph
   rc = run_step(h, rows, split_bucket(h, max_ctx, rows), cols, io, stream, nullptr);
   if (rc) return rc;
-  DFB_CUDA(cudaStreamSynchronize(stream));
+  bool arrived = false;
+  if ((h->opt.host_io & 2) && (h->opt.host_io & 4) && h->use_graph) {
+    // The publishing kernel is the step's last node: once its sequence word has changed in pinned memory the
+    // tokens and the status are there.  Polling it saves the driver's stream synchronisation; after about a
+    // tenth of a second without it (an error, a debugger) the ordinary synchronisation takes over.
+    const int want = (int)++h->published;
+    volatile int* word = h->host_tokens + kMaxRows + 4;
+    for (long spin = 0; spin < 40000000l; ++spin)
+      if (*word == want) { arrived = true; break; }
+  } else if (h->opt.host_io & 2) {
+    ++h->published;
+  }
+  if (!arrived) DFB_CUDA(cudaStreamSynchronize(stream));
   for (int r = 0; r < rows; ++r) out_tokens[r] = h->host_tokens[r];
   ++h->steps;
   if (h->host_tokens[kMaxRows]) {

@@ -1017,9 +1017,18 @@ __global__ void stage_inputs_kernel(const StageArgs a) {
 __global__ void copy_ints_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
   for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
 }
-__global__ void publish_result_kernel(const int* tokens_and_status, int* host_out, int n) {
+// `seq` (device) counts the steps published; its new value follows the data into host_out[n], after a
+// system-scope fence, so that a host thread polling that word sees complete data once it changes.
+__global__ void publish_result_kernel(const int* tokens_and_status, int* host_out, int n, unsigned int* seq) {
   pdl_wait();   // launched with a programmatic dependency on the LM head: everything before it has completed
   if ((int)threadIdx.x < n) host_out[threadIdx.x] = tokens_and_status[threadIdx.x];
+  __threadfence_system();
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const unsigned int next = *seq + 1u;
+    *seq = next;
+    *reinterpret_cast<volatile int*>(host_out + n) = (int)next;
+  }
 }
 
 // Between the steps of a burst (several decode steps enqueued at once, dfb_decode_burst_enqueue): publishes

@@ -165,6 +165,9 @@ class StreamDecoder:
         self._h_pos = (C.c_int64 * self._max_rows)()
         self._h_bt = (C.c_int32 * (self._max_rows * self._max_pages))()
         self._h_out = (C.c_int32 * self._max_rows)()
+        self._h_temp = (C.c_float * self._max_rows)()
+        self._step_host = self._lib.dfb_decode_step_host_sampled
+        self._current_stream = torch.cuda.current_stream
         self._step = native.DfbStepDesc()
 
     # -- lifecycle -----------------------------------------------------------
@@ -365,9 +368,27 @@ class StreamDecoder:
         host block table directly."""
         if self._torch.is_tensor(block_table):
             block_table = block_table.tolist()
-        table = list(block_table)[: self._max_pages]
-        temps = [float(temperature)] if temperature and temperature > 1e-10 else None
-        return self.decode_host([int(token_id)], [int(position)], [table], temperatures=temps)[0]
+        # the step every batch-1 token goes through: the persistent ctypes arrays are filled in place and the
+        # native call made directly (no per-call lists or arrays)
+        cols = min(len(block_table), self._max_pages)
+        if cols < 1:
+            raise ValueError("decode_row needs a block table")
+        h_bt = self._h_bt
+        for c in range(cols):
+            h_bt[c] = block_table[c]
+        self._h_ids[0] = token_id
+        self._h_pos[0] = position
+        temps = None
+        if temperature and temperature > 1e-10:
+            self._h_temp[0] = temperature
+            temps = self._h_temp
+        code = self._step_host(self._handle, 1, self._h_ids, self._h_pos, h_bt, cols, None, temps, self._h_out,
+                               self._current_stream().cuda_stream)
+        if code:
+            if code == -4:
+                self._raise_device_status()
+            self._native.check(code, "dfb_decode_step_host_sampled")
+        return self._h_out[0]
 
     # -- the one-step interface MegakernelBackend calls -----------------------
     def step(self, token_id: int, position: int | None = None, block_table=None, temperature: float = 0.0) -> int:

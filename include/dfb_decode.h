@@ -213,8 +213,10 @@ typedef struct DfbStatus {
                                   (default 0: measured slower than the staged kernels at every batch) */
 #define DFB_OPT_HOST_IO 24      /* steps from host buffers, a bit mask: 1 = the packed inputs are read from pinned host
                                   memory by a one-warp kernel, 2 = tokens and status are written to pinned host
-                                  memory by a one-warp kernel, instead of copy nodes in the step's graph (default 2: the
-                                  output side takes 6-7 us off a step, the input side is neutral) */
+                                  memory by a one-warp kernel, instead of copy nodes in the step's graph; 4 = with 2:
+                                  the call returns when the sequence word that the kernel writes after the tokens
+                                  has arrived (polled in pinned memory) instead of synchronising the stream
+                                  (default 6) */
 #define DFB_OPT_TRACE 4       /* 1: every kernel records its timeline (see dfb_read_trace); default 0 */
 
 /* Build a decoder for one model on the current device: validates the geometry,
