@@ -196,7 +196,7 @@ class MegakernelBackend:
         seed = _get_attr(self.config, "megakernel_seed", None)
         if seed is not None:
             self.decoder.set_seed(int(seed))
-        if _get_attr(self.config, "megakernel_warm", True):
+        if _get_attr(self.config, "megakernel_warm", True) and group is None:   # sharded decoders capture lazily
             # every step geometry this engine can ask for is captured now, as ModelRunner.capture_cudagraph does
             # for the torch path (engine/model_runner.py:379-416): 160 graphs, about 0.1 s and 70 MB at 8 rows
             rows = min(int(_get_attr(self.config, "max_num_seqs", 8) or 8), 8)
