@@ -47,6 +47,30 @@ constexpr int kRingThreads = 32 * kRingHeads;
 constexpr int kRingSmemBytes = kRingStages * kRingStageBytes + 128;
 constexpr int kKernelAttnRing = 7;
 
+// Packed FP32 multiply-add (two IEEE fused multiply-adds in one instruction slot): the kernel is bound by
+// instruction issue, not by the FP32 pipe, and every result is bit-identical to two fmaf().
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+// the two bf16 values of a packed word as fp32
+__device__ __forceinline__ float2 bf2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
+
 __device__ __forceinline__ void fence_async_smem_ring() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // reductions over the 8 positions of a stage: lanes that differ only in bits 3-4 (the quarters) hold equal values
 __device__ __forceinline__ float pos_max(float v) {
@@ -243,18 +267,20 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const uint4 kv = *reinterpret_cast<const uint4*>(krow + 16 * ((4 * quarter + c + qp) & 15));
-        float kf[8], qa[8], qb[8];
-        unpack8(kv, kf);
-        unpack8(q0r[c], qa);
-        unpack8(q1r[c], qb);
-        float t0 = kf[0] * qa[0], t1 = kf[0] * qb[0], u0 = kf[1] * qa[1], u1 = kf[1] * qb[1];
+        // (even, odd) dimension pairs of the piece: the products of a pair go through one packed FMA, the
+        // accumulators (t, u) = (sum over even dimensions, sum over odd dimensions) per query head as before
+        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+        const uint32_t aw[4] = {q0r[c].x, q0r[c].y, q0r[c].z, q0r[c].w};
+        const uint32_t bw[4] = {q1r[c].x, q1r[c].y, q1r[c].z, q1r[c].w};
+        float2 tu0 = fmul2(bf2(kw[0]), bf2(aw[0])), tu1 = fmul2(bf2(kw[0]), bf2(bw[0]));
 #pragma unroll
-        for (int e = 2; e < 8; e += 2) {
-          t0 = fmaf(kf[e], qa[e], t0); t1 = fmaf(kf[e], qb[e], t1);
-          u0 = fmaf(kf[e + 1], qa[e + 1], u0); u1 = fmaf(kf[e + 1], qb[e + 1], u1);
+        for (int e = 1; e < 4; ++e) {
+          const float2 kf = bf2(kw[e]);
+          tu0 = ffma2(kf, bf2(aw[e]), tu0);
+          tu1 = ffma2(kf, bf2(bw[e]), tu1);
         }
-        d0 += t0 + u0;
-        d1 += t1 + u1;
+        d0 += tu0.x + tu0.y;
+        d1 += tu1.x + tu1.y;
       }
     }
     d0 += __shfl_xor_sync(0xffffffffu, d0, 8);  d1 += __shfl_xor_sync(0xffffffffu, d1, 8);
@@ -277,9 +303,12 @@ __global__ void __launch_bounds__(kRingThreads, 2) paged_attention_ring_kernel(c
       const float w0 = __shfl_sync(0xffffffffu, p0v, p), w1 = __shfl_sync(0xffffffffu, p1v, p);
       if (p < npos) {   // same for the whole warp; rows beyond npos were never loaded
         const uint2 v2 = *reinterpret_cast<const uint2*>(vcol + p * kRingRowBytes);
-        const float vf[4] = {bf_lo(v2.x), bf_hi(v2.x), bf_lo(v2.y), bf_hi(v2.y)};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { o0[e] = fmaf(w0, vf[e], o0[e]); o1[e] = fmaf(w1, vf[e], o1[e]); }
+        const float2 va = bf2(v2.x), vb = bf2(v2.y), ww0 = make_float2(w0, w0), ww1 = make_float2(w1, w1);
+        float2 r;
+        r = ffma2(ww0, va, make_float2(o0[0], o0[1])); o0[0] = r.x; o0[1] = r.y;
+        r = ffma2(ww0, vb, make_float2(o0[2], o0[3])); o0[2] = r.x; o0[3] = r.y;
+        r = ffma2(ww1, va, make_float2(o1[0], o1[1])); o1[0] = r.x; o1[1] = r.y;
+        r = ffma2(ww1, vb, make_float2(o1[2], o1[3])); o1[2] = r.x; o1[3] = r.y;
       }
     }
     __syncwarp();
