@@ -874,6 +874,57 @@ def run_profile_step(args):
         raise SystemExit(1)
 
 
+def run_store_kvcache(args):
+    """``dfb_store_kvcache`` alone: N prompt tokens' K and V rows (2 KB each) scattered to random slots of one
+    layer's cache, a fresh set of rows and slots per launch (inputs larger than L2 across the timed launches),
+    CUDA events around each launch; bytes = N x 2 x 2 KB read + as many written."""
+    import torch
+
+    import __graft_entry__  # noqa: F401
+    from dfb_b200.kv_store import store_kvcache
+
+    n = int(args.store_kvcache)
+    torch.cuda.set_device(0)
+    peak, peak_kind = measured_peaks()
+    heads, dim, bs = 8, 128, 256
+    blocks = max(2 * -(-n // bs), 64)
+    k_cache = torch.zeros(blocks, bs, heads, dim, dtype=torch.bfloat16, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    sets = max(4, (256 << 20) // max(n * 8192, 1))          # enough distinct inputs to exceed L2
+    sets = min(sets, 64)
+    qkvs = [torch.randn(n, 4096, device="cuda").bfloat16() for _ in range(sets)]
+    slots = [torch.randperm(blocks * bs, device="cuda")[:n].to(torch.int32) for _ in range(sets)]
+    from dfb_b200 import native
+
+    lib, stream = native.lib(), torch.cuda.current_stream().cuda_stream
+    num_slots = blocks * bs
+
+    def launch(i):   # the C entry point directly: the Python wrapper's checks would be what is timed at this size
+        q = qkvs[i % sets]
+        native.check(lib.dfb_store_kvcache(q.data_ptr() + 2 * 2048, q.data_ptr() + 2 * 3072, 4096, 4096,
+                                           k_cache.data_ptr(), v_cache.data_ptr(), slots[i % sets].data_ptr(), n,
+                                           heads * dim, num_slots, None, stream), "dfb_store_kvcache")
+
+    burst = 8                                                # launches per timed sample, back to back
+    store_kvcache(qkvs[0][:, 2048:3072].view(n, heads, dim), qkvs[0][:, 3072:4096].view(n, heads, dim), k_cache,
+                  v_cache, slots[0])                         # once through the public wrapper
+    times = []
+    for it in range(args.warmup + max(args.steps, 8)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for j in range(burst):
+            launch(it * burst + j)
+        b.record()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            times.append(1e3 * a.elapsed_time(b) / burst)
+    us = statistics.median(times)
+    moved = 2 * n * 2 * heads * dim * 2                        # K and V rows, read and written
+    print(json.dumps({"kernel": "store_kvcache_kernel", "tokens": n, "us": us, "bytes_read_plus_written": moved,
+                      "achieved_gbs": moved / us / 1e3, "peak_gbs": peak, "frac": moved / us / 1e3 / peak,
+                      "peak": peak_kind, "launches": len(times)}))
+
+
 def run_cta_sweep(args):
     """Per-op time against the CTA count (the reference's TG_NUM_SMS diagnostic,
     backends/megakernel/taskgraph.py:68-83): the persistent kernel at 1 ... 148
@@ -957,6 +1008,8 @@ def main():
     # profiling drivers
     ap.add_argument("--profile-step", action="store_true", help="run plain steps for a profiler instead of the benchmark")
     ap.add_argument("--cta-sweep", action="store_true", help="per-op time against the CTA count")
+    ap.add_argument("--store-kvcache", type=int, default=0, metavar="TOKENS",
+                    help="time dfb_store_kvcache (prefill-side KV write) alone for this many prompt tokens")
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--mode", choices=["persistent", "chained"], default="chained")
@@ -976,6 +1029,8 @@ def main():
         run_profile_step(args)
     elif args.cta_sweep:
         run_cta_sweep(args)
+    elif args.store_kvcache:
+        run_store_kvcache(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

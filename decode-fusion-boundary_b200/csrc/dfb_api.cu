@@ -1348,6 +1348,25 @@ int dfb_warm(DfbHandle* h, int32_t max_rows, int32_t max_context, int32_t kinds,
   return 0;
 }
 
+int dfb_store_kvcache(const void* key, const void* value, int64_t key_stride, int64_t value_stride, void* k_cache,
+                      void* v_cache, const int32_t* slot_mapping, int32_t n_tokens, int32_t row_elems,
+                      int64_t num_slots, int32_t* status, dfb_stream_t stream) {
+  if (!key || !value || !k_cache || !v_cache || !slot_mapping || n_tokens < 0 || num_slots < 1) return DFB_E_BAD_ARG;
+  // rows are moved in 16-byte pieces: bf16 rows of a multiple of 8 elements, 16-byte aligned bases and strides
+  if (row_elems < 8 || row_elems % 8 || key_stride < row_elems || value_stride < row_elems || key_stride % 8 ||
+      value_stride % 8)
+    return DFB_E_BAD_ARG;
+  if (((uintptr_t)key | (uintptr_t)value | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return DFB_E_BAD_ARG;
+  if (n_tokens == 0) return 0;
+  int grid = 8 * sm_count_cached();
+  if (grid > n_tokens) grid = n_tokens;
+  store_kvcache_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const unsigned char*)key, (const unsigned char*)value, 2 * key_stride, 2 * value_stride, (unsigned char*)k_cache,
+      (unsigned char*)v_cache, slot_mapping, n_tokens, 2 * row_elems, num_slots, status);
+  DFB_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int dfb_set_seed(DfbHandle* h, uint64_t seed) {
   if (!h) return DFB_E_BAD_ARG;
   // the seed is a kernel argument of every captured LM head; the noise stream restarts at step 0

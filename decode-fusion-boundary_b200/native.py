@@ -35,7 +35,7 @@ DFB_OPT_ATTN_RING32 = 22
 DFB_OPT_REG_WEIGHTS = 23
 DFB_OPT_HOST_IO = 24
 DFB_STATUS_BAD_POSITION, DFB_STATUS_BAD_BLOCK, DFB_STATUS_COPY_TIMEOUT = 1, 2, 3
-DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID = 4, 5, 6
+DFB_STATUS_PEER_TIMEOUT, DFB_STATUS_BAD_TOKEN, DFB_STATUS_BAD_GRID, DFB_STATUS_BAD_SLOT = 4, 5, 6, 7
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,6 +49,7 @@ EXPORTS = (
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
     "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
     "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host", "dfb_warm",
+    "dfb_store_kvcache",
 )
 
 
@@ -140,6 +141,7 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
     L.dfb_warm.argtypes = [vp, i32, i32, i32, vp]
+    L.dfb_store_kvcache.argtypes = [vp, vp, C.c_int64, C.c_int64, vp, vp, vp, i32, i32, C.c_int64, vp, vp]
     L.dfb_decode_burst_enqueue.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_decode_burst_collect.argtypes = [vp, i32, vp, vp]
     L.dfb_decode_burst_host.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]

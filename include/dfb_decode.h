@@ -144,6 +144,7 @@ typedef struct DfbTensorParallel {
 #define DFB_STATUS_COPY_TIMEOUT 3  /* a bulk copy into shared memory did not complete within its bounded wait */
 #define DFB_STATUS_PEER_TIMEOUT 4  /* tensor parallel: peer `index` did not deliver tag `value` in time */
 #define DFB_STATUS_BAD_TOKEN 5     /* token id of row `index` outside the embedding table (row 0 used instead) */
+#define DFB_STATUS_BAD_SLOT 7      /* dfb_store_kvcache: slot_mapping[index] outside [-1, num_slots): the row was skipped */
 #define DFB_STATUS_BAD_GRID 6      /* max_context smaller than positions[index] + 1: the attention grid is too small */
 
 typedef struct DfbStatus {
@@ -361,6 +362,17 @@ int dfb_launch_lmhead_argmax(DfbHandle* h, const void* hidden_in, const void* re
 /* The same with sampling: `temperatures` is a DEVICE array [rows] (NULL = greedy); layers/sampler.py:7-16. */
 int dfb_launch_lmhead_sample(DfbHandle* h, const void* hidden_in, const void* residual, const float* temperatures,
                              int32_t* out_tokens, float* out_logits, int32_t rows, dfb_stream_t stream);
+
+/* The prefill side of the shared paged cache (layers/attention.py:10-40, `store_kvcache` and its Triton kernel):
+ * the K / V rows of `n_tokens` prompt tokens, bf16 [n_tokens, row_elems] with row strides key_stride /
+ * value_stride (elements), go to rows slot_mapping[i] of k_cache / v_cache viewed as [num_slots, row_elems]
+ * (num_slots = num_blocks * block_size of one layer; row_elems = kv_heads * head_dim).  slot -1 is skipped as in
+ * the reference; any other slot outside [0, num_slots) is skipped too and recorded in `status` (NULL, or a device
+ * int32[4] that receives {DFB_STATUS_BAD_SLOT, kernel id, token index, slot}).  All pointers are device pointers;
+ * nothing is allocated and nothing synchronised.  Prefill ATTENTION itself stays on the engine's torch path. */
+int dfb_store_kvcache(const void* key, const void* value, int64_t key_stride, int64_t value_stride, void* k_cache,
+                      void* v_cache, const int32_t* slot_mapping, int32_t n_tokens, int32_t row_elems,
+                      int64_t num_slots, int32_t* status, dfb_stream_t stream);
 
 /* Final add+RMSNorm, tied LM head and greedy argmax WITHOUT any allocation.
  * (No counterpart in the reference: its LM head always runs inside a decoder

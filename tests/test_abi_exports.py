@@ -53,3 +53,14 @@ def test_argument_errors_need_no_device():
     assert lib.dfb_decode_step(None, None, None) == -1
     assert lib.dfb_error_string(-2) == b"dfb: unsupported model geometry"
     assert lib.dfb_error_string(0) == b"success"
+
+
+def test_store_kvcache_argument_checks_need_no_device():
+    """dfb_store_kvcache validates before any launch."""
+    lib = native.lib()
+    one = 16
+    assert lib.dfb_store_kvcache(None, one, 1024, 1024, one, one, one, 1, 1024, 10, None, None) == -1
+    assert lib.dfb_store_kvcache(one, one, 1024, 1024, one, one, one, 1, 1020, 10, None, None) == -1   # row not in 16-byte pieces
+    assert lib.dfb_store_kvcache(one, one, 512, 1024, one, one, one, 1, 1024, 10, None, None) == -1    # stride < row
+    assert lib.dfb_store_kvcache(one, one + 2, 1024, 1024, one, one, one, 1, 1024, 10, None, None) == -1  # misaligned
+    assert lib.dfb_store_kvcache(one, one, 1024, 1024, one, one, one, 0, 1024, 10, None, None) == 0    # nothing to do
