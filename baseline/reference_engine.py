@@ -126,10 +126,15 @@ def write_model_dir(path, seed: int = 0, layers: int = 28, vocab: int = 151936, 
     return path
 
 
-def install_backend_switch():
+STORE_KVCACHE_CALLS = [0]   # calls of this repository's store_kvcache made by the reference's Attention.forward
+
+
+def install_backend_switch(store_kvcache: bool = True):
     """The import switch of ``engine/model_runner.py:10-13`` applied at run time: the reference's
     ``ModelRunner`` (engine/model_runner.py:10-13,80-95,315-376) then builds this
-    repository's ``MegakernelBackend`` for ``decode_backend="megakernel"``."""
+    repository's ``MegakernelBackend`` for ``decode_backend="megakernel"``.  With ``store_kvcache`` the
+    reference's ``Attention.forward`` (layers/attention.py:59-64) also writes the prompt tokens' K / V into the
+    shared paged cache through this repository's kernel instead of its Triton kernel."""
     import_reference()
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
@@ -139,6 +144,15 @@ def install_backend_switch():
 
     model_runner.MegakernelBackend = dfb_b200.MegakernelBackend
     model_runner.is_megakernel_backend = dfb_b200.is_megakernel_backend
+    if store_kvcache:
+        from dfb_b200 import kv_store
+        from nanovllm.layers import attention
+
+        def counted_store(key, value, k_cache, v_cache, slot_mapping):
+            STORE_KVCACHE_CALLS[0] += 1
+            kv_store.store_kvcache(key, value, k_cache, v_cache, slot_mapping)
+
+        attention.store_kvcache = counted_store
     return model_runner
 
 
