@@ -160,6 +160,38 @@ cudaError_t ensure_large_clusters(const void* fn) {
   return e;
 }
 
+// Largest cluster of the attention kernel that this device can co-schedule (16 needs the non-portable opt-in
+// and enough SMs in one GPC; 8 is guaranteed): asked once per device from the occupancy calculator, for the
+// heaviest cluster instantiation.  A partitioned or smaller part then merges wider rows through the ticket path.
+template <typename Kernel>
+int max_attention_cluster(Kernel kernel, int threads) {
+  static std::map<int, int> best;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 8;
+  {
+    std::lock_guard<std::mutex> lock(g_attr_mu);
+    auto it = best.find(dev);
+    if (it != best.end()) return it->second;
+  }
+  int result = 8;
+  if (ensure_large_clusters((const void*)kernel) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16, 8, 1);
+    cfg.blockDim = dim3(threads);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 16; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n >= 1) result = 16;
+    else (void)cudaGetLastError();
+  }
+  std::lock_guard<std::mutex> lock(g_attr_mu);
+  best[dev] = result;
+  return result;
+}
+
 struct Launcher {
   cudaStream_t stream;
   bool pdl;
@@ -711,7 +743,8 @@ int launch_attention(Launcher& L, DfbHandle* h, int layer, const bf16* qkv, cons
     return L.err;
   }
   // 2..16 chunks: the chunks of one (row, KV head) form a thread-block cluster and merge in shared memory
-  const int cluster = (nsplit >= 2 && nsplit <= kAttnClusterMax && ctas <= L.opt->attn_cluster) ? nsplit : 0;
+  int cluster = (nsplit >= 2 && nsplit <= kAttnClusterMax && ctas <= L.opt->attn_cluster) ? nsplit : 0;
+  if (cluster > 8 && cluster > max_attention_cluster(paged_attention_kernel<256, 1, true, 2 * kAttnChunk>, 256)) cluster = 0;
   const bool wide = ctas <= L.opt->attn_wide_ctas;
   const dim3 grid(nsplit, m.kv_heads, rows);
   auto go = [&](auto kernel, int threads) {
