@@ -312,6 +312,15 @@ struct DfbHandle {
   unsigned int published = 0;           // host: the value the next published step will carry
   cudaEvent_t burst_event = nullptr;
   int burst_rows = 0, burst_steps = 0;  // of the burst in flight (0 = none)
+  // fixed-slot runtime (dfb_slot_* / dfb_slots_*): host-side state of every slot
+  struct Slot {
+    bool active = false;
+    long long token = 0;        // input of the slot's next step
+    long long position = 0;     // pre-decode length of the slot's next step
+    float temperature = 0.f;
+    std::vector<int> table;     // the slot's block table (physical block ids)
+  };
+  std::vector<Slot> slots;
   int* burst_status() const { return burst_ring + kMaxBurst * kMaxRows; }
   volatile int* burst_done() const { return burst_ring + kMaxBurst * kMaxRows + 4; }
   cudaStream_t capture_stream = nullptr;
@@ -1515,6 +1524,102 @@ int dfb_decode_step_host_sampled(DfbHandle* h, int32_t rows, const int64_t* inpu
     h->last_status[2] = h->host_tokens[kMaxRows + 2]; h->last_status[3] = h->host_tokens[kMaxRows + 3];
     DFB_CUDA(cudaMemsetAsync(h->status, 0, sizeof(int) * 4, stream));
     return DFB_E_DEVICE_STATUS;
+  }
+  return 0;
+}
+
+// ---- fixed-slot runtime --------------------------------------------------------------------------------
+// The decode side of a continuous-batching engine: DFB_MAX_SLOTS fixed slots whose sequences come and go
+// between steps; a step packs the live slots, in slot order, into launches of at most DFB_MAX_ROWS rows (every
+// geometry is a cached graph, so a change of the live set never captures once dfb_warm has run), advances
+// tokens and positions on the host side of the slots, and reports which slots emitted.
+int dfb_slot_set(DfbHandle* h, int32_t slot, int32_t active, int64_t token, int64_t position,
+                 const int32_t* block_table, int32_t cols, float temperature) {
+  if (!h || slot < 0 || slot >= DFB_MAX_SLOTS) return DFB_E_BAD_ARG;
+  if (h->slots.empty()) h->slots.resize(DFB_MAX_SLOTS);
+  DfbHandle::Slot& s = h->slots[slot];
+  if (!active) { s = DfbHandle::Slot(); return 0; }   // retired: the scheduler may hand its blocks to someone else
+  if (!block_table || cols < 1) return DFB_E_BAD_ARG;
+  if (cols > h->max_pages) return DFB_E_TOO_LARGE;
+  if (token < 0 || token >= h->embed_rows() || position < 0 || position >= h->m.max_model_len) return DFB_E_BAD_ARG;
+  if (!(temperature >= 0.f)) return DFB_E_BAD_ARG;
+  for (int c = 0; c < cols; ++c)
+    if (block_table[c] < 0 || block_table[c] >= h->m.num_blocks) return DFB_E_BAD_ARG;
+  s.active = true; s.token = token; s.position = position; s.temperature = temperature;
+  s.table.assign(block_table, block_table + cols);
+  return 0;
+}
+
+int dfb_slot_get(DfbHandle* h, int32_t slot, int32_t* active, int64_t* token, int64_t* position) {
+  if (!h || slot < 0 || slot >= DFB_MAX_SLOTS) return DFB_E_BAD_ARG;
+  const bool known = !h->slots.empty();
+  if (active) *active = known && h->slots[slot].active ? 1 : 0;
+  if (token) *token = known ? h->slots[slot].token : 0;
+  if (position) *position = known ? h->slots[slot].position : 0;
+  return 0;
+}
+
+int dfb_slots_step(DfbHandle* h, long long* sampled_tokens, int32_t* emitted, dfb_stream_t stream) {
+  if (!h || !sampled_tokens || !emitted) return DFB_E_BAD_ARG;
+  for (int i = 0; i < DFB_MAX_SLOTS; ++i) { sampled_tokens[i] = 0; emitted[i] = 0; }
+  if (h->slots.empty()) return 0;
+  // live slots that have room for their next token: a slot whose position ran past its block table (the
+  // scheduler has to append a block first) or past the model length sits the step out and emits nothing
+  int live[DFB_MAX_SLOTS], n_live = 0;
+  for (int i = 0; i < DFB_MAX_SLOTS; ++i) {
+    const DfbHandle::Slot& s = h->slots[i];
+    if (!s.active) continue;
+    if (s.position >= h->m.max_model_len || s.position >= (long long)s.table.size() * h->m.block_size) continue;
+    live[n_live++] = i;
+  }
+  int first_error = 0;
+  for (int g0 = 0; g0 < n_live; g0 += kMaxRows) {
+    const int rows = n_live - g0 < kMaxRows ? n_live - g0 : kMaxRows;
+    int64_t ids[kMaxRows], pos[kMaxRows];
+    float temps[kMaxRows];
+    int32_t out[kMaxRows];
+    int cols = 1;
+    bool sampled = false;
+    for (int r = 0; r < rows; ++r) {
+      const DfbHandle::Slot& s = h->slots[live[g0 + r]];
+      ids[r] = s.token; pos[r] = s.position; temps[r] = s.temperature;
+      sampled = sampled || s.temperature > 1e-10f;
+      // columns the launch needs: those that hold this row's context (the tables may be longer)
+      const int need = (int)(s.position / h->m.block_size) + 1;
+      if (need > cols) cols = need;
+    }
+    std::vector<int32_t> bt((size_t)rows * cols, 0);   // right-padded with block 0, as the engine pads its tables
+    for (int r = 0; r < rows; ++r) {
+      const DfbHandle::Slot& s = h->slots[live[g0 + r]];
+      for (int c = 0; c < cols && c < (int)s.table.size(); ++c) bt[(size_t)r * cols + c] = s.table[c];
+    }
+    const int rc = dfb_decode_step_host_sampled(h, rows, ids, pos, bt.data(), cols, nullptr, sampled ? temps : nullptr,
+                                                out, stream);
+    if (rc && rc != DFB_E_DEVICE_STATUS) return rc;
+    if (rc && !first_error) first_error = rc;
+    for (int r = 0; r < rows; ++r) {
+      DfbHandle::Slot& s = h->slots[live[g0 + r]];
+      s.token = out[r];
+      s.position += 1;
+      sampled_tokens[live[g0 + r]] = out[r];
+      emitted[live[g0 + r]] = 1;
+    }
+  }
+  return first_error;
+}
+
+int dfb_slots_run(DfbHandle* h, int32_t max_steps, dfb_token_callback callback, void* context, dfb_stream_t stream) {
+  if (!h || !callback || max_steps < 1) return DFB_E_BAD_ARG;
+  long long tokens[DFB_MAX_SLOTS];
+  int32_t emitted[DFB_MAX_SLOTS];
+  for (int step = 0; step < max_steps; ++step) {
+    const int rc = dfb_slots_step(h, tokens, emitted, stream);
+    if (rc) return rc;
+    int any = 0;
+    for (int i = 0; i < DFB_MAX_SLOTS; ++i) any |= emitted[i];
+    if (!any) return 0;                       // nothing is live, or every live slot waits for a block
+    // the callback may retire, admit or re-point slots (dfb_slot_set) before the next step
+    if (callback(context, tokens, emitted, DFB_MAX_SLOTS)) return 0;
   }
   return 0;
 }

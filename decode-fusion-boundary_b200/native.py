@@ -21,6 +21,8 @@ HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persist
 DFB_ABI_VERSION = 2
 DFB_MAX_ROWS = 8
 DFB_MAX_BURST = 1024
+DFB_MAX_SLOTS = 32
+TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_longlong), C.POINTER(C.c_int32), C.c_int32)
 DFB_ATTN_CHUNK = 64
 DFB_TP_HANDLE_BYTES = 64
 DFB_OPT_USE_GRAPH, DFB_OPT_USE_PDL, DFB_OPT_LMHEAD_CTAS, DFB_OPT_TRACE = 1, 2, 3, 4
@@ -49,7 +51,7 @@ EXPORTS = (
     "dfb_lmhead_argmax_noalloc", "dfb_set_tensor_parallel", "dfb_tp_window_handle", "dfb_tp_open_peers",
     "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
     "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host", "dfb_warm",
-    "dfb_store_kvcache",
+    "dfb_store_kvcache", "dfb_slot_set", "dfb_slot_get", "dfb_slots_step", "dfb_slots_run",
 )
 
 
@@ -141,6 +143,10 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
     L.dfb_warm.argtypes = [vp, i32, i32, i32, vp]
+    L.dfb_slot_set.argtypes = [vp, i32, i32, C.c_int64, C.c_int64, vp, i32, f32]
+    L.dfb_slot_get.argtypes = [vp, i32, vp, vp, vp]
+    L.dfb_slots_step.argtypes = [vp, vp, vp, vp]
+    L.dfb_slots_run.argtypes = [vp, i32, TOKEN_CALLBACK, vp, vp]
     L.dfb_store_kvcache.argtypes = [vp, vp, C.c_int64, C.c_int64, vp, vp, vp, i32, i32, C.c_int64, vp, vp]
     L.dfb_decode_burst_enqueue.argtypes = [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.dfb_decode_burst_collect.argtypes = [vp, i32, vp, vp]

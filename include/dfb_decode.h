@@ -305,6 +305,32 @@ int dfb_decode_burst_host(DfbHandle* h, int32_t rows, int32_t steps, const int64
                           const int32_t* row_active, const float* temperatures, int32_t* out_tokens,
                           dfb_stream_t stream);
 
+/* Fixed-slot runtime: the decode side of a continuous-batching engine as the reference designed it (fixed rows
+ * whose sequences come and go, `set_slot(row, active, start_pos, ...)`, a token callback after every step:
+ * backends/megakernel/row_contract.py:1-24, csrc/tg_abi.h:185-199) and never built.  DFB_MAX_SLOTS slots live in
+ * the decoder; a step packs the live ones, in slot order, into launches of at most DFB_MAX_ROWS rows — more live
+ * slots than that become several launches per step — runs them from host state (one packed copy each), and then
+ * holds each slot's new token and position.  A slot whose next position lies beyond its block table (the
+ * scheduler has to append a block and call dfb_slot_set again) or beyond the model length sits the step out.
+ * A retired slot (active = 0) is simply no longer launched, so its freed blocks are never written again; every
+ * geometry is a cached graph (dfb_warm), so a change of the live set captures nothing.
+ *   dfb_slot_set   admit (active = 1: next input token, pre-decode length, block table, temperature; 0 = greedy)
+ *                  or retire (active = 0) a slot; also the way to give a live slot a longer block table;
+ *   dfb_slot_get   the slot's state as the runtime holds it;
+ *   dfb_slots_step one step of all live slots: sampled_tokens[DFB_MAX_SLOTS], emitted[DFB_MAX_SLOTS] (1 = this
+ *                  slot produced sampled_tokens[slot]); synchronises `stream`;
+ *   dfb_slots_run  steps until max_steps, until no slot emits, or until the callback returns non-zero; the
+ *                  callback (the reference's TgTokenCallback signature) runs on the calling thread after each
+ *                  step and may call dfb_slot_set.  Scheduling, preemption and prefill stay with the engine. */
+#define DFB_MAX_SLOTS 32
+typedef int (*dfb_token_callback)(void* context, const long long* sampled_tokens, const int32_t* emitted_rows,
+                                  int32_t batch_size);
+int dfb_slot_set(DfbHandle* h, int32_t slot, int32_t active, int64_t token, int64_t position,
+                 const int32_t* block_table, int32_t cols, float temperature);
+int dfb_slot_get(DfbHandle* h, int32_t slot, int32_t* active, int64_t* token, int64_t* position);
+int dfb_slots_step(DfbHandle* h, long long* sampled_tokens, int32_t* emitted, dfb_stream_t stream);
+int dfb_slots_run(DfbHandle* h, int32_t max_steps, dfb_token_callback callback, void* context, dfb_stream_t stream);
+
 /* Seed of the sampling noise (default 0) and restart of its stream.  A sampled row takes
  * argmax_i(logit_i / T - log E_i), E_i ~ Exp(1) clamped at 1e-10, which is the reference's
  * argmax(softmax(logits / T) / E) without the softmax pass.  E_i = -log(u_i), u_i = (top 23 bits of
