@@ -32,3 +32,30 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, status=None) -> No
         key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
         slot_mapping.data_ptr(), n, d, num_slots, status.data_ptr() if status is not None else None,
         torch.cuda.current_stream().cuda_stream), "dfb_store_kvcache")
+
+
+def prefill_attention(q, k, v, cu_seqlens, max_seqlen: int, softmax_scale: float):
+    """The reference's ``flash_attn_varlen_func(q, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=m,
+    max_seqlen_k=m, softmax_scale=s, causal=True)`` of ``layers/attention.py:64-70`` for the case without a
+    prefix cache: ``q`` ``[N, q_heads, 128]``, ``k`` / ``v`` ``[N, kv_heads, 128]`` bf16 CUDA tensors (any row
+    stride), ``cu_seqlens`` int32 ``[batch + 1]``; returns ``[N, q_heads, 128]`` bf16."""
+    import torch
+
+    from . import native
+
+    n, q_heads, head_dim = q.shape
+    kv_heads = k.shape[1]
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert q.stride(1) == head_dim and k.stride(1) == head_dim and v.stride(1) == head_dim
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("prefill_attention takes bf16 tensors")
+    if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_cuda:
+        raise TypeError("cu_seqlens must be an int32 CUDA tensor")
+    out = torch.empty(n, q_heads, head_dim, dtype=torch.bfloat16, device=q.device)
+    if n == 0:
+        return out
+    native.check(native.lib().dfb_prefill_attention(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1,
+        int(max_seqlen), q.stride(0), k.stride(0), v.stride(0), out.stride(0), q_heads, kv_heads, head_dim,
+        float(softmax_scale), torch.cuda.current_stream().cuda_stream), "dfb_prefill_attention")
+    return out

@@ -16,7 +16,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libdfb_decode.so"
 SOURCES = [PKG_DIR / "csrc" / "dfb_api.cu"]
-HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR / "csrc" / "dfb_tcgemv.cuh", PKG_DIR / "csrc" / "dfb_attnring.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
+HEADERS = [PKG_DIR / "csrc" / "dfb_kernels.cuh", PKG_DIR / "csrc" / "dfb_persistent.cuh", PKG_DIR / "csrc" / "dfb_rowgemv.cuh", PKG_DIR / "csrc" / "dfb_exchange.cuh", PKG_DIR / "csrc" / "dfb_pairgemv.cuh", PKG_DIR / "csrc" / "dfb_tcgemv.cuh", PKG_DIR / "csrc" / "dfb_attnring.cuh", PKG_DIR / "csrc" / "dfb_prefill.cuh", PKG_DIR.parent / "include" / "dfb_decode.h"]
 
 DFB_ABI_VERSION = 2
 DFB_MAX_ROWS = 8
@@ -52,6 +52,7 @@ EXPORTS = (
     "dfb_tp_open_loopback", "dfb_decode_step_host_sampled", "dfb_set_seed", "dfb_launch_lmhead_sample",
     "dfb_decode_burst_enqueue", "dfb_decode_burst_collect", "dfb_decode_burst_host", "dfb_warm",
     "dfb_store_kvcache", "dfb_slot_set", "dfb_slot_get", "dfb_slots_step", "dfb_slots_run",
+    "dfb_prefill_attention",
 )
 
 
@@ -143,6 +144,8 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
     L.dfb_warm.argtypes = [vp, i32, i32, i32, vp]
+    L.dfb_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                        i32, i32, i32, f32, vp]
     L.dfb_slot_set.argtypes = [vp, i32, i32, C.c_int64, C.c_int64, vp, i32, f32]
     L.dfb_slot_get.argtypes = [vp, i32, vp, vp, vp]
     L.dfb_slots_step.argtypes = [vp, vp, vp, vp]

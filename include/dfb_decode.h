@@ -400,6 +400,20 @@ int dfb_store_kvcache(const void* key, const void* value, int64_t key_stride, in
                       void* v_cache, const int32_t* slot_mapping, int32_t n_tokens, int32_t row_elems,
                       int64_t num_slots, int32_t* status, dfb_stream_t stream);
 
+/* Causal prefill attention over the prompt tokens of `batch` sequences laid back to back (the reference's
+ * flash_attn_varlen_func(..., causal=True) call of layers/attention.py:64-70, without a prefix cache: K / V are
+ * the projections of the same tokens).  q [N, q_heads, head_dim], k / v [N, kv_heads, head_dim], out [N, q_heads,
+ * head_dim], all bf16 device pointers with row strides in elements; sequence b is rows [cu_seqlens[b],
+ * cu_seqlens[b + 1]) (cu_seqlens: device int32 [batch + 1]); max_seqlen bounds the grid (a longer sequence would
+ * lose its tail rows).  head_dim 128, grouped-query attention with q_heads a multiple of kv_heads.  fp32
+ * accumulation and softmax, probabilities rounded to bf16 before they multiply V (as FlashAttention does).
+ * Allocates nothing, synchronises nothing.  The prefix-cache variant (K / V read back through block tables) is
+ * not built. */
+int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                          int32_t batch, int32_t max_seqlen, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                          int64_t out_stride, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float scale,
+                          dfb_stream_t stream);
+
 /* Final add+RMSNorm, tied LM head and greedy argmax WITHOUT any allocation.
  * (No counterpart in the reference: its LM head always runs inside a decoder
  * that allocated its scratch at start-up.)

@@ -64,3 +64,19 @@ def test_store_kvcache_argument_checks_need_no_device():
     assert lib.dfb_store_kvcache(one, one, 512, 1024, one, one, one, 1, 1024, 10, None, None) == -1    # stride < row
     assert lib.dfb_store_kvcache(one, one + 2, 1024, 1024, one, one, one, 1, 1024, 10, None, None) == -1  # misaligned
     assert lib.dfb_store_kvcache(one, one, 1024, 1024, one, one, one, 0, 1024, 10, None, None) == 0    # nothing to do
+
+
+def test_prefill_attention_argument_checks_need_no_device():
+    lib = native.lib()
+    one = 16
+    ok = (one, one, one, one, one, 1, 8, 4096, 4096, 4096, 2048, 16, 8, 128, 0.088, None)
+    bad = list(ok); bad[0] = None
+    assert lib.dfb_prefill_attention(*bad) == -1
+    bad = list(ok); bad[13] = 64                 # head_dim the kernel is not built for
+    assert lib.dfb_prefill_attention(*bad) == -2
+    bad = list(ok); bad[11], bad[12] = 16, 5     # q heads not a multiple of kv heads
+    assert lib.dfb_prefill_attention(*bad) == -2
+    bad = list(ok); bad[7] = 1000                # q stride shorter than a row
+    assert lib.dfb_prefill_attention(*bad) == -1
+    bad = list(ok); bad[8] = 4100                # k stride not a multiple of 8
+    assert lib.dfb_prefill_attention(*bad) == -1
