@@ -925,6 +925,60 @@ def run_store_kvcache(args):
                       "peak": peak_kind, "launches": len(times)}))
 
 
+def run_prefill_attention(args):
+    """``dfb_prefill_attention`` alone on BATCH sequences of LEN prompt tokens (q / k / v as slices of a fused
+    projection output, 16 / 8 heads of 128): CUDA events around each launch, median; causal FLOPs =
+    2 n^2 d Hq per sequence.  The library kernel the reference calls for this step (flash_attn_varlen_func) is
+    timed on the same tensors when it can be imported, as the point of comparison."""
+    import torch
+
+    import __graft_entry__  # noqa: F401
+    from dfb_b200.kv_store import prefill_attention
+
+    batch, length = (int(x) for x in args.prefill_attention.lower().split("x"))
+    torch.cuda.set_device(0)
+    hq, hkv, d = 16, 8, 128
+    n = batch * length
+    qkv = torch.randn(n, 4096, device="cuda").bfloat16()
+    q, k, v = qkv[:, :2048].view(n, hq, d), qkv[:, 2048:3072].view(n, hkv, d), qkv[:, 3072:].view(n, hkv, d)
+    cu = torch.arange(0, n + 1, length, dtype=torch.int32, device="cuda")
+    scale = d ** -0.5
+    flops = batch * 2.0 * length * length * d * hq
+
+    def timed(fn):
+        ts = []
+        for it in range(args.warmup + max(args.steps, 10)):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); out = fn(); b.record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                ts.append(1e3 * a.elapsed_time(b))
+        return statistics.median(ts), out
+
+    us, mine = timed(lambda: prefill_attention(q, k, v, cu, length, scale))
+    line = {"kernel": "prefill_attention_kernel", "batch": batch, "seq_len": length, "us": us,
+            "causal_flops": flops, "achieved_tflops": flops / us / 1e6}
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak_tf = float(peaks.get("bf16_tflops", 0) or 0)
+    if peak_tf:
+        line.update(peak_tflops=peak_tf, frac=flops / us / 1e6 / peak_tf, peak="measured cuBLAS bf16 burst")
+    try:
+        from flash_attn import flash_attn_varlen_func
+
+        fa_us, theirs = timed(lambda: flash_attn_varlen_func(q, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu,
+                                                             max_seqlen_q=length, max_seqlen_k=length,
+                                                             softmax_scale=scale, causal=True))
+        line.update(flash_attn_us=fa_us, flash_attn_tflops=flops / fa_us / 1e6,
+                    max_abs_diff_to_flash_attn=float((mine.float() - theirs.float()).abs().max()))
+    except Exception as exc:   # the comparison is optional
+        line["flash_attn"] = f"not timed: {type(exc).__name__}"
+    print(json.dumps(line))
+
+
 def run_cta_sweep(args):
     """Per-op time against the CTA count (the reference's TG_NUM_SMS diagnostic,
     backends/megakernel/taskgraph.py:68-83): the persistent kernel at 1 ... 148
@@ -1008,6 +1062,8 @@ def main():
     # profiling drivers
     ap.add_argument("--profile-step", action="store_true", help="run plain steps for a profiler instead of the benchmark")
     ap.add_argument("--cta-sweep", action="store_true", help="per-op time against the CTA count")
+    ap.add_argument("--prefill-attention", type=str, default="", metavar="BATCHxLEN",
+                    help="time dfb_prefill_attention alone, e.g. 8x512, next to flash_attn_varlen_func on the same inputs")
     ap.add_argument("--store-kvcache", type=int, default=0, metavar="TOKENS",
                     help="time dfb_store_kvcache (prefill-side KV write) alone for this many prompt tokens")
     ap.add_argument("--layers", type=int, default=28)
@@ -1031,6 +1087,8 @@ def main():
         run_cta_sweep(args)
     elif args.store_kvcache:
         run_store_kvcache(args)
+    elif args.prefill_attention:
+        run_prefill_attention(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

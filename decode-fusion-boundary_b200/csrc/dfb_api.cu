@@ -1424,6 +1424,7 @@ int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return DFB_E_BAD_ARG;
   cudaError_t e = ensure_dynamic_smem((const void*)prefill_attention_kernel, kPfSmemBytes);
   if (e != cudaSuccess) return (int)e;
+  prefer_carveout((const void*)prefill_attention_kernel, 100);   // two CTAs of 68 KB per SM (registers allow no more)
   PrefillArgs a = {};
   a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.out = (bf16*)out; a.cu_seqlens = cu_seqlens;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride; a.out_stride = out_stride;
