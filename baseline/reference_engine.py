@@ -127,6 +127,7 @@ def write_model_dir(path, seed: int = 0, layers: int = 28, vocab: int = 151936, 
 
 
 STORE_KVCACHE_CALLS = [0]   # calls of this repository's store_kvcache made by the reference's Attention.forward
+PREFILL_ATTENTION_CALLS = [0]   # ... and of its prefill attention
 
 
 def install_backend_switch(store_kvcache: bool = True):
@@ -134,7 +135,8 @@ def install_backend_switch(store_kvcache: bool = True):
     ``ModelRunner`` (engine/model_runner.py:10-13,80-95,315-376) then builds this
     repository's ``MegakernelBackend`` for ``decode_backend="megakernel"``.  With ``store_kvcache`` the
     reference's ``Attention.forward`` (layers/attention.py:59-64) also writes the prompt tokens' K / V into the
-    shared paged cache through this repository's kernel instead of its Triton kernel."""
+    shared paged cache through this repository's kernel instead of its Triton kernel, and runs the causal
+    attention of a prefill without prefix cache on this repository's kernel instead of FlashAttention."""
     import_reference()
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
@@ -153,6 +155,20 @@ def install_backend_switch(store_kvcache: bool = True):
             kv_store.store_kvcache(key, value, k_cache, v_cache, slot_mapping)
 
         attention.store_kvcache = counted_store
+        library_attention = attention.flash_attn_varlen_func
+
+        def prefill_attention(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, cu_seqlens_k, softmax_scale,
+                              causal, block_table=None):
+            # a prefill without prefix cache (K / V are the projections of the same tokens) runs on this
+            # repository's kernel; the prefix-cache case stays on the library kernel
+            if block_table is None and causal and max_seqlen_q == max_seqlen_k:
+                PREFILL_ATTENTION_CALLS[0] += 1
+                return kv_store.prefill_attention(q, k, v, cu_seqlens_q, max_seqlen_q, softmax_scale)
+            return library_attention(q, k, v, max_seqlen_q=max_seqlen_q, cu_seqlens_q=cu_seqlens_q,
+                                     max_seqlen_k=max_seqlen_k, cu_seqlens_k=cu_seqlens_k,
+                                     softmax_scale=softmax_scale, causal=causal, block_table=block_table)
+
+        attention.flash_attn_varlen_func = prefill_attention
     return model_runner
 
 

@@ -74,6 +74,8 @@ def test_megakernel_switch_inside_the_reference_engine(model_dir):
     assert runner.last_backend_used == "megakernel"
     # every prefill wrote its K / V rows through this repository's store_kvcache (28 layers per prefill pass)
     assert R.STORE_KVCACHE_CALLS[0] >= 2 * 28, R.STORE_KVCACHE_CALLS
+    # ... and attended over its prompt with this repository's prefill attention
+    assert R.PREFILL_ATTENTION_CALLS[0] >= 2 * 28, R.PREFILL_ATTENTION_CALLS
     for rep in (rep_single, rep_batch):
         for req in rep["requests"]:
             # prefill ran on the torch path, every decode step on this repository's kernels
