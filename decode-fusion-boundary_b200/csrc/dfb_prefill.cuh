@@ -10,7 +10,7 @@
 //     operand, 16 rows x 128 dims) stay in registers; K / V tiles of 64 positions are brought into shared memory
 //     (rows padded by 16 bytes, so that the fragment reads below are free of bank conflicts), two tiles in
 //     flight (cp.async double buffer);
-//   * S = Q K^T: K rows are the B operand directly (32-bit shared loads in fragment order); the causal mask is
+//   * S = Q K^T: K rows are the B operand directly (ldmatrix, two position tiles per instruction); the causal mask is
 //     applied on the diagonal tiles; online softmax in fp32 with one running (max, sum) per row, held by the four
 //     lanes that share the row;
 //   * O += P V: the S accumulators, rounded to bf16, ARE the A fragments of the second product (no trip through
@@ -48,6 +48,11 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s) : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -125,14 +130,17 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArg
     float s[8][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n) { s[n][0] = 0.f; s[n][1] = 0.f; s[n][2] = 0.f; s[n][3] = 0.f; }
+    // one ldmatrix.x4 brings the B fragments of two position tiles for one k-step: matrices (positions 16 np ..
+    // + 7, dims 16 ks .. + 7), (same positions, dims + 8), (positions + 8 .. + 15, dims 16 ks ..), (those, dims + 8)
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const unsigned char* krow = kt + (8 * n + g) * kPfRowBytes + 4 * t;   // position 8n + g, dims 2t, 2t + 1
+    for (int np = 0; np < 4; ++np) {
+      const unsigned char* kaddr = kt + (16 * np + (lane & 7) + (lane >> 4) * 8) * kPfRowBytes + ((lane >> 3) & 1) * 16;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
-        mma_bf16_16816_full(s[n], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+        uint32_t kb[4];
+        ldmatrix_x4(kb, kaddr + 32 * ks);
+        mma_bf16_16816_full(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[0], kb[1]);
+        mma_bf16_16816_full(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[2], kb[3]);
       }
     }
     // ---- scale, causal mask (and the tail of the sequence), online softmax ----
