@@ -136,7 +136,7 @@ def install_backend_switch(store_kvcache: bool = True):
     repository's ``MegakernelBackend`` for ``decode_backend="megakernel"``.  With ``store_kvcache`` the
     reference's ``Attention.forward`` (layers/attention.py:59-64) also writes the prompt tokens' K / V into the
     shared paged cache through this repository's kernel instead of its Triton kernel, and runs the causal
-    attention of a prefill without prefix cache on this repository's kernel instead of FlashAttention."""
+    attention of every prefill (with or without a prefix cache) on this repository's kernel instead of FlashAttention."""
     import_reference()
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
@@ -159,11 +159,12 @@ def install_backend_switch(store_kvcache: bool = True):
 
         def prefill_attention(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, cu_seqlens_k, softmax_scale,
                               causal, block_table=None):
-            # a prefill without prefix cache (K / V are the projections of the same tokens) runs on this
-            # repository's kernel; the prefix-cache case stays on the library kernel
-            if block_table is None and causal and max_seqlen_q == max_seqlen_k:
+            # both cases of the reference's call: K / V as the projections of the same tokens, or (prefix cache)
+            # as the layer's cache read through the block table
+            if causal:
                 PREFILL_ATTENTION_CALLS[0] += 1
-                return kv_store.prefill_attention(q, k, v, cu_seqlens_q, max_seqlen_q, softmax_scale)
+                return kv_store.prefill_attention(q, k, v, cu_seqlens_q, max_seqlen_q, softmax_scale,
+                                                  cu_seqlens_k=cu_seqlens_k, block_table=block_table)
             return library_attention(q, k, v, max_seqlen_q=max_seqlen_q, cu_seqlens_q=cu_seqlens_q,
                                      max_seqlen_k=max_seqlen_k, cu_seqlens_k=cu_seqlens_k,
                                      softmax_scale=softmax_scale, causal=causal, block_table=block_table)

@@ -1410,11 +1410,12 @@ int dfb_store_kvcache(const void* key, const void* value, int64_t key_stride, in
   return 0;
 }
 
-int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
-                          int32_t batch, int32_t max_seqlen, int64_t q_stride, int64_t k_stride, int64_t v_stride,
-                          int64_t out_stride, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float scale,
-                          dfb_stream_t stream) {
-  if (!q || !k || !v || !out || !cu_seqlens || batch < 1 || max_seqlen < 1) return DFB_E_BAD_ARG;
+int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens_q,
+                          const int32_t* cu_seqlens_k, int32_t batch, int32_t max_seqlen_q, int64_t q_stride,
+                          int64_t k_stride, int64_t v_stride, int64_t out_stride, int32_t q_heads, int32_t kv_heads,
+                          int32_t head_dim, float scale, const int32_t* block_tables, int32_t block_table_stride,
+                          int32_t block_size, int32_t num_blocks, int32_t* status, dfb_stream_t stream) {
+  if (!q || !k || !v || !out || !cu_seqlens_q || batch < 1 || max_seqlen_q < 1) return DFB_E_BAD_ARG;
   if (head_dim != kHeadDim || q_heads < 1 || kv_heads < 1 || q_heads % kv_heads) return DFB_E_GEOMETRY;
   // 16-byte pieces of K / V rows and 4-byte pieces of Q / out rows: aligned bases, strides in multiples of 8
   if (q_stride < (int64_t)q_heads * head_dim || out_stride < (int64_t)q_heads * head_dim ||
@@ -1422,14 +1423,17 @@ int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out
     return DFB_E_BAD_ARG;
   if ((q_stride | k_stride | v_stride | out_stride) % 8) return DFB_E_BAD_ARG;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return DFB_E_BAD_ARG;
+  if (block_tables && (block_table_stride < 1 || block_size < 1 || num_blocks < 1)) return DFB_E_BAD_ARG;
   cudaError_t e = ensure_dynamic_smem((const void*)prefill_attention_kernel, kPfSmemBytes);
   if (e != cudaSuccess) return (int)e;
   prefer_carveout((const void*)prefill_attention_kernel, 100);   // two CTAs of 68 KB per SM (registers allow no more)
   PrefillArgs a = {};
-  a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.out = (bf16*)out; a.cu_seqlens = cu_seqlens;
+  a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.out = (bf16*)out;
+  a.cu_seqlens = cu_seqlens_q; a.cu_seqlens_k = cu_seqlens_k ? cu_seqlens_k : cu_seqlens_q;
+  a.block_tables = block_tables; a.bt_stride = block_table_stride; a.block_size = block_size; a.num_blocks = num_blocks;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride; a.out_stride = out_stride;
-  a.q_heads = q_heads; a.kv_heads = kv_heads; a.scale = scale;
-  const dim3 grid((max_seqlen + kPfTile - 1) / kPfTile, q_heads, batch);
+  a.q_heads = q_heads; a.kv_heads = kv_heads; a.scale = scale; a.status = status;
+  const dim3 grid((max_seqlen_q + kPfTile - 1) / kPfTile, q_heads, batch);
   prefill_attention_kernel<<<grid, 128, kPfSmemBytes, (cudaStream_t)stream>>>(a);
   DFB_CUDA(cudaGetLastError());
   return 0;

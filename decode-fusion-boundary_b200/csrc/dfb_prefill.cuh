@@ -1,7 +1,9 @@
 // Causal prefill attention over the prompt tokens of a batch of sequences: the step on the other side of the
 // shared paged cache.  The reference calls FlashAttention for it (flash_attn_varlen_func with causal = True,
-// layers/attention.py:64-70); this is the same computation for the case without a prefix cache (K / V are the
-// fresh projections of the same tokens), written against the tensor cores with mma.sync:
+// layers/attention.py:64-70); this is the same computation, written against the tensor cores with mma.sync, for
+// both of its cases: without a prefix cache K / V are the fresh projections of the same tokens; with one they
+// are read back from the paged cache through the block tables, the sequence's keys outnumber its queries, and
+// query i attends to keys 0 .. i + (keys - queries) (the causal mask aligned to the last key, as FlashAttention):
 //
 //   * q [N, q_heads, 128], k / v [N, kv_heads, 128] bf16, tokens of all sequences back to back, sequence b =
 //     rows [cu_seqlens[b], cu_seqlens[b + 1]); grouped-query attention (q head h reads KV head
@@ -29,16 +31,23 @@ constexpr int kPfTile = 64;                      // query rows per CTA and KV po
 constexpr int kPfRowBytes = kHeadDim * 2 + 16;   // padded shared-memory row of a K / V tile
 constexpr int kPfTileBytes = kPfTile * kPfRowBytes;
 constexpr int kPfSmemBytes = 4 * kPfTileBytes;   // K and V, two buffers each
+constexpr int kKernelPrefill = 9;
 
 struct PrefillArgs {
   const __nv_bfloat16* q;
   const __nv_bfloat16* k;
   const __nv_bfloat16* v;
   __nv_bfloat16* out;
-  const int* cu_seqlens;        // [batch + 1]
-  long long q_stride, k_stride, v_stride, out_stride;   // elements between token rows
+  const int* cu_seqlens;        // [batch + 1] query rows
+  const int* cu_seqlens_k;      // [batch + 1] keys; equal to cu_seqlens without a prefix cache
+  const int* block_tables;      // null: k / v hold the keys of sequence b at rows cu_seqlens_k[b] ...; else
+                                // [batch, bt_stride] physical blocks and k / v are one layer's cache
+                                // [num_blocks, block_size] rows
+  int bt_stride, block_size, num_blocks;
+  long long q_stride, k_stride, v_stride, out_stride;   // elements between token rows (cache: between slots)
   int q_heads, kv_heads;
   float scale;
+  int* status;                  // optional device status word (a block id outside the cache)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -66,10 +75,12 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArg
   const int seq = blockIdx.z, head = blockIdx.y;
   const int kvh = head / (a.q_heads / a.kv_heads);
   const int seq_start = a.cu_seqlens[seq], seq_len = a.cu_seqlens[seq + 1] - seq_start;
+  const int k_start = a.cu_seqlens_k[seq], k_len = a.cu_seqlens_k[seq + 1] - k_start;
+  const int shift = max(k_len - seq_len, 0);      // keys before the first query (the cached prefix)
   const int q0 = blockIdx.x * kPfTile;            // first query row of this CTA inside the sequence
-  if (q0 >= seq_len) return;
+  if (q0 >= seq_len || k_len < 1) return;
   const int q_hi = min(q0 + kPfTile, seq_len);    // one past the CTA's last query row
-  const int n_tiles = (q_hi + kPfTile - 1) / kPfTile;   // causal: KV positions [0, q_hi)
+  const int n_tiles = (shift + q_hi + kPfTile - 1) / kPfTile;   // causal: key positions [0, shift + q_hi)
 
   auto k_tile = [&](int buf) { return pf_smem + buf * kPfTileBytes; };
   auto v_tile = [&](int buf) { return pf_smem + (2 + buf) * kPfTileBytes; };
@@ -82,10 +93,20 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArg
       const int idx = tid + 128 * i, row = idx >> 4, piece = idx & 15;
       unsigned char* kd = k_tile(buf) + row * kPfRowBytes + 16 * piece;
       unsigned char* vd = v_tile(buf) + row * kPfRowBytes + 16 * piece;
-      if (p0 + row < seq_len) {
-        const size_t tok = (size_t)(seq_start + p0 + row);
-        cp_async16(kd, a.k + tok * a.k_stride + (size_t)kvh * kHeadDim + 8 * piece);
-        cp_async16(vd, a.v + tok * a.v_stride + (size_t)kvh * kHeadDim + 8 * piece);
+      const int p = p0 + row;
+      long long tok = -1;                          // row of k / v that holds key p, or none
+      if (p < k_len) {
+        if (a.block_tables) {
+          const int block = a.block_tables[(size_t)seq * a.bt_stride + p / a.block_size];
+          if (block >= 0 && block < a.num_blocks) tok = (long long)block * a.block_size + p % a.block_size;
+          else if (piece == 0) report_status(a.status, kStatusBadBlock, kKernelPrefill, seq, block);   // row read as zeros
+        } else {
+          tok = k_start + p;
+        }
+      }
+      if (tok >= 0) {
+        cp_async16(kd, a.k + (size_t)tok * a.k_stride + (size_t)kvh * kHeadDim + 8 * piece);
+        cp_async16(vd, a.v + (size_t)tok * a.v_stride + (size_t)kvh * kHeadDim + 8 * piece);
       } else {
         *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
@@ -150,9 +171,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArg
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int pos = p0 + 8 * n + 2 * t + e;
-        const bool in = pos < seq_len;
-        s[n][e] = (in && pos <= r_lo) ? s[n][e] * sl2 : -INFINITY;
-        s[n][2 + e] = (in && pos <= r_hi) ? s[n][2 + e] * sl2 : -INFINITY;
+        const bool in = pos < k_len;
+        s[n][e] = (in && pos <= shift + r_lo) ? s[n][e] * sl2 : -INFINITY;
+        s[n][2 + e] = (in && pos <= shift + r_hi) ? s[n][2 + e] * sl2 : -INFINITY;
         t_lo = fmaxf(t_lo, s[n][e]);
         t_hi = fmaxf(t_hi, s[n][2 + e]);
       }

@@ -144,8 +144,8 @@ def lib() -> C.CDLL:
     L.dfb_decode_step_host_sampled.argtypes = [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.dfb_set_seed.argtypes = [vp, C.c_uint64]
     L.dfb_warm.argtypes = [vp, i32, i32, i32, vp]
-    L.dfb_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
-                                        i32, i32, i32, f32, vp]
+    L.dfb_prefill_attention.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                        i32, i32, i32, f32, vp, i32, i32, i32, vp, vp]
     L.dfb_slot_set.argtypes = [vp, i32, i32, C.c_int64, C.c_int64, vp, i32, f32]
     L.dfb_slot_get.argtypes = [vp, i32, vp, vp, vp]
     L.dfb_slots_step.argtypes = [vp, vp, vp, vp]

@@ -400,19 +400,27 @@ int dfb_store_kvcache(const void* key, const void* value, int64_t key_stride, in
                       void* v_cache, const int32_t* slot_mapping, int32_t n_tokens, int32_t row_elems,
                       int64_t num_slots, int32_t* status, dfb_stream_t stream);
 
-/* Causal prefill attention over the prompt tokens of `batch` sequences laid back to back (the reference's
- * flash_attn_varlen_func(..., causal=True) call of layers/attention.py:64-70, without a prefix cache: K / V are
- * the projections of the same tokens).  q [N, q_heads, head_dim], k / v [N, kv_heads, head_dim], out [N, q_heads,
- * head_dim], all bf16 device pointers with row strides in elements; sequence b is rows [cu_seqlens[b],
- * cu_seqlens[b + 1]) (cu_seqlens: device int32 [batch + 1]); max_seqlen bounds the grid (a longer sequence would
- * lose its tail rows).  head_dim 128, grouped-query attention with q_heads a multiple of kv_heads.  fp32
- * accumulation and softmax, probabilities rounded to bf16 before they multiply V (as FlashAttention does).
- * Allocates nothing, synchronises nothing.  The prefix-cache variant (K / V read back through block tables) is
- * not built. */
-int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
-                          int32_t batch, int32_t max_seqlen, int64_t q_stride, int64_t k_stride, int64_t v_stride,
-                          int64_t out_stride, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float scale,
-                          dfb_stream_t stream);
+/* Causal prefill attention over the prompt tokens of `batch` sequences laid back to back: the reference's
+ * flash_attn_varlen_func(..., causal=True[, block_table=...]) call of layers/attention.py:64-70, both cases.
+ * q [N, q_heads, head_dim] and out [N, q_heads, head_dim] hold the query tokens, sequence b = rows
+ * [cu_seqlens_q[b], cu_seqlens_q[b + 1]) (device int32 [batch + 1]); max_seqlen_q bounds the grid (a longer
+ * sequence would lose its tail rows).
+ *   without a prefix cache (block_tables = NULL): k / v [N, kv_heads, head_dim] are the projections of the same
+ *     tokens and cu_seqlens_k may be NULL (= cu_seqlens_q);
+ *   with one: k / v are ONE LAYER of the paged cache, [num_blocks * block_size, kv_heads, head_dim] rows with
+ *     k_stride / v_stride elements between slots, sequence b's keys 0 .. cu_seqlens_k[b + 1] - cu_seqlens_k[b] - 1
+ *     are found through block_tables[b, position / block_size] (device int32 [batch, block_table_stride]), and
+ *     query i attends to keys 0 .. i + (keys - queries) (the mask aligned to the last key, as FlashAttention).
+ * All tensors bf16, row strides in elements; head_dim 128, grouped-query attention with q_heads a multiple of
+ * kv_heads.  fp32 accumulation and softmax, probabilities rounded to bf16 before they multiply V (as
+ * FlashAttention does).  A block id outside [0, num_blocks) is never followed: the key row is read as zeros and
+ * `status` (NULL, or a device int32[4]) receives {DFB_STATUS_BAD_BLOCK, kernel id, sequence, block id}.
+ * Allocates nothing, synchronises nothing. */
+int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens_q,
+                          const int32_t* cu_seqlens_k, int32_t batch, int32_t max_seqlen_q, int64_t q_stride,
+                          int64_t k_stride, int64_t v_stride, int64_t out_stride, int32_t q_heads, int32_t kv_heads,
+                          int32_t head_dim, float scale, const int32_t* block_tables, int32_t block_table_stride,
+                          int32_t block_size, int32_t num_blocks, int32_t* status, dfb_stream_t stream);
 
 /* Final add+RMSNorm, tied LM head and greedy argmax WITHOUT any allocation.
  * (No counterpart in the reference: its LM head always runs inside a decoder

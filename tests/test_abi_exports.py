@@ -69,14 +69,16 @@ def test_store_kvcache_argument_checks_need_no_device():
 def test_prefill_attention_argument_checks_need_no_device():
     lib = native.lib()
     one = 16
-    ok = (one, one, one, one, one, 1, 8, 4096, 4096, 4096, 2048, 16, 8, 128, 0.088, None)
+    ok = (one, one, one, one, one, None, 1, 8, 4096, 4096, 4096, 2048, 16, 8, 128, 0.088, None, 0, 0, 0, None, None)
     bad = list(ok); bad[0] = None
     assert lib.dfb_prefill_attention(*bad) == -1
-    bad = list(ok); bad[13] = 64                 # head_dim the kernel is not built for
+    bad = list(ok); bad[14] = 64                 # head_dim the kernel is not built for
     assert lib.dfb_prefill_attention(*bad) == -2
-    bad = list(ok); bad[11], bad[12] = 16, 5     # q heads not a multiple of kv heads
+    bad = list(ok); bad[12], bad[13] = 16, 5     # q heads not a multiple of kv heads
     assert lib.dfb_prefill_attention(*bad) == -2
-    bad = list(ok); bad[7] = 1000                # q stride shorter than a row
+    bad = list(ok); bad[8] = 1000                # q stride shorter than a row
     assert lib.dfb_prefill_attention(*bad) == -1
-    bad = list(ok); bad[8] = 4100                # k stride not a multiple of 8
+    bad = list(ok); bad[9] = 4100                # k stride not a multiple of 8
+    assert lib.dfb_prefill_attention(*bad) == -1
+    bad = list(ok); bad[16] = one                # a block table without its geometry
     assert lib.dfb_prefill_attention(*bad) == -1

@@ -83,3 +83,56 @@ def test_prefill_attention_then_store_fill_the_cache_like_the_decode_path_reads_
     assert int((k_cache.float().abs().sum(dim=(2, 3)) > 0).sum()) == n          # no other slot was written
     want = _reference(q.cpu(), k.cpu(), v.cpu(), lens, d ** -0.5)
     assert float((out.float().cpu() - want).abs().max()) <= 2.0 ** -6
+
+
+@pytest.mark.parametrize("case", [((300, 44),), ((513, 1), (256, 256)), ((70, 70), (1000, 300), (64, 3))])
+def test_prefill_attention_with_prefix_cache(cuda_device, case):
+    """Keys read back from the paged cache through scattered block tables, fewer queries than keys: query i of a
+    sequence attends to keys 0 .. i + (keys - queries), like the last `queries` rows of a full causal pass."""
+    from dfb_b200 import native
+    from dfb_b200.kv_store import prefill_attention, store_kvcache
+
+    rng = np.random.Generator(np.random.Philox(key=95 + len(case)))
+    hq, hkv, d, bs = 16, 8, 128, 256
+    k_lens, q_lens = [c[0] for c in case], [c[1] for c in case]
+    n_k = sum(k_lens)
+    qkv = torch.from_numpy(rng.standard_normal((n_k, 4096), dtype=np.float32)).to(BF)
+    q_all, k_all, v_all = qkv[:, :2048].view(n_k, hq, d), qkv[:, 2048:3072].view(n_k, hkv, d), qkv[:, 3072:].view(n_k, hkv, d)
+    want_all = _reference(q_all, k_all, v_all, k_lens, d ** -0.5)          # full causal pass over every sequence
+    # scattered physical blocks, the whole of every sequence's K / V written through store_kvcache
+    need = [-(-n // bs) for n in k_lens]
+    pool = rng.permutation(sum(need) + 3).tolist()
+    tables, slots = [], []
+    for n, nb in zip(k_lens, need):
+        t = [pool.pop() for _ in range(nb)]
+        tables.append(t)
+        slots += [t[p // bs] * bs + p % bs for p in range(n)]
+    dev = qkv.cuda()
+    kd, vd = dev[:, 2048:3072].view(n_k, hkv, d), dev[:, 3072:].view(n_k, hkv, d)
+    k_cache = torch.zeros(sum(need) + 3, bs, hkv, d, dtype=BF, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    store_kvcache(kd, vd, k_cache, v_cache, torch.tensor(slots, dtype=torch.int32, device="cuda"))
+    # the queries: only the last q_len tokens of every sequence
+    rows, start = [], 0
+    for n, m in zip(k_lens, q_lens):
+        rows += list(range(start + n - m, start + n))
+        start += n
+    qd = dev[rows][:, :2048].contiguous().view(len(rows), hq, d)
+    cu_q = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor(np.concatenate([[0], np.cumsum(k_lens)]), dtype=torch.int32, device="cuda")
+    width = max(need)
+    bt = torch.tensor([t + [0] * (width - len(t)) for t in tables], dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    got = prefill_attention(qd, k_cache, v_cache, cu_q, max(q_lens), d ** -0.5, cu_seqlens_k=cu_k, block_table=bt,
+                            status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    diff = (got.float().cpu() - want_all[rows]).abs()
+    assert float(diff.max()) <= 2.0 ** -6, float(diff.max())
+    # a block id outside the cache is recorded, not followed
+    bad = bt.clone()
+    bad[0, 0] = k_cache.shape[0] + 5
+    prefill_attention(qd, k_cache, v_cache, cu_q, max(q_lens), d ** -0.5, cu_seqlens_k=cu_k, block_table=bad, status=status)
+    torch.cuda.synchronize()
+    st = status.tolist()
+    assert st[0] == native.DFB_STATUS_BAD_BLOCK and st[2] == 0 and st[3] == k_cache.shape[0] + 5
