@@ -1423,18 +1423,26 @@ int dfb_prefill_attention(const void* q, const void* k, const void* v, void* out
     return DFB_E_BAD_ARG;
   if ((q_stride | k_stride | v_stride | out_stride) % 8) return DFB_E_BAD_ARG;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return DFB_E_BAD_ARG;
-  if (block_tables && (block_table_stride < 1 || block_size < 1 || num_blocks < 1)) return DFB_E_BAD_ARG;
-  cudaError_t e = ensure_dynamic_smem((const void*)prefill_attention_kernel, kPfSmemBytes);
+  int block_shift = 0;
+  if (block_tables) {
+    if (block_table_stride < 1 || block_size < 1 || num_blocks < 1 || !cu_seqlens_k) return DFB_E_BAD_ARG;
+    if (block_size & (block_size - 1)) return DFB_E_GEOMETRY;   // blocks of a power of two tokens (the reference's are 256)
+    while ((1 << block_shift) < block_size) ++block_shift;
+  }
+  const void* fn = block_tables ? (const void*)prefill_attention_kernel<true> : (const void*)prefill_attention_kernel<false>;
+  cudaError_t e = ensure_dynamic_smem(fn, kPfSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  prefer_carveout((const void*)prefill_attention_kernel, 100);   // two CTAs of 68 KB per SM (registers allow no more)
+  prefer_carveout(fn, 100);   // two CTAs of 68 KB per SM (registers allow no more)
   PrefillArgs a = {};
   a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.out = (bf16*)out;
   a.cu_seqlens = cu_seqlens_q; a.cu_seqlens_k = cu_seqlens_k ? cu_seqlens_k : cu_seqlens_q;
   a.block_tables = block_tables; a.bt_stride = block_table_stride; a.block_size = block_size; a.num_blocks = num_blocks;
+  a.block_shift = block_shift;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride; a.out_stride = out_stride;
   a.q_heads = q_heads; a.kv_heads = kv_heads; a.scale = scale; a.status = status;
   const dim3 grid((max_seqlen_q + kPfTile - 1) / kPfTile, q_heads, batch);
-  prefill_attention_kernel<<<grid, 128, kPfSmemBytes, (cudaStream_t)stream>>>(a);
+  if (block_tables) prefill_attention_kernel<true><<<grid, 128, kPfSmemBytes, (cudaStream_t)stream>>>(a);
+  else prefill_attention_kernel<false><<<grid, 128, kPfSmemBytes, (cudaStream_t)stream>>>(a);
   DFB_CUDA(cudaGetLastError());
   return 0;
 }

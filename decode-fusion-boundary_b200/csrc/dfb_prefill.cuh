@@ -43,7 +43,7 @@ struct PrefillArgs {
   const int* block_tables;      // null: k / v hold the keys of sequence b at rows cu_seqlens_k[b] ...; else
                                 // [batch, bt_stride] physical blocks and k / v are one layer's cache
                                 // [num_blocks, block_size] rows
-  int bt_stride, block_size, num_blocks;
+  int bt_stride, block_size, block_shift, num_blocks;   // block_size = 1 << block_shift
   long long q_stride, k_stride, v_stride, out_stride;   // elements between token rows (cache: between slots)
   int q_heads, kv_heads;
   float scale;
@@ -68,6 +68,9 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s) : "memory");
 }
 
+// PAGED: keys come from the paged cache through the block tables (block_size a power of two: the position's
+// block and offset are a shift and a mask); else they are rows of k / v, and the copy loop has no table walk.
+template <bool PAGED>
 __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) unsigned char pf_smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -96,9 +99,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(const PrefillArg
       const int p = p0 + row;
       long long tok = -1;                          // row of k / v that holds key p, or none
       if (p < k_len) {
-        if (a.block_tables) {
-          const int block = a.block_tables[(size_t)seq * a.bt_stride + p / a.block_size];
-          if (block >= 0 && block < a.num_blocks) tok = (long long)block * a.block_size + p % a.block_size;
+        if (PAGED) {
+          const int block = a.block_tables[(size_t)seq * a.bt_stride + (p >> a.block_shift)];
+          if (block >= 0 && block < a.num_blocks) tok = ((long long)block << a.block_shift) + (p & (a.block_size - 1));
           else if (piece == 0) report_status(a.status, kStatusBadBlock, kKernelPrefill, seq, block);   // row read as zeros
         } else {
           tok = k_start + p;
